@@ -1,0 +1,64 @@
+// Shared helpers of the sm_100a kernels: error reporting to the host, dtype
+// tags, loads and stores that convert to and from float.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define AYK_DTYPE_F32 0
+#define AYK_DTYPE_BF16 1
+
+#define AYK_ACT_NONE 0
+#define AYK_ACT_GELU_ERF 1
+#define AYK_ACT_GELU_TANH 2
+#define AYK_ACT_QUICK_GELU 3
+
+#define AYK_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Every entry point returns 0 or a negative code; the text is read back with
+// ayk_last_error().
+int ayk_fail(const char* fmt, ...);
+int ayk_check_launch(const char* what);
+
+#define AYK_REQUIRE(cond, ...)                 \
+  do {                                         \
+    if (!(cond)) return ayk_fail(__VA_ARGS__); \
+  } while (0)
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float apply_activation(float x, int act) {
+  // Formulas in 32-bit, as the reference's activation kernels compute them
+  // (kernel/triton/activation.py:145-154).
+  if (act == AYK_ACT_GELU_ERF) return x * 0.5f * (1.0f + erff(x * 0.7071067811865475f));
+  if (act == AYK_ACT_GELU_TANH) {
+    float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return x * 0.5f * (1.0f + tanhf(inner));
+  }
+  if (act == AYK_ACT_QUICK_GELU) return x / (1.0f + expf(-1.702f * x));
+  return x;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}

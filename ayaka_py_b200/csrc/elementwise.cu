@@ -1,0 +1,173 @@
+// Embedding + learned positions, LayerNorm, paged KV append; and the host-side
+// error channel of the library.
+//
+// Reference counterparts: embedding lookup kernel/triton/embedding.py:162-175
+// plus the wpe add of models/gpt2.py:516-517 (fused here); LayerNorm
+// kernel/triton/norm.py:311-374 (two-pass mean / biased variance in 32-bit);
+// KV scatter kernel/triton/cache/paged_kv.py:141-214.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+// ------------------------------------------------------------ error channel --
+static thread_local char g_error[512] = "";
+
+int ayk_fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return -1;
+}
+
+int ayk_check_launch(const char* what) {
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return ayk_fail("%s: %s", what, cudaGetErrorString(err));
+  return 0;
+}
+
+AYK_EXPORT const char* ayk_last_error() { return g_error; }
+
+AYK_EXPORT int ayk_init(int device) {
+  cudaError_t err = cudaSetDevice(device);
+  if (err != cudaSuccess) return ayk_fail("cudaSetDevice(%d): %s", device, cudaGetErrorString(err));
+  cudaDeviceProp prop;
+  err = cudaGetDeviceProperties(&prop, device);
+  if (err != cudaSuccess) return ayk_fail("cudaGetDeviceProperties: %s", cudaGetErrorString(err));
+  if (prop.major != 10) return ayk_fail("this library is built for sm_100a, device %d is sm_%d%d", device, prop.major, prop.minor);
+  return 0;
+}
+
+// ------------------------------------------------------------------- embed --
+template <typename W>
+__global__ void embed_kernel(float* __restrict__ out, const int* __restrict__ tok,
+                             const int* __restrict__ pos, const W* __restrict__ wte,
+                             const W* __restrict__ wpe, int d) {
+  int t = blockIdx.x;
+  const W* e = wte + (size_t)tok[t] * d;
+  const W* p = wpe ? wpe + (size_t)pos[t] * d : nullptr;
+  float* o = out + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = to_float<W>(e[i]);
+    if (p) v += to_float<W>(p[i]);
+    o[i] = v;
+  }
+}
+
+// out[t, :] = wte[tok[t], :] (+ wpe[pos[t], :]) as float32.  The host has
+// checked the ids against the table sizes.
+AYK_EXPORT int ayk_embed(float* out, const int* tok, const int* pos, const void* wte,
+                         const void* wpe, int T, int d, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  int threads = d >= 256 ? 256 : 128;
+  if (dtype == AYK_DTYPE_F32)
+    embed_kernel<float><<<T, threads, 0, stream>>>(out, tok, pos, (const float*)wte, (const float*)wpe, d);
+  else if (dtype == AYK_DTYPE_BF16)
+    embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(out, tok, pos, (const __nv_bfloat16*)wte,
+                                                          (const __nv_bfloat16*)wpe, d);
+  else
+    return ayk_fail("ayk_embed: unknown dtype %d", dtype);
+  return ayk_check_launch("ayk_embed");
+}
+
+// --------------------------------------------------------------- layernorm --
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarp; ++w) total += red[w];   // same order in every thread
+  return total;
+}
+
+template <typename O>
+__global__ void layernorm_kernel(O* __restrict__ out, const float* __restrict__ x,
+                                 const float* __restrict__ gamma, const float* __restrict__ beta,
+                                 const int* __restrict__ rows, int d, float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * d;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = src[i];
+    row[i] = v;
+    s += v;
+  }
+  float mean = block_sum(s, red) / (float)d;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float c = row[i] - mean;
+    q += c * c;
+  }
+  float var = block_sum(q, red) / (float)d;
+  float rstd = rsqrtf(var + eps);
+  O* dst = out + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = (row[i] - mean) * rstd * gamma[i] + (beta ? beta[i] : 0.f);
+    dst[i] = from_float<O>(v);
+  }
+}
+
+// out[r, :] = LayerNorm(x[rows ? rows[r] : r, :]); x float32, statistics and
+// affine in 32-bit, result stored as out_dtype.
+AYK_EXPORT int ayk_layernorm(void* out, const float* x, const float* gamma, const float* beta,
+                             const int* rows, int n_rows, int d, float eps, int out_dtype,
+                             cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AYK_REQUIRE(d >= 1 && (size_t)d * 4 <= 48 * 1024, "ayk_layernorm: width %d is not in [1, 12288]", d);
+  int threads = d >= 1024 ? 256 : 128;
+  size_t smem = (size_t)d * sizeof(float);
+  if (out_dtype == AYK_DTYPE_F32)
+    layernorm_kernel<float><<<n_rows, threads, smem, stream>>>((float*)out, x, gamma, beta, rows, d, eps);
+  else if (out_dtype == AYK_DTYPE_BF16)
+    layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>((__nv_bfloat16*)out, x, gamma, beta, rows, d, eps);
+  else
+    return ayk_fail("ayk_layernorm: unknown dtype %d", out_dtype);
+  return ayk_check_launch("ayk_layernorm");
+}
+
+// --------------------------------------------------------------- kv append --
+template <typename T>
+__global__ void kv_append_kernel(T* __restrict__ kcache, T* __restrict__ vcache,
+                                 const T* __restrict__ k, const T* __restrict__ v, int row_stride,
+                                 const int* __restrict__ row_req, const int* __restrict__ pos,
+                                 const int* __restrict__ table, int table_stride, int page_size,
+                                 int width) {
+  int t = blockIdx.x;
+  int p = pos[t];
+  int page = table[(size_t)row_req[t] * table_stride + p / page_size];
+  if (page <= 0) return;   // the padding page holds nothing; a live row never maps to it
+  size_t dst = ((size_t)page * page_size + (p % page_size)) * width;
+  const T* ks = k + (size_t)t * row_stride;
+  const T* vs = v + (size_t)t * row_stride;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    kcache[dst + i] = ks[i];
+    vcache[dst + i] = vs[i];
+  }
+}
+
+// Writes the keys and values of the step's rows into their pages:
+// cache[page(row), pos % P, :, :] = k[row, :]; page(row) = table[row_req[row], pos / P].
+// width = kv_heads * head_dim; k and v are rows of a wider matrix (row_stride elements).
+AYK_EXPORT int ayk_kv_append(void* kcache, void* vcache, const void* k, const void* v,
+                             int row_stride, const int* row_req, const int* pos, const int* table,
+                             int table_stride, int page_size, int T, int width, int dtype,
+                             cudaStream_t stream) {
+  if (T == 0) return 0;
+  int threads = width >= 512 ? 256 : 128;
+  if (dtype == AYK_DTYPE_F32)
+    kv_append_kernel<float><<<T, threads, 0, stream>>>((float*)kcache, (float*)vcache, (const float*)k,
+                                                       (const float*)v, row_stride, row_req, pos, table,
+                                                       table_stride, page_size, width);
+  else if (dtype == AYK_DTYPE_BF16)
+    kv_append_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
+        (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+        row_stride, row_req, pos, table, table_stride, page_size, width);
+  else
+    return ayk_fail("ayk_kv_append: unknown dtype %d", dtype);
+  return ayk_check_launch("ayk_kv_append");
+}

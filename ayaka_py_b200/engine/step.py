@@ -1,0 +1,168 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A batch holds at most one entry per request: a contiguous run of that request's
+next tokens, starting at its committed length; portions of prompts ride beside
+single decoded tokens, cut anywhere (the reference's slices,
+``sched/plan.py:124-162``; packed without padding, ``:316-319``).  The step runs
+only these tokens, from the cache that earlier steps left, and returns float32
+logits at the wanted places only, in the order of the entries and of ``want``.
+
+All step metadata is packed into one pinned int32 buffer and copied to the
+device with one transfer; kernels read block tables and row maps from there
+(the reference uploads one tensor per field, ``runner/buffers.py:369-462``, and
+builds a CSR slot list per step, which these kernels do not need).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..parts.base import KVNeed
+
+
+@dataclass
+class StepEntry:
+    slot: int                    # the request's slot in the cache manager
+    start: int                   # position of the first token (= tokens cached so far)
+    tokens: Sequence[int]        # its next tokens
+    want: Sequence[int] = ()     # places among ``tokens`` whose logits are asked for
+
+
+@dataclass
+class StepContext:
+    """What parts may read during a step.  Device tensors are int32."""
+    num_rows: int
+    num_requests: int
+    num_wanted: int
+    tokens: torch.Tensor         # [T]
+    positions: torch.Tensor      # [T] absolute positions
+    row_req: torch.Tensor        # [T] index of the row's request within this step
+    want_rows: torch.Tensor      # [S] rows whose logits are wanted
+    req_q_start: torch.Tensor    # [R + 1] first row of each request
+    req_pos0: torch.Tensor       # [R] position of each request's first row
+    req_slot: torch.Tensor       # [R] cache slot of each request
+    req_kv_len: torch.Tensor     # [R] tokens cached after this step
+    tables: list                 # per cache group: [R, columns] block-table rows, or None
+    cache: CacheManager
+    dtype: torch.dtype
+    host: dict = field(default_factory=dict)   # the same arrays as NumPy, for host-side decisions
+    max_q_len: int = 1
+    max_kv_len: int = 1
+
+
+class StepRunner:
+    def __init__(self, model, cache: CacheManager, max_tokens: int = 2048, max_requests: int | None = None):
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.max_requests = max_requests or cache.max_requests
+        self.kv_groups = [g for g, spec in enumerate(cache.groups) if isinstance(spec.need, KVNeed)]
+        self._allocate(max_tokens)
+        self.steps = 0
+        self.rows_run = 0
+
+    def _allocate(self, max_tokens: int) -> None:
+        T, R, C = max_tokens, self.max_requests, self.cache.columns
+        sizes = {"tokens": T, "positions": T, "row_req": T, "want_rows": T,
+                 "req_q_start": R + 1, "req_pos0": R, "req_slot": R, "req_kv_len": R}
+        for g in self.kv_groups:
+            sizes[f"table{g}"] = R * C
+        self.max_tokens = T
+        self.offsets, total = {}, 0
+        for name, n in sizes.items():
+            self.offsets[name] = (total, n)
+            total += (n + 3) // 4 * 4            # 16-byte aligned fields
+        self.host_buf = torch.zeros(total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        self.host_np = self.host_buf.numpy()
+        self.dev_buf = torch.zeros(total, dtype=torch.int32, device=self.device)
+        self._copied = None      # event after the last upload: the pinned buffer is free again
+
+    def _field(self, buf, name: str, n: int):
+        lo, cap = self.offsets[name]
+        return buf[lo:lo + n]
+
+    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        if self._copied is not None:
+            self._copied.synchronize()
+        R = len(entries)
+        if R > self.max_requests:
+            raise ValueError(f"{R} requests in one step, the engine was built for {self.max_requests}")
+        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=R)
+        if (counts < 1).any():
+            raise ValueError("every entry must bring at least one token")
+        T = int(counts.sum())
+        if T > self.max_tokens:
+            self._allocate(max(T, 2 * self.max_tokens))
+        slots = np.fromiter((e.slot for e in entries), dtype=np.int64, count=R)
+        if len(set(slots.tolist())) != R:
+            raise ValueError("a request appears twice in one step")
+        starts = np.fromiter((e.start for e in entries), dtype=np.int64, count=R)
+        ends = starts + counts
+        for e, end in zip(entries, ends):
+            if e.slot not in self.cache.request_of or not self.cache.in_step[e.slot]:
+                raise RuntimeError(f"slot {e.slot} was not reserved for this step")
+            if e.start != self.cache.length[e.slot]:
+                raise ValueError(f"slot {e.slot}: entry starts at {e.start}, the cache holds {self.cache.length[e.slot]}")
+        limit = self.model.max_positions
+        if int(ends.max()) > limit:
+            raise ValueError(f"a request would reach {int(ends.max())} tokens, the model has {limit} positions")
+
+        h = self.host_np
+        q_start = np.zeros(R + 1, dtype=np.int64)
+        np.cumsum(counts, out=q_start[1:])
+        tok = self._field(h, "tokens", T)
+        pos = self._field(h, "positions", T)
+        row_req = self._field(h, "row_req", T)
+        wanted = []
+        for r, e in enumerate(entries):
+            a, b = int(q_start[r]), int(q_start[r + 1])
+            tok[a:b] = np.asarray(e.tokens, dtype=np.int64)
+            pos[a:b] = np.arange(e.start, e.start + (b - a))
+            row_req[a:b] = r
+            for w in e.want:
+                if not 0 <= w < b - a:
+                    raise ValueError(f"want {w} is outside the entry's {b - a} tokens")
+                wanted.append(a + int(w))
+        if tok.min() < 0 or tok.max() >= self.model.vocab_size:
+            raise ValueError(f"token id outside [0, {self.model.vocab_size})")
+        S = len(wanted)
+        self._field(h, "want_rows", S)[:] = wanted
+        self._field(h, "req_q_start", R + 1)[:] = q_start
+        self._field(h, "req_pos0", R)[:] = starts
+        self._field(h, "req_slot", R)[:] = slots
+        self._field(h, "req_kv_len", R)[:] = ends
+        C = self.cache.columns
+        for g in self.kv_groups:
+            self._field(h, f"table{g}", R * C)[:] = self.cache.table_rows(g, slots).reshape(-1)
+        self.dev_buf.copy_(self.host_buf, non_blocking=True)
+        if self.dev_buf.is_cuda:
+            self._copied = torch.cuda.Event()
+            self._copied.record()
+
+        d = self.dev_buf
+        tables = [None] * len(self.cache.groups)
+        for g in self.kv_groups:
+            tables[g] = self._field(d, f"table{g}", R * C).view(R, C)
+        self.steps += 1
+        self.rows_run += T
+        return StepContext(
+            num_rows=T, num_requests=R, num_wanted=S,
+            tokens=self._field(d, "tokens", T), positions=self._field(d, "positions", T),
+            row_req=self._field(d, "row_req", T), want_rows=self._field(d, "want_rows", S),
+            req_q_start=self._field(d, "req_q_start", R + 1), req_pos0=self._field(d, "req_pos0", R),
+            req_slot=self._field(d, "req_slot", R), req_kv_len=self._field(d, "req_kv_len", R),
+            tables=tables, cache=self.cache, dtype=self.model.dtype,
+            host={"q_start": q_start, "pos0": starts, "slots": slots, "kv_len": ends, "counts": counts},
+            max_q_len=int(counts.max()), max_kv_len=int(ends.max()))
+
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Logits [S, V] float32 on the device.  The caller has reserved the
+        step in the cache manager and commits it afterwards."""
+        return self.model.forward(self.prepare(entries))

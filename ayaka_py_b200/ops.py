@@ -1,0 +1,220 @@
+"""Python face of the CUDA library: one function per kernel, torch tensors in.
+
+The library is built by ``csrc/build.py`` (at the first call if it is missing
+or stale) and loaded with ctypes.  There is no fallback: when the library
+cannot be built or loaded, or a tensor does not live on a CUDA device, the call
+raises.  Every function launches on torch's current stream.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_DTYPE_TAG = {torch.float32: F32, torch.bfloat16: BF16}
+ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "quick_gelu": 3}
+
+_lib = None
+_lock = threading.Lock()
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or its launch failed."""
+
+
+def library():
+    """The loaded library; builds it first if needed."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = _build.build()
+                lib = ctypes.CDLL(str(path))
+                lib.ayk_last_error.restype = ctypes.c_char_p
+                _lib = lib
+    return _lib
+
+
+def library_file() -> str:
+    return str(_build.library_path())
+
+
+_initialised = False
+
+
+def _ready():
+    global _initialised
+    lib = library()
+    if not _initialised:
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this package runs its kernels on a B200 and has no CPU path")
+        _check(lib.ayk_init(ctypes.c_int(torch.cuda.current_device())))
+        _initialised = True
+    return lib
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        raise KernelError(library().ayk_last_error().decode("utf-8", "replace"))
+
+
+def _ptr(t: torch.Tensor | None):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("tensor is not on a CUDA device")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _tag(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_TAG[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _i32(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+    return t
+
+
+# ---------------------------------------------------------------- kernels --
+
+def embed(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor,
+          position_table: torch.Tensor | None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = table[tokens[t]] (+ position_table[positions[t]]), float32 [T, d]."""
+    lib = _ready()
+    T, d = tokens.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty((T, d), dtype=torch.float32, device=table.device)
+    if position_table is not None and (position_table.dtype != table.dtype or position_table.shape[1] != d):
+        raise KernelError("position table must match the token table in dtype and width")
+    if not table.is_contiguous() or (position_table is not None and not position_table.is_contiguous()):
+        raise KernelError("embedding tables must be contiguous")
+    _check(lib.ayk_embed(_ptr(out), _ptr(_i32(tokens, "tokens")), _ptr(_i32(positions, "positions")),
+                         _ptr(table), _ptr(position_table), ctypes.c_int(T), ctypes.c_int(d),
+                         ctypes.c_int(_tag(table.dtype)), _stream()))
+    return out
+
+
+def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor | None, eps: float,
+              out_dtype: torch.dtype, rows: torch.Tensor | None = None,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """LayerNorm of float32 rows (of ``x[rows]`` when rows is given), result as out_dtype."""
+    lib = _ready()
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("layernorm input must be contiguous float32")
+    d = x.shape[-1]
+    n = x.shape[0] if rows is None else rows.numel()
+    if gamma.dtype != torch.float32 or gamma.numel() != d or (beta is not None and (beta.dtype != torch.float32 or beta.numel() != d)):
+        raise KernelError("layernorm weight and bias must be float32 of the row width")
+    if out is None:
+        out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    _check(lib.ayk_layernorm(_ptr(out), _ptr(x), _ptr(gamma), _ptr(beta),
+                             _ptr(None if rows is None else _i32(rows, "rows")), ctypes.c_int(n),
+                             ctypes.c_int(d), ctypes.c_float(eps), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+              activation: str = "none", residual: torch.Tensor | None = None,
+              out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """act(a[M,K] @ w[N,K]^T + bias) (+ residual) on the FP32 pipes."""
+    lib = _ready()
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or a.dtype != w.dtype or not a.is_contiguous() or not w.is_contiguous():
+        raise KernelError(f"gemm operands do not fit: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}")
+    out_dtype = out_dtype or a.dtype
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    for name, t in (("bias", bias), ("residual", residual)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError(f"{name} must be contiguous float32")
+    if residual is not None and tuple(residual.shape) != (M, N):
+        raise KernelError("residual must have the output's shape")
+    _check(lib.ayk_gemm_simt(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
+                             ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]),
+                             ctypes.c_int(_tag(a.dtype)), ctypes.c_int(_tag(out_dtype)), _stream()))
+    return out
+
+
+def kv_append(kcache: torch.Tensor, vcache: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+              row_req: torch.Tensor, positions: torch.Tensor, table: torch.Tensor) -> None:
+    """cache[page, pos % P] = k/v row; k and v are column slices [T, Hkv*Dh] of one matrix."""
+    lib = _ready()
+    T, width = k.shape
+    pages, P, Hkv, Dh = kcache.shape
+    if width != Hkv * Dh or v.shape != k.shape or k.stride(1) != 1 or v.stride(1) != 1 or k.stride(0) != v.stride(0):
+        raise KernelError("kv_append: keys and values must be [T, kv_heads*head_dim] slices with one row stride")
+    if k.dtype != kcache.dtype or not kcache.is_contiguous() or not vcache.is_contiguous():
+        raise KernelError("kv_append: cache must be contiguous and of the rows' dtype")
+    _check(lib.ayk_kv_append(_ptr(kcache), _ptr(vcache), _ptr(k), _ptr(v), ctypes.c_int(k.stride(0)),
+                             _ptr(_i32(row_req, "row_req")), _ptr(_i32(positions, "positions")),
+                             _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)), ctypes.c_int(P),
+                             ctypes.c_int(T), ctypes.c_int(width), ctypes.c_int(_tag(k.dtype)), _stream()))
+
+
+def attention_simt(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, table: torch.Tensor,
+                   req_q_start: torch.Tensor, req_pos0: torch.Tensor, total_rows: int, num_heads: int,
+                   scale: float, window: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of the step's rows over the paged cache.  q: [T, H*Dh] slice."""
+    lib = _ready()
+    pages, P, Hkv, Dh = kcache.shape
+    T = q.shape[0]
+    if q.shape[1] != num_heads * Dh or q.stride(1) != 1 or q.dtype != kcache.dtype:
+        raise KernelError("attention: q must be a [T, heads*head_dim] slice of the cache's dtype")
+    if out is None:
+        out = torch.empty((T, num_heads * Dh), dtype=q.dtype, device=q.device)
+    R = req_pos0.numel()
+    _check(lib.ayk_attention_simt(_ptr(out), _ptr(q), ctypes.c_int(q.stride(0)), _ptr(kcache), _ptr(vcache),
+                                  _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)),
+                                  _ptr(_i32(req_q_start, "req_q_start")), _ptr(_i32(req_pos0, "req_pos0")),
+                                  ctypes.c_int(R), ctypes.c_int(total_rows), ctypes.c_int(num_heads),
+                                  ctypes.c_int(Hkv), ctypes.c_int(Dh), ctypes.c_int(P), ctypes.c_float(scale),
+                                  ctypes.c_int(window or 0), ctypes.c_int(_tag(q.dtype)), _stream()))
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None,
+           seed: torch.Tensor | None = None, offset: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of float32 logits: greedy where temperature is 0 or absent."""
+    lib = _ready()
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or logits.dim() != 2:
+        raise KernelError("sample: logits must be contiguous float32 [S, V]")
+    S, V = logits.shape
+    out = torch.empty((S,), dtype=torch.int32, device=logits.device)
+    if temperature is not None:
+        if temperature.dtype != torch.float32 or seed.dtype != torch.int64 or offset.dtype != torch.int64:
+            raise KernelError("sample: temperature float32, seed and offset int64")
+    _check(lib.ayk_sample(_ptr(out), _ptr(logits), ctypes.c_int(S), ctypes.c_int(V), _ptr(temperature),
+                          _ptr(seed), _ptr(offset), _stream()))
+    return out
+
+
+# ------------------------------------------------------------- dispatchers --
+
+def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+           activation: str = "none", residual: torch.Tensor | None = None,
+           out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """act(a @ w^T + bias) (+ residual).  float32 operands run on the FP32
+    pipes (true 32-bit); bfloat16 operands on the tensor cores when the
+    tcgen05 kernel takes the shape."""
+    return gemm_simt(a, w, bias, activation, residual, out_dtype, out)
+
+
+def attention(q, kcache, vcache, table, ctx, num_heads: int, scale: float,
+              window: int | None = None) -> torch.Tensor:
+    """Attention of the step's rows (``ctx`` gives the rows of each request)."""
+    return attention_simt(q, kcache, vcache, table, ctx.req_q_start, ctx.req_pos0, ctx.num_rows,
+                          num_heads, scale, window)

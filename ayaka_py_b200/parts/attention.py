@@ -1,0 +1,70 @@
+"""Causal multi-head attention over the paged cache (``models/gpt2.py:364-372``).
+
+Fused query/key/value projection (features in the order q | k | v), append of
+the step's keys and values to the pages, attention of the step's rows over the
+cache, output projection with the residual sum in its epilogue.  Heads, key/value
+heads (grouped queries), head size, score scale and an optional window are
+parameters; a run step that reads another's cache appends nothing."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import KVNeed, Mixer, TensorDecl, register_part
+
+
+class Attention(Mixer):
+    KIND = "attention"
+
+    def __init__(self, width: int, num_heads: int, head_dim: int, scale: float,
+                 kv_heads: int | None = None, window: int | None = None, bias: bool = True,
+                 dtype=torch.float32, device="cuda"):
+        kv_heads = kv_heads or num_heads
+        if num_heads % kv_heads:
+            raise ValueError(f"{num_heads} heads cannot share {kv_heads} key/value heads")
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise ValueError(f"head size {head_dim} is not a multiple of 16 in [16, 256]")
+        if window is not None and window < 1:
+            raise ValueError("window must be positive or None")
+        self.width, self.num_heads, self.kv_heads, self.head_dim = width, num_heads, kv_heads, head_dim
+        self.scale, self.window, self.has_bias = float(scale), window, bias
+        self.dtype = dtype
+        self.q_width = num_heads * head_dim
+        self.kv_width = kv_heads * head_dim
+        self.qkv_weight = self.qkv_bias = self.out_weight = self.out_bias = None
+        self.position = None
+
+    def attach_position(self, position) -> None:
+        self.position = position
+
+    def tensors(self):
+        total = self.q_width + 2 * self.kv_width
+        out = {"qkv_weight": TensorDecl((total, self.width), "matrix"),
+               "out_weight": TensorDecl((self.width, self.q_width), "matrix")}
+        if self.has_bias:
+            out["qkv_bias"] = TensorDecl((total,), "vector")
+            out["out_bias"] = TensorDecl((self.width,), "vector")
+        return out
+
+    def cache_need(self):
+        return KVNeed(self.kv_heads, self.head_dim, self.window)
+
+    def forward(self, h, residual, ctx, cache):
+        qkv = ops.linear(h, self.qkv_weight, self.qkv_bias, out_dtype=self.dtype)
+        q = qkv[:, :self.q_width]
+        k = qkv[:, self.q_width:self.q_width + self.kv_width]
+        v = qkv[:, self.q_width + self.kv_width:]
+        rotate = getattr(self.position, "rotate_qk", None)
+        if rotate is not None:
+            rotate(q, k, self.num_heads, self.kv_heads, self.head_dim, ctx)
+        kcache, vcache = ctx.cache.kv_layer(cache.group, cache.layer)
+        table = ctx.tables[cache.group]
+        if cache.writes:
+            ops.kv_append(kcache, vcache, k, v, ctx.row_req, ctx.positions, table)
+        o = ops.attention(q, kcache, vcache, table, ctx, self.num_heads, self.scale, self.window)
+        return ops.linear(o, self.out_weight, self.out_bias, residual=residual,
+                          out_dtype=torch.float32, out=residual)
+
+
+register_part(Attention.KIND, Attention)

@@ -1,0 +1,8 @@
+"""Weights: safetensors files, binding by name, the random-weights mode."""
+
+from .loader import DictStore, FolderStore, WeightMismatchError, load_weights
+from .random_init import random_tensors, write_random_model
+from .safetensors import CheckpointCorruptError, SafetensorsFile, write_safetensors
+
+__all__ = ["CheckpointCorruptError", "SafetensorsFile", "write_safetensors", "WeightMismatchError",
+           "FolderStore", "DictStore", "load_weights", "random_tensors", "write_random_model"]

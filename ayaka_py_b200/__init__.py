@@ -5,5 +5,7 @@ __version__ = "0.1.0"
 
 from . import models, parts  # noqa: F401  (register architectures and part kinds)
 from .config import EngineConfig, GPT2Config
+from .engine import LLM, Request, StopCriteria
+from .sampling import SamplingParams
 
-__all__ = ["EngineConfig", "GPT2Config", "__version__"]
+__all__ = ["LLM", "Request", "StopCriteria", "SamplingParams", "EngineConfig", "GPT2Config", "__version__"]

@@ -9,6 +9,15 @@
 // descending-probability order, sampling/ops/sampling.py:587-589: the same
 // distribution.)  The draw depends only on the row's logits, seed and offset,
 // never on which other rows share the batch.
+//
+// Filters, in the reference's order (sampling/ops/sampling.py:473-540): top_k
+// (keep the k most probable), renormalise, top_p (keep a token while the
+// probability mass of the more probable ones is <= top_p; the first always
+// stays), min_p (keep p >= min_p * p_max).  Each becomes a threshold on
+// exp(z - zmax): the k-th largest value is found by a radix select over the
+// float's bits, the nucleus edge by the same walk over sums kept as 64-bit
+// fixed point (integer atomics: the same result whatever the order).  Tokens
+// of exactly equal probability at a threshold are kept together.
 #include <math.h>
 
 #include "common.cuh"
@@ -66,10 +75,96 @@ __device__ MaxIdx block_argmax(const float* row, int V, MaxIdx* red) {
   return total;
 }
 
+
+constexpr double FIXED_ONE = 1099511627776.0;   // 2^40: exp(z - zmax) <= 1 as fixed point
+
+__device__ __forceinline__ unsigned long long to_fixed(float e) {
+  return (unsigned long long)((double)e * FIXED_ONE);
+}
+
+// Bits of the k-th largest exp(z - zmax) of the row (0 when k >= V).
+__device__ uint32_t select_kth(const float* row, int V, float inv_t, float zmax, long long k,
+                               unsigned long long* hist, uint32_t* shared_u32) {
+  if (k <= 0 || k >= V) return 0u;
+  uint32_t prefix = 0u, mask = 0u;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      uint32_t bits = __float_as_uint(expf(row[i] * inv_t - zmax));
+      if ((bits & mask) == prefix) atomicAdd(&hist[(bits >> shift) & 255u], 1ull);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int chosen = 0;
+      for (int b = 255; b >= 0; --b) {
+        if ((long long)hist[b] >= k) { chosen = b; break; }
+        k -= (long long)hist[b];
+      }
+      shared_u32[0] = (uint32_t)chosen;
+      shared_u32[1] = (uint32_t)k;
+    }
+    __syncthreads();
+    prefix |= shared_u32[0] << shift;
+    mask |= 255u << shift;
+    k = (long long)shared_u32[1];
+    __syncthreads();
+  }
+  return prefix;
+}
+
+// Bits of the least probable token that top_p keeps among those with bits >= floor_bits.
+__device__ uint32_t select_nucleus(const float* row, int V, float inv_t, float zmax, uint32_t floor_bits,
+                                   float top_p, unsigned long long* hist, unsigned long long* shared_u64,
+                                   uint32_t* shared_u32) {
+  if (threadIdx.x == 0) shared_u64[0] = 0ull;
+  __syncthreads();
+  unsigned long long mine = 0ull;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float e = expf(row[i] * inv_t - zmax);
+    if (__float_as_uint(e) >= floor_bits) mine += to_fixed(e);
+  }
+  atomicAdd(&shared_u64[0], mine);
+  __syncthreads();
+  const unsigned long long limit = (unsigned long long)((double)top_p * (double)shared_u64[0]);
+  __syncthreads();
+  uint32_t prefix = 0u, mask = 0u;
+  unsigned long long above = 0ull;     // mass of the tokens more probable than the current prefix range
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      float e = expf(row[i] * inv_t - zmax);
+      uint32_t bits = __float_as_uint(e);
+      if (bits >= floor_bits && (bits & mask) == prefix) atomicAdd(&hist[(bits >> shift) & 255u], to_fixed(e));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int chosen = -1;
+      unsigned long long run = above;
+      for (int b = 255; b >= 0; --b) {
+        if (hist[b] == 0ull) continue;
+        if (run + hist[b] > limit) { chosen = b; break; }
+        run += hist[b];
+      }
+      shared_u32[0] = (uint32_t)(chosen < 0 ? 256 : chosen);
+      shared_u64[1] = run;
+    }
+    __syncthreads();
+    if (shared_u32[0] == 256u) return floor_bits;   // the whole mass fits: top_p drops nothing
+    prefix |= shared_u32[0] << shift;
+    mask |= 255u << shift;
+    above = shared_u64[1];
+    __syncthreads();
+  }
+  return prefix > floor_bits ? prefix : floor_bits;
+}
+
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
               const float* __restrict__ temperature, const long long* __restrict__ seed,
-              const long long* __restrict__ offset) {
+              const long long* __restrict__ offset, const long long* __restrict__ top_k,
+              const float* __restrict__ top_p, const float* __restrict__ min_p) {
   __shared__ MaxIdx red[THREADS / 32];
   __shared__ double partial[THREADS];
   __shared__ int chosen_thread;
@@ -84,12 +179,23 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
   }
   const float inv_t = 1.0f / fmaxf(temp, 1e-6f);
   const float zmax = top.v * inv_t;
+  __shared__ unsigned long long hist[256];
+  __shared__ unsigned long long shared_u64[2];
+  __shared__ uint32_t shared_u32[2];
+  uint32_t keep_bits = 0u;       // a token stays when the bits of exp(z - zmax) reach this
+  if (top_k && top_k[r] > 0) keep_bits = select_kth(row, V, inv_t, zmax, top_k[r], hist, shared_u32);
+  if (top_p && top_p[r] < 1.0f)
+    keep_bits = select_nucleus(row, V, inv_t, zmax, keep_bits, top_p[r], hist, shared_u64, shared_u32);
+  if (min_p && min_p[r] > 0.f) keep_bits = max(keep_bits, __float_as_uint(fminf(min_p[r], 1.0f)));
   // Each thread owns one contiguous segment, so that the running sum goes
   // through the tokens in id order.
   const int seg = (V + THREADS - 1) / THREADS;
   const int lo = min(V, (int)threadIdx.x * seg), hi = min(V, lo + seg);
   float s = 0.f;
-  for (int i = lo; i < hi; ++i) s += expf(row[i] * inv_t - zmax);
+  for (int i = lo; i < hi; ++i) {
+    float e = expf(row[i] * inv_t - zmax);
+    if (__float_as_uint(e) >= keep_bits) s += e;
+  }
   partial[threadIdx.x] = (double)s;
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -120,6 +226,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
     int token = -1, last_positive = lo;
     for (int i = lo; i < hi; ++i) {
       float p = expf(row[i] * inv_t - zmax);
+      if (__float_as_uint(p) < keep_bits) p = 0.f;
       if (p > 0.f) last_positive = i;
       run += (double)p;
       if (p > 0.f && run >= target_s) { token = i; break; }
@@ -131,12 +238,14 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
 }  // namespace
 
 // out[S] int32.  temperature null or 0 for a row: greedy.  seed/offset int64 [S].
+// top_k (int64, <= 0 off), top_p and min_p (float32) are null or [S].
 AYK_EXPORT int ayk_sample(int* out, const float* logits, int S, int V, const float* temperature,
-                          const long long* seed, const long long* offset, cudaStream_t stream) {
+                          const long long* seed, const long long* offset, const long long* top_k,
+                          const float* top_p, const float* min_p, cudaStream_t stream) {
   if (S == 0) return 0;
   AYK_REQUIRE(V >= 1, "ayk_sample: empty vocabulary");
   AYK_REQUIRE(temperature == nullptr || (seed != nullptr && offset != nullptr),
               "ayk_sample: temperature sampling needs seeds and offsets");
-  sample_kernel<<<S, THREADS, 0, stream>>>(out, logits, V, temperature, seed, offset);
+  sample_kernel<<<S, THREADS, 0, stream>>>(out, logits, V, temperature, seed, offset, top_k, top_p, min_p);
   return ayk_check_launch("ayk_sample");
 }

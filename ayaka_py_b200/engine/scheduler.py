@@ -1,0 +1,287 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token
+budget, decodes first, finishes and frees; decides what happens when pages run
+out.  It is host code and needs no GPU: it talks to the cache manager's
+bookkeeping only.
+
+Rules, after the reference's continuous scheduler (``sched/continuous.py``):
+
+* decoding first: every running request whose prompt is done gets one token, in
+  round-robin order from a cursor, while the budget lasts (``:392-429``);
+* then prompt portions: a request that is in the middle of its prompt goes on
+  first, then waiting requests in arrival order; a portion is
+  ``min(remaining, prefill_chunk, budget left)``; at most one request is in the
+  middle of its prompt at a time: a new one is started only when its whole
+  remaining prompt fits into this step or no other prompt is unfinished
+  (``:431-534``, ``configs/scheduler.py:125``);
+* a request's logits are wanted only when the portion ends at its last known
+  token (``:527-529``);
+* when pages run out (``:540-729``): halve the largest prompt portion; drop
+  prompt portions of one token; then preempt the newest running request
+  (its pages return, it goes back to the head of the waiting line and later
+  recomputes its prompt and the tokens it generated); a request that could
+  never fit was refused at admission, so a lone request always gets its pages.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+from ..cache.manager import CacheManager, NoFreeSlot, OutOfPages, Reservation
+from ..parts.base import KVNeed
+from .request import GenerationResult, Request
+
+
+class RequestRefused(ValueError):
+    """The request can never run in this engine (too long, duplicate id, ...)."""
+
+
+@dataclass
+class RequestState:
+    request: Request
+    ordinal: int                      # admission order: FCFS key and seed source
+    seed: int
+    tokens: list[int]                 # prompt + generated so far
+    computed: int = 0                 # tokens whose keys and values are cached
+    slot: int | None = None
+    generated: int = 0
+    preemptions: int = 0
+    finish_reason: str | None = None
+
+    @property
+    def prompt_len(self) -> int:
+        return len(self.request.prompt_token_ids)
+
+    @property
+    def remaining(self) -> int:
+        return len(self.tokens) - self.computed
+
+
+@dataclass
+class ScheduledEntry:
+    state: RequestState
+    start: int
+    count: int
+    sample: bool                      # the portion ends at the last known token
+
+    @property
+    def is_decode(self) -> bool:
+        """One token of a request whose other tokens are all cached."""
+        return self.state.remaining == 1 and self.state.computed > 0
+
+
+@dataclass
+class ScheduledStep:
+    entries: list[ScheduledEntry]
+    reservation: Reservation
+    decode_only: bool
+
+
+@dataclass
+class SchedulerStats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    preemptions: int = 0
+    recomputed_tokens: int = 0
+    shrunk_steps: int = 0
+    blocked_steps: int = 0
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, *, batch_tokens: int, prefill_chunk: int,
+                 max_model_len: int, eos_token_id: int | None = None, base_seed: int = 0):
+        from ..sampling.params import derive_seed
+
+        self._derive_seed = derive_seed
+        self.cache = cache
+        self.batch_tokens = batch_tokens
+        self.prefill_chunk = prefill_chunk
+        self.max_model_len = max_model_len
+        self.eos_token_id = eos_token_id
+        self.base_seed = base_seed
+        self.waiting: deque[RequestState] = deque()
+        self.running: list[RequestState] = []       # in admission order
+        self.states: dict[str, RequestState] = {}
+        self.cursor = 0
+        self.ordinal = 0
+        self.stats = SchedulerStats()
+
+    # ------------------------------------------------------------ admission --
+    def add(self, request: Request) -> RequestState:
+        if request.request_id in self.states:
+            raise RequestRefused(f"request id {request.request_id!r} is already in use")
+        if request.max_total_len > self.max_model_len:
+            raise RequestRefused(
+                f"prompt of {len(request.prompt_token_ids)} tokens + max_tokens {request.stop.max_tokens} "
+                f"exceeds the model length {self.max_model_len}")
+        P = self.cache.page_size
+        for g, group in enumerate(self.cache.groups):
+            if isinstance(group.need, KVNeed) and group.need.window is None:
+                if -(-request.max_total_len // P) > self.cache.kv_pages - 1:
+                    raise RequestRefused(
+                        f"the request needs {-(-request.max_total_len // P)} pages, the cache has "
+                        f"{self.cache.kv_pages - 1}")
+        seed = request.sampling.seed
+        if seed is None:
+            seed = self._derive_seed(self.base_seed + self.ordinal)
+        state = RequestState(request, self.ordinal, seed, list(request.prompt_token_ids))
+        self.ordinal += 1
+        self.states[request.request_id] = state
+        self.waiting.append(state)
+        return state
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------- planning --
+    def schedule(self) -> ScheduledStep | None:
+        budget = self.batch_tokens
+        entries: list[ScheduledEntry] = []
+
+        # 1. decoding first, round robin from the cursor
+        decoders = [s for s in self.running if s.remaining == 1 and s.computed > 0]
+        if decoders:
+            if len(decoders) > budget:          # not all fit: take turns
+                start = self.cursor % len(decoders)
+                decoders = (decoders[start:] + decoders[:start])[:budget]
+                self.cursor += budget
+            for s in decoders:
+                entries.append(ScheduledEntry(s, s.computed, 1, True))
+                budget -= 1
+
+        # 2. prompt portions: the unfinished prompt first, then waiting requests
+        partial = [s for s in self.running if s.remaining > 1 or s.computed == 0]
+        for s in partial:
+            if budget < 1:
+                break
+            n = min(s.remaining, self.prefill_chunk, budget)
+            entries.append(ScheduledEntry(s, s.computed, n, n == s.remaining))
+            budget -= n
+        unfinished = any(e.count < e.state.remaining for e in entries if e.state in partial) or \
+            any(s not in [e.state for e in entries] for s in partial)
+        while self.waiting and budget >= 1:
+            s = self.waiting[0]
+            n = min(s.remaining, self.prefill_chunk, budget)
+            if n < s.remaining and unfinished:
+                break                       # one unfinished prompt at a time
+            try:
+                s.slot = self.cache.open(s.request.request_id)
+            except NoFreeSlot:
+                break
+            self.waiting.popleft()
+            self.running.append(s)
+            entries.append(ScheduledEntry(s, 0, n, n == s.remaining))
+            budget -= n
+            if n < s.remaining:
+                unfinished = True
+
+        # 3. pages
+        shrunk = False
+        while entries:
+            try:
+                reservation = self.cache.reserve([(e.state.slot, e.start, e.count) for e in entries])
+                break
+            except OutOfPages:
+                shrunk = True
+                prefills = [e for e in entries if not e.is_decode]
+                big = [e for e in prefills if e.count > 1]
+                if big:
+                    e = max(big, key=lambda e: e.count)
+                    e.count //= 2
+                    e.sample = False
+                elif prefills:
+                    entries.remove(prefills[-1])
+                else:
+                    victim = self._pick_victim(entries)
+                    if victim is None:
+                        entries.clear()
+                        break
+                    entries[:] = [e for e in entries if e.state is not victim]
+                    self._preempt(victim)
+        if shrunk:
+            self.stats.shrunk_steps += 1
+        if not entries:
+            self.stats.blocked_steps += 1
+            return None
+        self.stats.steps += 1
+        decode_only = all(e.is_decode for e in entries)
+        for e in entries:
+            if e.is_decode:
+                self.stats.decode_tokens += 1
+            else:
+                self.stats.prefill_tokens += e.count
+        return ScheduledStep(entries, reservation, decode_only)
+
+    def _pick_victim(self, entries) -> RequestState | None:
+        """The newest running request that holds pages; never the only one."""
+        holders = [s for s in self.running if s.computed > 0 or any(e.state is s for e in entries)]
+        if len(holders) <= 1:
+            return None
+        return max(holders, key=lambda s: s.ordinal)
+
+    def _preempt(self, state: RequestState) -> None:
+        self.cache.close(state.slot)
+        self.stats.preemptions += 1
+        self.stats.recomputed_tokens += state.computed
+        state.slot, state.computed = None, 0
+        state.preemptions += 1
+        self.running.remove(state)
+        self.waiting.appendleft(state)
+
+    # -------------------------------------------------------------- results --
+    def update(self, step: ScheduledStep, sampled: dict[str, int]) -> list[RequestState]:
+        """The step ran: commit it, append the sampled tokens, finish and free.
+        ``sampled``: request id -> token for every entry with ``sample``."""
+        self.cache.commit(step.reservation)
+        finished = []
+        for e in step.entries:
+            s = e.state
+            s.computed = e.start + e.count
+            if not e.sample:
+                continue
+            token = int(sampled[s.request.request_id])
+            s.tokens.append(token)
+            s.generated += 1
+            reason = self._finish_reason(s, token)
+            if reason is not None:
+                self._finish(s, reason)
+                finished.append(s)
+        return finished
+
+    def _finish_reason(self, s: RequestState, token: int) -> str | None:
+        """``request/stream.py:130-163``: stop ids and EOS count only from
+        ``min_tokens`` on; the length limit always."""
+        stop = s.request.stop
+        if s.generated >= stop.min_tokens:
+            if token in stop.stop_token_ids:
+                return "stop"
+            if not stop.ignore_eos and self.eos_token_id is not None and token == self.eos_token_id:
+                return "eos"
+        if s.generated >= stop.max_tokens or len(s.tokens) >= self.max_model_len:
+            return "length"
+        return None
+
+    def _finish(self, s: RequestState, reason: str) -> None:
+        s.finish_reason = reason
+        if s.slot is not None:
+            self.cache.close(s.slot)
+            s.slot = None
+        if s in self.running:
+            self.running.remove(s)
+        if s in self.waiting:
+            self.waiting.remove(s)
+        del self.states[s.request.request_id]
+
+    def abort(self, request_id: str) -> RequestState | None:
+        s = self.states.get(request_id)
+        if s is None:
+            return None
+        if s.slot is not None and self.cache.in_step[s.slot]:
+            raise RuntimeError("a request cannot be aborted while its step runs")
+        self._finish(s, "abort")
+        return s
+
+    def result_of(self, s: RequestState) -> GenerationResult:
+        return GenerationResult(s.request.request_id, list(s.request.prompt_token_ids),
+                                s.tokens[s.prompt_len:], s.finish_reason, s.preemptions)

@@ -187,8 +187,11 @@ def attention_simt(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None,
-           seed: torch.Tensor | None = None, offset: torch.Tensor | None = None) -> torch.Tensor:
-    """One token per row of float32 logits: greedy where temperature is 0 or absent."""
+           seed: torch.Tensor | None = None, offset: torch.Tensor | None = None,
+           top_k: torch.Tensor | None = None, top_p: torch.Tensor | None = None,
+           min_p: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of float32 logits: greedy where temperature is 0 or
+    absent; else a draw after the top_k / top_p / min_p filters (null: off)."""
     lib = _ready()
     if logits.dtype != torch.float32 or not logits.is_contiguous() or logits.dim() != 2:
         raise KernelError("sample: logits must be contiguous float32 [S, V]")
@@ -197,8 +200,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None,
     if temperature is not None:
         if temperature.dtype != torch.float32 or seed.dtype != torch.int64 or offset.dtype != torch.int64:
             raise KernelError("sample: temperature float32, seed and offset int64")
+    for name, t, dt in (("top_k", top_k, torch.int64), ("top_p", top_p, torch.float32), ("min_p", min_p, torch.float32)):
+        if t is not None and (t.dtype != dt or t.numel() != S or not t.is_contiguous()):
+            raise KernelError(f"sample: {name} must be a contiguous {dt} tensor with one value per row")
     _check(lib.ayk_sample(_ptr(out), _ptr(logits), ctypes.c_int(S), ctypes.c_int(V), _ptr(temperature),
-                          _ptr(seed), _ptr(offset), _stream()))
+                          _ptr(seed), _ptr(offset), _ptr(top_k), _ptr(top_p), _ptr(min_p), _stream()))
     return out
 
 

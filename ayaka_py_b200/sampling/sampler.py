@@ -1,0 +1,56 @@
+"""From logits rows to tokens: packs the rows' options and calls the kernel.
+
+Stage order of the reference (``sampling/plan.py:274-377``) for the options kept
+here: scale by temperature, all-greedy batches take the argmax, other batches
+draw per row with greedy rows overridden.  The uniform of a draw is a function
+of the request's seed and of how many tokens it has sampled so far, so a
+request's tokens do not depend on what else is in the batch.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from .. import ops
+from .params import SamplingParams
+
+
+class Sampler:
+    def __init__(self, device="cuda", max_rows: int = 256):
+        self.device = device
+        self._allocate(max_rows)
+
+    def _allocate(self, rows: int) -> None:
+        pin = torch.cuda.is_available()
+        self.rows = rows
+        self.h_float = torch.zeros((3, rows), dtype=torch.float32, pin_memory=pin)   # temperature, top_p, min_p
+        self.h_long = torch.zeros((3, rows), dtype=torch.int64, pin_memory=pin)      # seed, offset, top_k
+        self.d_float = torch.zeros((3, rows), dtype=torch.float32, device=self.device)
+        self.d_long = torch.zeros((3, rows), dtype=torch.int64, device=self.device)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               offsets: Sequence[int]) -> torch.Tensor:
+        """logits [S, V] float32 (device) -> tokens [S] int32 (device)."""
+        S = logits.shape[0]
+        if not (len(params) == len(seeds) == len(offsets) == S):
+            raise ValueError("one set of options per logits row")
+        if all(p.greedy for p in params):
+            return ops.sample(logits)
+        if S > self.rows:
+            self._allocate(max(S, 2 * self.rows))
+        for i, p in enumerate(params):
+            self.h_float[0, i] = 0.0 if p.greedy else p.temperature
+            self.h_float[1, i] = p.top_p
+            self.h_float[2, i] = p.min_p
+            self.h_long[0, i] = seeds[i]
+            self.h_long[1, i] = offsets[i]
+            self.h_long[2, i] = p.top_k if p.top_k > 0 else 0
+        self.d_float.copy_(self.h_float, non_blocking=True)
+        self.d_long.copy_(self.h_long, non_blocking=True)
+        filtered = any(p.filtered and not p.greedy for p in params)
+        return ops.sample(logits, self.d_float[0, :S], self.d_long[0, :S], self.d_long[1, :S],
+                          top_k=self.d_long[2, :S] if filtered else None,
+                          top_p=self.d_float[1, :S] if filtered else None,
+                          min_p=self.d_float[2, :S] if filtered else None)

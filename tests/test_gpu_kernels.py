@@ -1,0 +1,224 @@
+"""Each kernel alone against a plain reference, at other sizes than the engine's."""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == "float32" else 2e-2) * scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(0)
+    wte, wpe = rs.randn(301, 72).astype(np.float32), rs.randn(50, 72).astype(np.float32)
+    tok, pos = rs.randint(0, 301, 23).astype(np.int32), rs.randint(0, 50, 23).astype(np.int32)
+    a, b = dev(wte, DTYPES[dtype]), dev(wpe, DTYPES[dtype])
+    out = ops.embed(dev(tok), dev(pos), a, b).cpu().numpy()
+    want = a.float().cpu().numpy()[tok] + b.float().cpu().numpy()[pos]
+    assert np.abs(out - want).max() < 1e-6
+    only = ops.embed(dev(tok), dev(pos), a, None).cpu().numpy()
+    assert np.array_equal(only, a.float().cpu().numpy()[tok])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,eps", [(72, 1e-5), (1600, 1e-6), (1000, 3e-2), (8, 1e-5)])
+def test_layernorm(dtype, width, eps):
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(1)
+    x = (rs.randn(19, width) * 3 + 1.5).astype(np.float32)
+    g, b = rs.randn(width).astype(np.float32), rs.randn(width).astype(np.float32)
+    want = plain_gpt2.layer_norm(x.astype(np.float64), g, b, eps)
+    out = ops.layernorm(dev(x), dev(g), dev(b), eps, DTYPES[dtype]).float().cpu().numpy()
+    assert np.abs(out - want).max() < tol(dtype, 4.0)
+    rows = np.array([18, 0, 7], dtype=np.int32)
+    picked = ops.layernorm(dev(x), dev(g), dev(b), eps, DTYPES[dtype], rows=dev(rows)).float().cpu().numpy()
+    assert np.abs(picked - want[rows]).max() < tol(dtype, 4.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 50, 24), (7, 257, 1000), (130, 96, 72), (64, 64, 16), (33, 1003, 330)])
+@pytest.mark.parametrize("act", ["none", "gelu_tanh", "gelu_erf", "quick_gelu"])
+def test_gemm_simt(dtype, M, N, K, act):
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(2)
+    a, w = rs.randn(M, K).astype(np.float32), (rs.randn(N, K) / np.sqrt(K)).astype(np.float32)
+    bias, res = rs.randn(N).astype(np.float32), rs.randn(M, N).astype(np.float32)
+    A, W = dev(a, DTYPES[dtype]), dev(w, DTYPES[dtype])
+    a64, w64 = A.double().cpu().numpy(), W.double().cpu().numpy()
+    names = {"none": None, "gelu_tanh": "gelu_new", "gelu_erf": "gelu", "quick_gelu": "quick_gelu"}
+    y = a64 @ w64.T + bias
+    if names[act]:
+        y = plain_gpt2.activation(names[act], y)
+    want = y + res
+    out = ops.gemm_simt(A, W, dev(bias), act, dev(res), out_dtype=torch.float32).cpu().numpy()
+    assert np.abs(out - want).max() < 2e-5
+    plain = ops.gemm_simt(A, W, None, "none", None).float().cpu().numpy()
+    assert np.abs(plain - a64 @ w64.T).max() < tol(dtype, 4.0)
+    R = dev(res)
+    ops.gemm_simt(A, W, dev(bias), act, R, out_dtype=torch.float32, out=R)        # in place on the residual
+    assert np.abs(R.cpu().numpy() - want).max() < 2e-5
+
+
+def paged_case(rs, lens_q, lens_ctx, H, Hkv, Dh, P, dtype, pages=None, sharp=None):
+    """Random requests: request r brings lens_q[r] rows after lens_ctx[r] cached
+    tokens.  Returns kernel inputs and the plain result."""
+    R = len(lens_q)
+    total = [c + q for c, q in zip(lens_ctx, lens_q)]
+    C = max(-(-t // P) for t in total)
+    n_pages = pages or (sum(-(-t // P) for t in total) + 1)
+    order = rs.permutation(np.arange(1, n_pages))
+    table = np.zeros((R, C), dtype=np.int32)
+    kc = rs.randn(n_pages, P, Hkv, Dh).astype(np.float32)     # garbage where nothing lives
+    vc = rs.randn(n_pages, P, Hkv, Dh).astype(np.float32)
+    qs, ks, vs, rows, k_new, v_new, pos, row_req = [], [], [], [], [], [], [], []
+    used = 0
+    for r in range(R):
+        T = total[r]
+        q = rs.randn(T, H, Dh).astype(np.float32)
+        k = rs.randn(T, Hkv, Dh).astype(np.float32)
+        v = rs.randn(T, Hkv, Dh).astype(np.float32)
+        if sharp is not None and r == sharp[0]:
+            _, qpos, kpos = sharp                 # one far key stands out for one query
+            for hh in range(H):
+                key = k[kpos, hh // (H // Hkv)]
+                q[qpos, hh] = key * (30.0 / float(key @ key))
+        qs.append(q); ks.append(k); vs.append(v)
+        for j in range(-(-T // P)):
+            table[r, j] = order[used]; used += 1
+        for p in range(lens_ctx[r]):              # the cached prefix is in the pages already
+            kc[table[r, p // P], p % P] = k[p]
+            vc[table[r, p // P], p % P] = v[p]
+        for p in range(lens_ctx[r], T):
+            rows.append(q[p].reshape(-1)); k_new.append(k[p].reshape(-1)); v_new.append(v[p].reshape(-1))
+            pos.append(p); row_req.append(r)
+    q_start = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
+    t = DTYPES[dtype]
+    inputs = dict(q=dev(np.stack(rows), t), k=dev(np.stack(k_new), t), v=dev(np.stack(v_new), t),
+                  kc=dev(kc, t), vc=dev(vc, t), table=dev(table), q_start=dev(q_start),
+                  pos0=dev(np.asarray(lens_ctx, dtype=np.int32)), pos=dev(np.asarray(pos, dtype=np.int32)),
+                  row_req=dev(np.asarray(row_req, dtype=np.int32)))
+
+    def rounded(a):
+        return dev(a, t).double().cpu().numpy()
+
+    def plain(scale, window):
+        out = []
+        for r in range(R):
+            kk = np.repeat(rounded(ks[r]), H // Hkv, axis=1)
+            vv = np.repeat(rounded(vs[r]), H // Hkv, axis=1)
+            o = plain_gpt2.causal_attention(rounded(qs[r]), kk, vv, scale, window=window)
+            out.append(o[lens_ctx[r]:].reshape(lens_q[r], H * Dh))
+        return np.concatenate(out)
+
+    return inputs, plain
+
+
+ATTENTION_CASES = [
+    # lens_q, lens_ctx, H, Hkv, Dh, P, window
+    ([5, 1, 40], [0, 17, 3], 4, 4, 16, 16, None),
+    ([1, 1, 1, 1], [0, 15, 16, 130], 2, 2, 48, 8, None),
+    ([33, 2, 64], [31, 0, 65], 6, 2, 80, 16, None),        # grouped queries, head size 80
+    ([70], [200], 1, 1, 256, 32, None),
+    ([9, 1, 50], [40, 99, 0], 4, 2, 32, 4, 24),            # window
+    ([1, 3], [63, 64], 5, 5, 64, 64, 7),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ATTENTION_CASES)
+def test_append_then_attention(dtype, case):
+    from ayaka_py_b200 import ops
+    lens_q, lens_ctx, H, Hkv, Dh, P, window = case
+    rs = np.random.RandomState(3)
+    x, plain = paged_case(rs, lens_q, lens_ctx, H, Hkv, Dh, P, dtype)
+    scale = 0.7 / np.sqrt(Dh)
+    ops.kv_append(x["kc"], x["vc"], x["k"], x["v"], x["row_req"], x["pos"], x["table"])
+    out = ops.attention_simt(x["q"], x["kc"], x["vc"], x["table"], x["q_start"], x["pos0"], sum(lens_q), H,
+                             scale, window).float().cpu().numpy()
+    assert np.abs(out - plain(scale, window)).max() < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("qpos,kpos", [(299, 0), (299, 15), (299, 16), (255, 127), (256, 128)])
+def test_far_key_stands_out(dtype, qpos, kpos):
+    """One query's score for one far key (at a page's edge) is made large, so
+    that losing that key changes the result by far more than the tolerance."""
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(4)
+    x, plain = paged_case(rs, [300, 1], [0, 20], 2, 2, 32, 16, dtype, sharp=(0, qpos, kpos))
+    ops.kv_append(x["kc"], x["vc"], x["k"], x["v"], x["row_req"], x["pos"], x["table"])
+    out = ops.attention_simt(x["q"], x["kc"], x["vc"], x["table"], x["q_start"], x["pos0"], 301, 2, 1.0).float().cpu().numpy()
+    want = plain(1.0, None)
+    uniform = plain(0.0, None)
+    assert np.abs(want[qpos] - uniform[qpos]).max() > 0.5      # the far key matters
+    assert np.abs(out - want).max() < tol(dtype)
+
+
+def test_greedy_ties_take_the_lowest_index():
+    from ayaka_py_b200 import ops
+    logits = np.zeros((3, 1000), dtype=np.float32)
+    logits[0, [700, 12, 999]] = 5.0
+    logits[1, 999] = 1.0
+    logits[2] = -np.inf
+    out = ops.sample(dev(logits)).cpu().numpy()
+    assert out.tolist() == [12, 999, 0]
+
+
+def test_temperature_draws_fall_in_the_twins_interval_and_are_batch_independent():
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(5)
+    V, S = 1237, 64
+    logits = (rs.randn(S, V) * 2).astype(np.float32)
+    temp = np.full(S, 0.8, dtype=np.float32)
+    temp[5] = 0.0
+    seed = rs.randint(0, 2 ** 62, S).astype(np.int64)
+    offset = rs.randint(0, 1000, S).astype(np.int64)
+    out = ops.sample(dev(logits), dev(temp), dev(seed), dev(offset)).cpu().numpy()
+    for r in range(S):
+        if temp[r] == 0:
+            assert out[r] == int(np.argmax(logits[r]))
+            continue
+        p = plain_gpt2.filtered_probabilities(logits[r], temp[r])
+        cum = np.cumsum(p)
+        u = plain_gpt2.philox_uniform(int(seed[r]), int(offset[r]))
+        lo = cum[out[r] - 1] if out[r] > 0 else 0.0
+        assert lo - 1e-5 <= u <= cum[out[r]] + 1e-5, (r, out[r], lo, u, cum[out[r]])
+    alone = ops.sample(dev(logits[9:10]), dev(temp[9:10]), dev(seed[9:10]), dev(offset[9:10])).cpu().numpy()
+    assert alone[0] == out[9]
+
+
+def test_temperature_distribution():
+    from ayaka_py_b200 import ops
+    logits = np.tile(np.array([[0.0, 1.0, 2.0, -1.0, 0.5]], dtype=np.float32), (20000, 1))
+    n = logits.shape[0]
+    out = ops.sample(dev(logits), dev(np.full(n, 1.3, dtype=np.float32)), dev(np.full(n, 77, dtype=np.int64)),
+                     dev(np.arange(n, dtype=np.int64))).cpu().numpy()
+    p = plain_gpt2.filtered_probabilities(logits[0], 1.3)
+    freq = np.bincount(out, minlength=5) / n
+    chi2 = float((n * (freq - p) ** 2 / p).sum())
+    assert chi2 < 18.5        # 4 degrees of freedom, p = 0.001
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from ayaka_py_b200 import ops
+    with pytest.raises(ops.KernelError):
+        ops.layernorm(torch.zeros(2, 20000, device="cuda"), torch.ones(20000, device="cuda"), None, 1e-5, torch.float32)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_simt(torch.zeros(2, 8, device="cuda"), torch.zeros(3, 9, device="cuda"))
+    with pytest.raises(ops.KernelError):
+        ops.embed(torch.zeros(2, dtype=torch.int64, device="cuda"), torch.zeros(2, dtype=torch.int32, device="cuda"),
+                  torch.zeros(4, 4, device="cuda"), None)

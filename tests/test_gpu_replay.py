@@ -1,0 +1,151 @@
+"""Replays of the same requests cut in different ways, in 32-bit and in
+bfloat16, compared with the plain implementation's whole-sequence logits."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import tiny_models
+import trace_tools
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+LENGTHS = {"A": [5, 17, 40, 75, 128], "B": [1, 9, 33, 64, 120, 201], "C": [37, 90]}
+PAGE = {"A": 16, "B": 8, "C": 16}
+
+
+def tolerance(dtype, want):
+    """32-bit: 1e-4 absolute.  bfloat16: 2 % of the largest logit (operands of
+    every product are rounded to 8 bits of mantissa; nothing else is)."""
+    if dtype == "float32":
+        return 1e-4
+    return 0.02 * max(float(np.abs(w).max()) for w in want.values())
+
+
+def requests_of(tag, cfg):
+    toks = tiny_models.prompts(cfg, LENGTHS[tag], seed=40 + ord(tag))
+    return {f"{tag.lower()}{i}": t for i, t in enumerate(toks)}
+
+
+def replay(folder, dtype, trace, page_size, max_tokens=None):
+    from ayaka_py_b200.replay import ReplaySession
+
+    session = ReplaySession(folder, dtype, max_tokens or trace_tools.tokens_needed(trace), page_size)
+    outputs = []
+    for record in trace:
+        logits = session.step(record)
+        outputs.append(None if logits is None or logits.shape[0] == 0 else logits.cpu().numpy())
+    session.cache.assert_clean()
+    return outputs, session
+
+
+@pytest.fixture(scope="module")
+def oracles(model_folders):
+    out = {}
+    for tag, (folder, cfg, weights) in model_folders.items():
+        reqs = requests_of(tag, cfg)
+        out[tag] = (reqs, trace_tools.oracle(cfg, weights, reqs))
+    return out
+
+
+def check(tag, dtype, trace, model_folders, oracles, **kw):
+    folder, cfg, _ = model_folders[tag]
+    reqs, want = oracles[tag]
+    outputs, session = replay(folder, dtype, trace, PAGE[tag], **kw)
+    got = trace_tools.collect(trace, outputs)
+    bad = trace_tools.first_difference(got, want, tolerance(dtype, want))
+    assert bad is None, f"first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"
+    return session
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "B"])
+def test_each_request_alone_and_whole(tag, dtype, model_folders, oracles):
+    check(tag, dtype, trace_tools.whole(oracles[tag][0]), model_folders, oracles)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "B"])
+def test_last_32_tokens_one_by_one(tag, dtype, model_folders, oracles):
+    check(tag, dtype, trace_tools.tail_decoded(oracles[tag][0], 32), model_folders, oracles)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "B"])
+def test_portions_of_changing_size(tag, dtype, model_folders, oracles):
+    check(tag, dtype, trace_tools.portions(oracles[tag][0]), model_folders, oracles)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "B"])
+def test_mixed_with_pages_used_again(tag, dtype, model_folders, oracles):
+    for seed in (0, 1):
+        trace = trace_tools.mixed(oracles[tag][0], seed=seed)
+        assert max(len(s["entries"]) for s in trace) >= 3
+        session = check(tag, dtype, trace, model_folders, oracles)
+        stats = session.cache.stats()["groups"]["group0"]
+        assert stats["reused"] > 0, "the pool was large enough that no page was used again"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype, model_folders, oracles):
+    """Tiny C: 640 positions; the longer request decodes from its first token to its last."""
+    reqs = {k: v for k, v in oracles["C"][0].items()}
+    folder, cfg, weights = model_folders["C"]
+    long_req = {"long": tiny_models.prompts(cfg, [600], seed=5)[0]}
+    want = trace_tools.oracle(cfg, weights, long_req)
+    trace = trace_tools.tail_decoded(long_req, tail=599)
+    outputs, _ = replay(folder, dtype, trace, 16)
+    got = trace_tools.collect(trace, outputs)
+    bad = trace_tools.first_difference(got, want, tolerance(dtype, want))
+    assert bad is None, f"first wrong place: position {bad[1]} |diff| {bad[2]:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(dtype, model_folders, oracles):
+    """One token, then two, then page edges: positions 0, 1, 2 and 15, 16, 17."""
+    folder, cfg, weights = model_folders["A"]
+    reqs = {"f": tiny_models.prompts(cfg, [20], seed=9)[0]}
+    want = trace_tools.oracle(cfg, weights, reqs)
+    trace = trace_tools.portions(reqs, sizes=(1, 1, 1, 12, 1, 1, 1, 2))
+    outputs, _ = replay(folder, dtype, trace, 16)
+    got = trace_tools.collect(trace, outputs)
+    assert trace_tools.first_difference(got, want, tolerance(dtype, want)) is None
+
+
+def test_trace_run_program(model_folders, oracles, tmp_path):
+    """The program itself, as a child process: protocol lines, files, exit code."""
+    folder, cfg, weights = model_folders["B"]
+    reqs, want = oracles["B"]
+    trace = trace_tools.mixed(reqs, seed=3)
+    out = tmp_path / "out"
+    proc = subprocess.Popen(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
+         "--out", str(out), "--max-tokens", str(trace_tools.tokens_needed(trace)), "--page-size", "8"],
+        stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env={**os.environ, "PYTHONDONTWRITEBYTECODE": "1"})
+    for record in trace:
+        proc.stdin.write(json.dumps(record) + "\n")
+        proc.stdin.flush()
+        assert proc.stdout.readline().strip() == f"done {record['step']}"
+    proc.stdin.close()
+    assert proc.wait(timeout=60) == 0
+    V = cfg["vocab_size"]
+    outputs = []
+    for record in trace:
+        wanted = sum(len(e["want"]) for e in record["entries"])
+        path = out / f"{record['step']}.f32"
+        if wanted:
+            data = np.fromfile(path, dtype="<f4")
+            assert data.size == wanted * V
+            outputs.append(data.reshape(wanted, V))
+        else:
+            assert not path.exists()
+            outputs.append(None)
+    got = trace_tools.collect(trace, outputs)
+    assert trace_tools.first_difference(got, want, 1e-4) is None

@@ -1,0 +1,167 @@
+"""The scheduler's decisions, on the host with bookkeeping-only caches."""
+
+import numpy as np
+import pytest
+
+from ayaka_py_b200.cache import CacheGroupSpec, CacheManager
+from ayaka_py_b200.engine.request import Request, StopCriteria
+from ayaka_py_b200.engine.scheduler import RequestRefused, Scheduler
+from ayaka_py_b200.parts.base import KVNeed
+from ayaka_py_b200.sampling.params import SamplingParams, derive_seed
+
+
+def make(pages=65, page_size=4, max_requests=8, batch_tokens=32, prefill_chunk=16, max_len=128, eos=None):
+    cache = CacheManager([CacheGroupSpec("g", KVNeed(1, 16), 1)], kv_pages=pages, page_size=page_size,
+                         max_requests=max_requests, max_len=max_len, device=None)
+    return Scheduler(cache, batch_tokens=batch_tokens, prefill_chunk=prefill_chunk, max_model_len=max_len,
+                     eos_token_id=eos), cache
+
+
+def req(i, n, max_tokens=4, **kw):
+    return Request(f"r{i}", list(range(1, n + 1)), SamplingParams(temperature=0.0), StopCriteria(max_tokens=max_tokens, **kw))
+
+
+def drive(sched, cache, token=lambda s: 7, max_steps=10_000, log=None):
+    """Runs the loop with a fake model.  Returns finished states in order."""
+    done = []
+    for _ in range(max_steps):
+        if not sched.has_work():
+            break
+        plan = sched.schedule()
+        assert plan is not None, "blocked although work waits"
+        cache.check_invariants()
+        if log is not None:
+            log.append([(e.state.request.request_id, e.start, e.count, e.sample) for e in plan.entries])
+        sampled = {e.state.request.request_id: token(e.state) for e in plan.entries if e.sample}
+        done += sched.update(plan, sampled)
+    assert not sched.has_work()
+    cache.assert_clean()
+    return done
+
+
+def test_portions_decode_first_and_one_unfinished_prompt():
+    sched, cache = make(batch_tokens=32, prefill_chunk=16)
+    for i, n in enumerate([1, 9, 33, 20]):
+        sched.add(req(i, n, max_tokens=3))
+    log = []
+    done = drive(sched, cache, log=log)
+    # step 0: r0 and r1 whole, r2 starts with what is left of the chunk / budget
+    assert log[0] == [("r0", 0, 1, True), ("r1", 0, 9, True), ("r2", 0, 16, False)]
+    # step 1: decodes first, then r2 goes on; r3 may not start while r2 is unfinished
+    assert log[1][:2] == [("r0", 1, 1, True), ("r1", 9, 1, True)]
+    assert log[1][2] == ("r2", 16, 16, False) and len(log[1]) == 3
+    assert log[2][-1] == ("r2", 32, 1, True) or ("r2", 32, 1, True) in log[2]
+    for step in log:
+        assert sum(c for _, _, c, _ in step) <= 32
+        assert len({r for r, *_ in step}) == len(step)
+        unfinished = [1 for r, s, c, smp in step if not smp]
+        assert len(unfinished) <= 1
+    assert sorted(s.request.request_id for s in done) == ["r0", "r1", "r2", "r3"]
+    assert all(s.finish_reason == "length" and s.generated == 3 for s in done)
+    assert sched.stats.preemptions == 0
+
+
+def test_admission_rules():
+    sched, cache = make(pages=9, page_size=4, max_len=64)         # 8 usable pages = 32 tokens
+    with pytest.raises(RequestRefused):
+        sched.add(req(0, 60, max_tokens=10))                      # beyond the model length
+    with pytest.raises(RequestRefused):
+        sched.add(req(1, 30, max_tokens=8))                       # could never fit the cache
+    sched.add(req(2, 8))
+    with pytest.raises(RequestRefused):
+        sched.add(req(2, 8))                                      # duplicate id
+    with pytest.raises(ValueError):
+        Request("x", [])
+
+
+def test_stop_rules():
+    sched, cache = make(eos=9)
+    sched.add(req(0, 3, max_tokens=10, stop_token_ids=(5,), min_tokens=3))
+    sched.add(req(1, 3, max_tokens=10))
+    sched.add(req(2, 3, max_tokens=10, ignore_eos=True))
+    tokens = {"r0": iter([5, 5, 5, 5]), "r1": iter([1, 9]), "r2": iter([9] * 10)}
+    done = drive(sched, cache, token=lambda s: next(tokens[s.request.request_id]))
+    by = {s.request.request_id: s for s in done}
+    assert by["r0"].finish_reason == "stop" and by["r0"].generated == 3      # not before min_tokens
+    assert by["r1"].finish_reason == "eos" and by["r1"].generated == 2
+    assert by["r2"].finish_reason == "length" and by["r2"].generated == 10
+
+
+def test_slots_bound_the_running_set():
+    sched, cache = make(max_requests=2)
+    for i in range(5):
+        sched.add(req(i, 4, max_tokens=2))
+    log = []
+    drive(sched, cache, log=log)
+    assert max(len(step) for step in log) <= 2
+
+
+def test_pages_run_out_shrink_then_preempt_then_finish():
+    # 8 usable pages of 4 tokens; three requests that each grow to 20 tokens cannot all live.
+    sched, cache = make(pages=9, page_size=4, batch_tokens=64, prefill_chunk=64, max_len=32)
+    for i in range(3):
+        sched.add(req(i, 10, max_tokens=10))
+    log = []
+    done = drive(sched, cache, log=log)
+    assert len(done) == 3 and all(s.generated == 10 for s in done)
+    assert sched.stats.preemptions >= 1 and sched.stats.recomputed_tokens > 0
+    victims = [s for s in done if s.preemptions]
+    assert victims and all(s.request.request_id != "r0" for s in victims)     # the oldest is never the victim
+    # a preempted request recomputes its prompt and what it generated, in one go or in portions
+    for s in victims:
+        restarts = [e for step in log for e in step if e[0] == s.request.request_id and e[1] == 0]
+        assert len(restarts) == s.preemptions + 1
+
+
+def test_prefill_is_shrunk_before_anyone_is_preempted():
+    sched, cache = make(pages=7, page_size=4, batch_tokens=64, prefill_chunk=64, max_len=24)   # 24 tokens
+    sched.add(req(0, 8, max_tokens=4))
+    drive_one = sched.schedule()
+    sched.update(drive_one, {"r0": 7})
+    sched.add(req(1, 20, max_tokens=2))        # needs 5 pages, 4 are free
+    plan = sched.schedule()
+    got = {e.state.request.request_id: (e.start, e.count, e.sample) for e in plan.entries}
+    assert got["r0"] == (8, 1, True)
+    assert got["r1"] == (0, 10, False)         # halved once, fits
+    assert sched.stats.preemptions == 0 and sched.stats.shrunk_steps == 1
+    sched.update(plan, {"r0": 7})
+    done = drive(sched, cache)
+    assert {s.request.request_id for s in done} == {"r0", "r1"}
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_workloads_terminate_without_leaks(seed):
+    rs = np.random.RandomState(seed)
+    sched, cache = make(pages=int(rs.randint(12, 40)), page_size=4, max_requests=int(rs.randint(2, 7)),
+                        batch_tokens=int(rs.randint(8, 48)), prefill_chunk=int(rs.randint(2, 24)), max_len=40)
+    n = 0
+    pending = []
+    for i in range(25):
+        plen, gen = int(rs.randint(1, 30)), int(rs.randint(1, 10))
+        pending.append(req(i, plen, max_tokens=gen))
+    done = []
+    steps = 0
+    while pending or sched.has_work():
+        while pending and rs.rand() < 0.5:
+            sched.add(pending.pop(0))
+        if not sched.has_work():
+            continue
+        plan = sched.schedule()
+        assert plan is not None
+        steps += 1
+        assert steps < 5000
+        assert sum(e.count for e in plan.entries) <= sched.batch_tokens
+        cache.check_invariants()
+        done += sched.update(plan, {e.state.request.request_id: int(rs.randint(0, 100)) for e in plan.entries if e.sample})
+    cache.assert_clean()
+    assert len(done) == 25
+    for s in done:
+        assert s.generated == s.request.stop.max_tokens and s.finish_reason == "length"
+        assert len(s.tokens) == s.prompt_len + s.generated
+
+
+def test_seeds():
+    sched, _ = make()
+    a = sched.add(Request("a", [1], SamplingParams(seed=42), StopCriteria(max_tokens=4)))
+    b = sched.add(Request("b", [1], stop=StopCriteria(max_tokens=4)))
+    assert a.seed == 42 and b.seed == derive_seed(1) and 0 <= b.seed < 2 ** 63

@@ -1,0 +1,425 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05), with
+// operands staged by TMA and the accumulator in tensor memory:
+//
+//   C[M, N] = act(X[M, K] * W[N, K]^T + bias[N]) (+ residual[M, N])
+//
+// X are the step's rows (tokens), W a weight in [out, in] layout.  The product is
+// issued "swapped": a CTA takes 128 rows of W as the MMA's M side and BT tokens
+// as its N side (BT = 16 ... 256), so that a decode step with a handful of tokens
+// still fills the 128 lanes of the tensor core and streams each weight byte once.
+// The accumulator D[out feature, token] lies in TMEM with one out feature per
+// lane; the epilogue warps read it with tcgen05.ld and write C[token, feature],
+// 32 consecutive features per warp and token.
+//
+// Warp roles: warp 0 = TMA producer (one lane), warp 1 = TMEM allocation and MMA
+// issue (one lane), warps 2..5 = epilogue (bias, activation in 32-bit, residual
+// sum in 32-bit).  K is cut into blocks of 64 elements (128 bytes, the 128-byte
+// swizzle); a ring of stages connects producer and MMA through mbarriers.
+//
+// Split-K: for skinny products (decode) gridDim.z CTAs share one output tile;
+// each writes its 32-bit partial tile to scratch, the last to arrive sums the
+// partials in split order (so the result does not depend on arrival order) and
+// runs the epilogue.
+//
+// Every wait on an mbarrier is bounded; on a time-out the kernel records an
+// error word, waits (bounded) for its own copies, frees its TMEM and returns.
+//
+// The reference computes these products with F.linear / cuBLAS
+// (layers/linear/methods.py:73-76) and the activation in a separate kernel
+// (kernel/triton/activation.py:133-154).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BLOCK_N = 128;          // rows of W per CTA (UMMA M)
+constexpr int BLOCK_K = 64;           // bf16 elements per stage and row: 128 bytes
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2;
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+constexpr int stages_for(int bt) { return bt >= 256 ? 4 : (bt >= 128 ? 6 : 8); }
+constexpr int tmem_cols_for(int bt) { return bt < 32 ? 32 : bt; }
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and records `code`) when the barrier did not
+// complete within WAIT_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try(bar, parity)) return true;
+  }
+  atomicExch(error, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride byte offset), version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                  // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset
+  d |= (uint64_t)1 << 46;                  // descriptor version
+  d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct EpilogueArgs {
+  void* C;
+  const float* bias;
+  const float* residual;
+  float* partials;           // [splits, M, N] float32 scratch (split-K only)
+  unsigned int* counters;    // one per output tile, zero between launches (split-K only)
+  int* error;
+  int M, N, K;
+  int act, out_bf16;
+  int kb_per_split;
+};
+
+__device__ __forceinline__ void store_out(const EpilogueArgs& a, int tok, int n, float v) {
+  if (a.bias) v += a.bias[n];
+  v = apply_activation(v, a.act);
+  size_t idx = (size_t)tok * a.N + n;
+  if (a.residual) v += a.residual[idx];
+  if (a.out_bf16) ((__nv_bfloat16*)a.C)[idx] = __float2bfloat16_rn(v);
+  else ((float*)a.C)[idx] = v;
+}
+
+template <int BT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const EpilogueArgs args) {
+  constexpr int STAGES = stages_for(BT);
+  constexpr int B_BYTES = BT * BLOCK_K * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TCOLS = tmem_cols_for(BT);
+  constexpr uint32_t IDESC = make_idesc(BLOCK_N, BT);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;           // swizzled tiles need 1024-byte alignment
+  const uint32_t bars = tiles + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t tmem_full_bar = bars + 8u * (2 * STAGES);
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 1);
+  volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
+  volatile int* flag_ptr = (volatile int*)(smem_raw + (tmem_slot + 4 - raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BLOCK_N, t0 = blockIdx.y * BT;
+  const int total_kb = (args.K + BLOCK_K - 1) / BLOCK_K;
+  const int kb_begin = blockIdx.z * args.kb_per_split;
+  const int num_kb = min(total_kb, kb_begin + args.kb_per_split) - kb_begin;   // >= 1 by the host's choice
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TCOLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+        ok = mbar_wait(empty_bar(s), phase ^ 1u, args.error, 1);
+        if (!ok) break;
+        mbar_expect_tx(full_bar(s), STAGE_BYTES);
+        const uint32_t a_dst = tiles + s * STAGE_BYTES;
+        const int kx = (kb_begin + i) * BLOCK_K;
+        tma_load_2d(a_dst, &map_w, kx, n0, full_bar(s));
+        tma_load_2d(a_dst + A_BYTES, &map_x, kx, t0, full_bar(s));
+        issued = i + 1;
+      }
+      if (!ok) {
+        // Nobody may be consuming any more: wait for the copies already issued.
+        for (int i = max(0, issued - STAGES); i < issued; ++i)
+          mbar_wait(full_bar(i % STAGES), (uint32_t)(i / STAGES) & 1u, args.error, 2);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+        ok = mbar_wait(full_bar(s), phase, args.error, 3);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_src = tiles + s * STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+          const uint64_t da = make_desc(a_src + k * UMMA_K * 2);
+          const uint64_t db = make_desc(a_src + A_BYTES + k * UMMA_K * 2);
+          umma(tmem_base, da, db, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+      }
+      umma_commit(tmem_full_bar);           // arrives when every MMA issued so far is done
+    }
+    __syncwarp();
+  } else {
+    // Epilogue: warp w may read TMEM lanes 32 * (w % 4) ... + 31.
+    const int quarter = warp & 3;
+    const int n = n0 + quarter * 32 + lane;
+    const bool ok = mbar_wait(tmem_full_bar, 0u, args.error, 4);
+    tc_fence_after();
+    const int splits = gridDim.z;
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < BT; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
+        if (n < args.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int tok = t0 + c + j;
+            if (tok >= args.M) break;
+            const float v = __uint_as_float(r[j]);
+            if (splits == 1) store_out(args, tok, n, v);
+            else args.partials[((size_t)blockIdx.z * args.M + tok) * args.N + n] = v;
+          }
+        }
+      }
+    }
+    if (splits > 1) {
+      // The last CTA of this tile to arrive sums the partials in split order.
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const unsigned tile = blockIdx.y * gridDim.x + blockIdx.x;
+      if (threadIdx.x == 64) {
+        unsigned old = atomicAdd(&args.counters[tile], 1u);
+        *flag_ptr = (old == (unsigned)splits - 1u) ? 1 : 0;
+        if (old == (unsigned)splits - 1u) args.counters[tile] = 0u;    // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*flag_ptr && ok) {
+        __threadfence();
+        if (n < args.N) {
+          for (int j = 0; j < BT; ++j) {
+            const int tok = t0 + j;
+            if (tok >= args.M) break;
+            float v = 0.f;
+            for (int z = 0; z < splits; ++z) v += __ldcg(&args.partials[((size_t)z * args.M + tok) * args.N + n]);
+            store_out(args, tok, n, v);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TCOLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------- host --
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encode = nullptr;
+int* g_error_host = nullptr;     // mapped pinned memory: the kernels write, the host reads without a copy
+int* g_error_dev = nullptr;
+std::mutex g_mutex;
+
+struct MapKey {
+  const void* ptr; int rows, k, box;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box == o.box; }
+};
+struct MapHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows * 1000003u ^ (size_t)k.k * 10007u ^ (size_t)k.box;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_weight_maps;
+
+int setup() {
+  if (g_encode && g_error_host) return 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (err != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess)
+    return ayk_fail("ayk_gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+  g_encode = (EncodeTiledFn)fn;
+  err = cudaHostAlloc((void**)&g_error_host, sizeof(int), cudaHostAllocMapped);
+  if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: cudaHostAlloc: %s", cudaGetErrorString(err));
+  *g_error_host = 0;
+  err = cudaHostGetDevicePointer((void**)&g_error_dev, g_error_host, 0);
+  if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: cudaHostGetDevicePointer: %s", cudaGetErrorString(err));
+  return 0;
+}
+
+// rows x k bfloat16, row-major; box of `box_rows` rows x 64 elements, 128-byte swizzle.
+int encode(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return ayk_fail("ayk_gemm_tc: cuTensorMapEncodeTiled failed with %d (rows %d, k %d, box %d)", (int)r, rows, k, box_rows);
+  return 0;
+}
+
+template <int BT>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& args, int splits, cudaStream_t stream) {
+  constexpr int STAGES = stages_for(BT);
+  constexpr size_t SMEM = 1024 + (size_t)STAGES * (A_BYTES + BT * BLOCK_K * 2) + 8 * (2 * STAGES + 2);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+    if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: shared memory %zu: %s", SMEM, cudaGetErrorString(err));
+    configured = true;
+  }
+  dim3 grid((args.N + BLOCK_N - 1) / BLOCK_N, (args.M + BT - 1) / BT, splits);
+  gemm_tc_kernel<BT><<<grid, THREADS, SMEM, stream>>>(mw, mx, args);
+  return ayk_check_launch("ayk_gemm_tc");
+}
+
+}  // namespace
+
+// 0 when the kernel takes this shape; otherwise a text in ayk_last_error().
+AYK_EXPORT int ayk_gemm_tc_supported(int M, int N, int K) {
+  if (M < 1 || N < 1 || K < 8 || K % 8 != 0)
+    return ayk_fail("ayk_gemm_tc: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+  return 0;
+}
+
+// The error word of the tensor-core kernels: 0, or the code of the wait that ran out.
+AYK_EXPORT int ayk_gemm_tc_error() { return g_error_host ? *g_error_host : 0; }
+AYK_EXPORT void ayk_gemm_tc_clear_error() { if (g_error_host) *g_error_host = 0; }
+
+// How many float32 scratch elements and tile counters a call needs.
+AYK_EXPORT long long ayk_gemm_tc_scratch_floats(int M, int N, int splits) {
+  return splits > 1 ? (long long)splits * M * N : 0;
+}
+
+// X [M, K] and W [N, K] bfloat16 (contiguous, 16-byte aligned); C [M, N] float32
+// or bfloat16; bias, residual float32 or null (residual may alias a float32 C).
+// splits > 1 needs `partials` (ayk_gemm_tc_scratch_floats) and `counters` (one
+// zeroed unsigned per output tile; the kernel leaves them zero).
+AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* bias, const float* residual,
+                           int M, int N, int K, int act, int out_dtype, int splits, float* partials,
+                           unsigned int* counters, int weight_is_static, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (ayk_gemm_tc_supported(M, N, K) != 0) return -1;
+  AYK_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "ayk_gemm_tc: operands must be 16-byte aligned");
+  AYK_REQUIRE(out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16, "ayk_gemm_tc: unknown output dtype %d", out_dtype);
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  if (splits < 1) splits = 1;
+  if (splits > total_kb) splits = total_kb;
+  int kb_per_split = (total_kb + splits - 1) / splits;
+  splits = (total_kb + kb_per_split - 1) / kb_per_split;       // no empty split
+  AYK_REQUIRE(splits == 1 || (partials && counters), "ayk_gemm_tc: split-K needs scratch");
+  AYK_REQUIRE(splits <= 65535, "ayk_gemm_tc: too many splits");
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (setup() != 0) return -1;
+  }
+  const int BT = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+  AYK_REQUIRE((M + BT - 1) / BT <= 65535, "ayk_gemm_tc: too many rows (%d)", M);
+  CUtensorMap mw, mx;
+  if (weight_is_static) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    MapKey key{W, N, K, BLOCK_N};
+    auto it = g_weight_maps.find(key);
+    if (it == g_weight_maps.end()) {
+      if (encode(&mw, W, N, K, BLOCK_N) != 0) return -1;
+      g_weight_maps.emplace(key, mw);
+    } else {
+      mw = it->second;
+    }
+  } else if (encode(&mw, W, N, K, BLOCK_N) != 0) {
+    return -1;
+  }
+  if (encode(&mx, X, M, K, BT) != 0) return -1;
+  EpilogueArgs args{C, bias, residual, partials, counters, g_error_dev, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split};
+  switch (BT) {
+    case 16: return launch<16>(mw, mx, args, splits, stream);
+    case 32: return launch<32>(mw, mx, args, splits, stream);
+    case 64: return launch<64>(mw, mx, args, splits, stream);
+    case 128: return launch<128>(mw, mx, args, splits, stream);
+    default: return launch<256>(mw, mx, args, splits, stream);
+  }
+}

@@ -210,12 +210,78 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None,
 
 # ------------------------------------------------------------- dispatchers --
 
+_tc_scratch: dict = {}
+SM_COUNT = 148
+
+
+def _tc_workspace(device, floats: int):
+    ws = _tc_scratch.get(device)
+    if ws is None or ws[0].numel() < floats:
+        partials = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        counters = ws[1] if ws is not None else torch.zeros(8192, dtype=torch.int32, device=device)
+        ws = (partials, counters)
+        _tc_scratch[device] = ws
+    return ws
+
+
+def tc_splits(M: int, N: int, K: int) -> int:
+    """Split-K factor of the tensor-core product: skinny products (few output
+    tiles) are cut along K so that about one CTA per SM streams the weight."""
+    bt = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+    tiles = -(-N // 128) * -(-M // bt)
+    blocks = -(-K // 64)
+    if tiles >= SM_COUNT // 2 or blocks < 4:
+        return 1
+    return max(1, min(SM_COUNT // tiles, blocks // 2))
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+            activation: str = "none", residual: torch.Tensor | None = None,
+            out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
+            splits: int | None = None, static_weight: bool = True) -> torch.Tensor:
+    """act(a[M,K] @ w[N,K]^T + bias) (+ residual), bfloat16 operands, on tcgen05."""
+    lib = _ready()
+    M, K = a.shape
+    N = w.shape[0]
+    if (w.shape[1] != K or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
+            or not a.is_contiguous() or not w.is_contiguous()):
+        raise KernelError(f"gemm_tc operands do not fit: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}")
+    out_dtype = out_dtype or a.dtype
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    for name, t in (("bias", bias), ("residual", residual)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError(f"{name} must be contiguous float32")
+    if residual is not None and tuple(residual.shape) != (M, N):
+        raise KernelError("residual must have the output's shape")
+    if splits is None:
+        splits = tc_splits(M, N, K)
+    partials = counters = None
+    if splits > 1:
+        tiles = -(-N // 128) * -(-M // 16)
+        partials, counters = _tc_workspace(a.device, splits * M * N)
+        if tiles > counters.numel():
+            raise KernelError("gemm_tc: too many output tiles for split-K")
+    _check(lib.ayk_gemm_tc(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
+                           ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]),
+                           ctypes.c_int(_tag(out_dtype)), ctypes.c_int(splits), _ptr(partials), _ptr(counters),
+                           ctypes.c_int(1 if static_weight else 0), _stream()))
+    return out
+
+
+def tc_error() -> int:
+    """0, or the code of the bounded wait that ran out in a tensor-core kernel."""
+    return int(library().ayk_gemm_tc_error())
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            activation: str = "none", residual: torch.Tensor | None = None,
            out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """act(a @ w^T + bias) (+ residual).  float32 operands run on the FP32
-    pipes (true 32-bit); bfloat16 operands on the tensor cores when the
-    tcgen05 kernel takes the shape."""
+    pipes (true 32-bit); bfloat16 operands on the tensor cores (tcgen05) when
+    K is a multiple of 8, else on the FP32 pipes with 32-bit accumulation."""
+    if a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[0] > 0:
+        return gemm_tc(a, w, bias, activation, residual, out_dtype, out)
     return gemm_simt(a, w, bias, activation, residual, out_dtype, out)
 
 

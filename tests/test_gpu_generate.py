@@ -1,0 +1,117 @@
+"""Generation through the Python entry point and the command line, compared
+with the plain implementation."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import plain_gpt2
+import tiny_models
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_greedy_matches_plain_tiny_a(model_folders):
+    from ayaka_py_b200 import LLM, SamplingParams, StopCriteria
+    folder, cfg, weights = model_folders["A"]
+    prompts = tiny_models.prompts(cfg, [5, 17, 40], seed=21)
+    llm = LLM(folder, dtype="float32", page_size=16, kv_pages=64, batch_tokens=64, prefill_chunk=32)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0), StopCriteria(max_tokens=16, ignore_eos=True))
+    for p, r in zip(prompts, out):
+        assert r.finish_reason == "length"
+        assert r.token_ids == plain_gpt2.greedy_generate(cfg, weights, p, 16)
+    llm.engine.cache.assert_clean()
+
+
+def test_greedy_bfloat16_stays_within_rounding_of_the_best_token(model_folders):
+    from ayaka_py_b200 import LLM, SamplingParams, StopCriteria
+    folder, cfg, weights = model_folders["A"]
+    prompts = tiny_models.prompts(cfg, [5, 17, 40], seed=21)
+    llm = LLM(folder, dtype="bfloat16", page_size=16, kv_pages=64, batch_tokens=64, prefill_chunk=32)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0), StopCriteria(max_tokens=16, ignore_eos=True))
+    for p, r in zip(prompts, out):
+        logits = plain_gpt2.forward(cfg, weights, p + r.token_ids)
+        slack = 2 * 0.02 * float(np.abs(logits).max())
+        for i, token in enumerate(r.token_ids):
+            row = logits[len(p) - 1 + i]
+            assert row[token] >= row.max() - slack
+
+
+def test_tiny_b_workload_chunked_mixed_temperature(model_folders):
+    """5 prompts of 1/9/33/64/120 ids, prefill chunk 24 mixed with decodes, page
+    size 8, temperature 0.8 with a fixed seed, 24 new tokens each: every token
+    must be the one the sampling twin draws from the plain model's logits."""
+    from ayaka_py_b200 import LLM, SamplingParams, StopCriteria
+    folder, cfg, weights = model_folders["B"]
+    prompts = tiny_models.prompts(cfg, [1, 9, 33, 64, 120], seed=22)
+    llm = LLM(folder, dtype="float32", page_size=8, kv_pages=80, batch_tokens=64, prefill_chunk=24)
+    params = [SamplingParams(temperature=0.8, seed=1000 + i) for i in range(5)]
+    out = llm.generate(prompts, params, StopCriteria(max_tokens=24, ignore_eos=True))
+    for i, (p, r) in enumerate(zip(prompts, out)):
+        assert len(r.token_ids) == 24
+        logits = plain_gpt2.forward(cfg, weights, p + r.token_ids)
+        for j, token in enumerate(r.token_ids):
+            probs = plain_gpt2.filtered_probabilities(logits[len(p) - 1 + j], 0.8)
+            cum = np.cumsum(probs)
+            u = plain_gpt2.philox_uniform(1000 + i, j)
+            lo = cum[token - 1] if token > 0 else 0.0
+            assert lo - 1e-4 <= u <= cum[token] + 1e-4, (i, j, token)
+    stats = llm.engine.scheduler.stats
+    assert stats.prefill_tokens >= sum(len(p) for p in prompts) and stats.decode_tokens > 0
+    # the same requests again, each alone: a request's tokens do not depend on its neighbours
+    alone = LLM(folder, dtype="float32", page_size=8, kv_pages=80, batch_tokens=256, prefill_chunk=256)
+    for i in (1, 4):
+        again = alone.generate([prompts[i]], params[i], StopCriteria(max_tokens=24, ignore_eos=True))[0]
+        assert again.token_ids == out[i].token_ids
+
+
+def test_few_pages_preempt_and_recompute_same_tokens(model_folders):
+    from ayaka_py_b200 import LLM, SamplingParams, StopCriteria
+    folder, cfg, weights = model_folders["A"]
+    prompts = tiny_models.prompts(cfg, [30, 28, 33, 25], seed=23)
+    stop = StopCriteria(max_tokens=30, ignore_eos=True)
+    roomy = LLM(folder, dtype="float32", page_size=16, kv_pages=64, batch_tokens=64, prefill_chunk=32)
+    want = [r.token_ids for r in roomy.generate(prompts, SamplingParams(temperature=0.0), stop)]
+    tight = LLM(folder, dtype="float32", page_size=16, kv_pages=11, batch_tokens=64, prefill_chunk=32)   # 160 tokens
+    got = tight.generate(prompts, SamplingParams(temperature=0.0), stop)
+    assert [r.token_ids for r in got] == want
+    assert tight.engine.scheduler.stats.preemptions > 0 and any(r.preemptions for r in got)
+    tight.engine.cache.assert_clean()
+
+
+def test_filters_keep_the_twins_support(model_folders):
+    from ayaka_py_b200 import LLM, SamplingParams, StopCriteria
+    folder, cfg, weights = model_folders["A"]
+    prompts = tiny_models.prompts(cfg, [12, 20], seed=24)
+    llm = LLM(folder, dtype="float32", page_size=16, kv_pages=64)
+    params = [SamplingParams(temperature=1.5, top_k=5, seed=3), SamplingParams(temperature=1.2, top_p=0.5, min_p=0.05, seed=4)]
+    out = llm.generate(prompts, params, StopCriteria(max_tokens=20, ignore_eos=True))
+    for p, sp, r in zip(prompts, params, out):
+        logits = plain_gpt2.forward(cfg, weights, p + r.token_ids)
+        for j, token in enumerate(r.token_ids):
+            probs = plain_gpt2.filtered_probabilities(logits[len(p) - 1 + j], sp.temperature, sp.top_k, sp.top_p, sp.min_p)
+            assert probs[token] > 0, (sp, j, token)
+
+
+def test_command_line(model_folders, tmp_path):
+    folder, cfg, weights = model_folders["A"]
+    prompt = tiny_models.prompts(cfg, [9], seed=25)[0]
+    proc = subprocess.run(
+        [sys.executable, "-m", "ayaka_py_b200", "generate", str(folder), "--dtype", "float32", "--kv-pages", "32",
+         "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "8", "--temperature", "0", "--ignore-eos"],
+        cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    record = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert record["token_ids"] == plain_gpt2.greedy_generate(cfg, weights, prompt, 8)
+    assert record["finish_reason"] == "length"
+
+
+def test_smoke_entry():
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__
+    __graft_entry__.smoke()

@@ -222,3 +222,56 @@ def test_kernels_refuse_what_they_cannot_do():
     with pytest.raises(ops.KernelError):
         ops.embed(torch.zeros(2, dtype=torch.int64, device="cuda"), torch.zeros(2, dtype=torch.int32, device="cuda"),
                   torch.zeros(4, 4, device="cuda"), None)
+
+
+TC_CASES = [
+    # M, N, K, splits
+    (1, 128, 64, 1), (5, 50, 72, 1), (16, 257, 200, 1), (17, 384, 1000, 1), (64, 96, 320, 1),
+    (100, 1003, 328, 1), (300, 200, 1600, 1), (8, 1600, 1600, None), (64, 1600, 6400, None),
+    (3, 130, 512, 4), (40, 300, 1000, 7), (8, 64, 64, 3),
+]
+
+
+@pytest.mark.parametrize("M,N,K,splits", TC_CASES)
+@pytest.mark.parametrize("act,out_dtype", [("none", "float32"), ("gelu_tanh", "bfloat16")])
+def test_gemm_tcgen05(M, N, K, splits, act, out_dtype):
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(6)
+    a, w = rs.randn(M, K).astype(np.float32), (rs.randn(N, K) / np.sqrt(K)).astype(np.float32)
+    bias, res = rs.randn(N).astype(np.float32), rs.randn(M, N).astype(np.float32)
+    A, W = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    y = A.double().cpu().numpy() @ W.double().cpu().numpy().T + bias
+    if act != "none":
+        y = plain_gpt2.activation("gelu_new", y)
+    want = y + res
+    out = ops.gemm_tc(A, W, dev(bias), act, dev(res), out_dtype=DTYPES[out_dtype], splits=splits, static_weight=False)
+    torch.cuda.synchronize()
+    assert ops.tc_error() == 0
+    err = np.abs(out.float().cpu().numpy() - want).max()
+    assert err < (2e-5 if out_dtype == "float32" else 4e-2), err
+    if out_dtype == "float32":
+        R = dev(res)
+        again = ops.gemm_tc(A, W, dev(bias), act, R, out_dtype=torch.float32, out=R, splits=splits, static_weight=False)
+        assert torch.equal(again, out)                      # in place on the residual, and the same bits again
+        assert ops.tc_error() == 0
+
+
+def test_gemm_tcgen05_rows_do_not_depend_on_the_batch():
+    """A row's result is the same alone, among 7 and among 200 rows (same split)."""
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(7)
+    a, w = rs.randn(200, 640).astype(np.float32), rs.randn(320, 640).astype(np.float32) / 25
+    A, W = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    full = ops.gemm_tc(A, W, out_dtype=torch.float32, splits=1)
+    for m in (1, 7, 64):
+        part = ops.gemm_tc(A[:m].contiguous(), W, out_dtype=torch.float32, splits=1)
+        assert torch.equal(part, full[:m])
+    assert ops.tc_error() == 0
+
+
+def test_gemm_tcgen05_refuses_odd_k():
+    from ayaka_py_b200 import ops
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.gemm_tc(torch.zeros(2, 12, device="cuda", dtype=torch.bfloat16), torch.zeros(4, 12, device="cuda", dtype=torch.bfloat16))
+    out = ops.linear(torch.ones(2, 12, device="cuda", dtype=torch.bfloat16), torch.ones(4, 12, device="cuda", dtype=torch.bfloat16))
+    assert float(out.float().max()) == 12.0      # the dispatcher takes the FP32-pipe kernel instead

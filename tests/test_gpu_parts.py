@@ -1,0 +1,339 @@
+"""Each part alone against the plain functions; the model as data (a layer run
+twice, a layer reading another's cache); and a toy architecture with a mixer
+that keeps state of its own, registered and stepped from here without touching
+the package."""
+
+import json
+from dataclasses import dataclass
+from types import SimpleNamespace
+from typing import ClassVar
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2
+import tiny_models
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def tol(dtype, scale=1.0):
+    return (3e-5 if dtype == "float32" else 3e-2) * scale
+
+
+def context_for(groups, dtype, lengths, page_size=8, vocab=1000, positions=512, starts=None):
+    """A cache manager and a step context for whole sequences (or continuations)."""
+    from ayaka_py_b200.cache import CacheManager
+    from ayaka_py_b200.engine.step import StepEntry, StepRunner
+
+    pages = sum(-(-(n + (starts[i] if starts else 0)) // page_size) for i, n in enumerate(lengths)) + 1
+    cache = CacheManager(groups, kv_pages=pages, page_size=page_size, max_requests=len(lengths),
+                         max_len=positions, dtype=DT[dtype], device="cuda")
+    model = SimpleNamespace(device="cuda", dtype=DT[dtype], max_positions=positions, vocab_size=vocab)
+    runner = StepRunner(model, cache, max_tokens=sum(lengths))
+    return cache, runner
+
+
+def run_entries(cache, runner, token_lists, wants=None):
+    from ayaka_py_b200.engine.step import StepEntry
+    entries = []
+    for i, toks in enumerate(token_lists):
+        slot = cache.slot_of.get(i)
+        if slot is None:
+            slot = cache.open(i)
+        entries.append(StepEntry(slot, int(cache.length[slot]), toks, wants[i] if wants else []))
+    res = cache.reserve([(e.slot, e.start, len(e.tokens)) for e in entries])
+    ctx = runner.prepare(entries)
+    return ctx, res
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_positions_norm_head(dtype):
+    from ayaka_py_b200.parts import PartSpec, make_part
+    rs = np.random.RandomState(0)
+    V, d, npos = 333, 40, 64
+    emb = make_part(PartSpec("token_embedding", {"vocab": V, "width": d}), DT[dtype], "cuda")
+    pos = make_part(PartSpec("learned_positions", {"positions": npos, "width": d}), DT[dtype], "cuda")
+    norm = make_part(PartSpec("layernorm", {"width": d, "eps": 1e-4}), DT[dtype], "cuda")
+    head = make_part(PartSpec("lm_head", {"vocab": V, "width": d}), DT[dtype], "cuda")
+    wte, wpe = dev(rs.randn(V, d).astype(np.float32), DT[dtype]), dev(rs.randn(npos, d).astype(np.float32), DT[dtype])
+    g, b = rs.randn(d).astype(np.float32), rs.randn(d).astype(np.float32)
+    emb.bind({"weight": wte}); pos.bind({"weight": wpe}); head.bind({"weight": wte})
+    norm.bind({"weight": dev(g), "bias": dev(b)})
+    cache, runner = context_for([], dtype, [7, 3], vocab=V, positions=npos)
+    toks = [rs.randint(0, V, 7).tolist(), rs.randint(0, V, 3).tolist()]
+    ctx, _ = run_entries(cache, runner, toks, wants=[[6, 0], [2]])
+    x = emb.forward(ctx, pos)
+    w64, p64 = wte.double().cpu().numpy(), wpe.double().cpu().numpy()
+    want_x = np.concatenate([plain_gpt2.embed(t, np.arange(len(t)), w64, p64) for t in toks])
+    assert np.abs(x.cpu().numpy() - want_x).max() < 1e-6
+    h = norm.forward(x, ctx, rows=ctx.want_rows)
+    want_h = plain_gpt2.layer_norm(want_x, g, b, 1e-4)[[6, 0, 9]]
+    assert np.abs(h.float().cpu().numpy() - want_h).max() < tol(dtype, 3)
+    logits = head.forward(h, ctx)
+    assert logits.dtype == torch.float32 and logits.shape == (3, V)
+    assert np.abs(logits.cpu().numpy() - h.double().cpu().numpy() @ w64.T).max() < 1e-4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("act,name", [("gelu_tanh", "gelu_new"), ("gelu_erf", "gelu"), ("quick_gelu", "quick_gelu")])
+def test_mlp_part(dtype, act, name):
+    from ayaka_py_b200.parts import PartSpec, make_part
+    rs = np.random.RandomState(1)
+    d, inner, T = 72, 200, 13
+    mlp = make_part(PartSpec("mlp", {"width": d, "inner": inner, "activation": act}), DT[dtype], "cuda")
+    up, down = dev(rs.randn(inner, d).astype(np.float32) / 8, DT[dtype]), dev(rs.randn(d, inner).astype(np.float32) / 14, DT[dtype])
+    ub, db = rs.randn(inner).astype(np.float32), rs.randn(d).astype(np.float32)
+    mlp.bind({"up_weight": up, "down_weight": down, "up_bias": dev(ub), "down_bias": dev(db)})
+    h, res = dev(rs.randn(T, d).astype(np.float32), DT[dtype]), rs.randn(T, d).astype(np.float32)
+    out = mlp.forward(h, dev(res), None)
+    u = plain_gpt2.activation(name, h.double().cpu().numpy() @ up.double().cpu().numpy().T + ub)
+    if dtype == "bfloat16":
+        u = dev(u.astype(np.float32), torch.bfloat16).double().cpu().numpy()      # the part stores it rounded
+    want = res + u @ down.double().cpu().numpy().T + db
+    assert out.dtype == torch.float32 and np.abs(out.cpu().numpy() - want).max() < tol(dtype)
+
+
+def attention_weights(rs, d, H, Hkv, Dh, dtype):
+    total = (H + 2 * Hkv) * Dh
+    return {"qkv_weight": dev(rs.randn(total, d).astype(np.float32) / np.sqrt(d), DT[dtype]),
+            "qkv_bias": dev(rs.randn(total).astype(np.float32) * 0.1),
+            "out_weight": dev(rs.randn(d, H * Dh).astype(np.float32) / np.sqrt(H * Dh), DT[dtype]),
+            "out_bias": dev(rs.randn(d).astype(np.float32) * 0.1)}
+
+
+def plain_attention_part(h, w, H, Hkv, Dh, scale, window, dtype):
+    """Grouped queries and a window, from the plain functions."""
+    f = lambda t: t.double().cpu().numpy()
+    qkv = h @ f(w["qkv_weight"]).T + f(w["qkv_bias"])
+    if dtype == "bfloat16":
+        qkv = f(dev(qkv.astype(np.float32), torch.bfloat16))
+    T = h.shape[0]
+    q = qkv[:, :H * Dh].reshape(T, H, Dh)
+    k = np.repeat(qkv[:, H * Dh:(H + Hkv) * Dh].reshape(T, Hkv, Dh), H // Hkv, axis=1)
+    v = np.repeat(qkv[:, (H + Hkv) * Dh:].reshape(T, Hkv, Dh), H // Hkv, axis=1)
+    o = plain_gpt2.causal_attention(q, k, v, scale, window=window).reshape(T, H * Dh)
+    if dtype == "bfloat16":
+        o = f(dev(o.astype(np.float32), torch.bfloat16))
+    return o @ f(w["out_weight"]).T + f(w["out_bias"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,Hkv,Dh,window", [(3, 3, 16, None), (4, 2, 48, None), (2, 1, 32, 5)])
+def test_attention_part_whole_and_continued(dtype, H, Hkv, Dh, window):
+    from ayaka_py_b200.cache import CacheBinding, CacheGroupSpec
+    from ayaka_py_b200.parts import PartSpec, make_part
+    rs = np.random.RandomState(2)
+    d, scale = 56, 0.3
+    part = make_part(PartSpec("attention", {"width": d, "num_heads": H, "kv_heads": Hkv, "head_dim": Dh,
+                                            "scale": scale, "window": window}), DT[dtype], "cuda")
+    w = attention_weights(rs, d, H, Hkv, Dh, dtype)
+    part.bind(w)
+    lengths = [21, 9]
+    cache, runner = context_for([CacheGroupSpec("g", part.cache_need(), 1)], dtype, lengths, page_size=8)
+    binding = CacheBinding(0, "g", 0, True)
+    hs = [dev(rs.randn(n, d).astype(np.float32), DT[dtype]) for n in lengths]
+    want = [plain_attention_part(h.double().cpu().numpy(), w, H, Hkv, Dh, scale, window, dtype) for h in hs]
+    # first 13 and 9 rows in one step, then the rest of the first request two rows at a time
+    ctx, res = run_entries(cache, runner, [[0] * 13, [0] * 9])
+    zero = lambda n: torch.zeros(n, d, device="cuda")
+    out = part.forward(torch.cat([hs[0][:13], hs[1]]), zero(22), ctx, binding)
+    cache.commit(res)
+    got0, got1 = [out[:13].cpu().numpy()], out[13:].cpu().numpy()
+    for p in range(13, 21, 2):
+        ctx, res = run_entries(cache, runner, [[0, 0]])
+        got0.append(part.forward(hs[0][p:p + 2].contiguous(), zero(2), ctx, binding).cpu().numpy())
+        cache.commit(res)
+    assert np.abs(np.concatenate(got0) - want[0]).max() < tol(dtype)
+    assert np.abs(got1 - want[1]).max() < tol(dtype)
+
+
+def test_block_arrangement_and_run_order():
+    """A layer named twice keeps two caches; a run step reading another's cache
+    appends nothing and sees the other's keys."""
+    from ayaka_py_b200.config.model import GPT2Config
+    from ayaka_py_b200.models.gpt2 import gpt2_spec
+    from ayaka_py_b200.models.model import Model
+    from ayaka_py_b200.parts import RunStep
+    import dataclasses
+
+    cfg = GPT2Config.from_dict(tiny_models.TINY_A)
+    spec = gpt2_spec(cfg)
+    twice = dataclasses.replace(spec, order=(RunStep(0), RunStep(1), RunStep(0), RunStep(1, cache_of=1)))
+    model = Model(twice, torch.float32, "cuda")
+    assert model.groups[0].layers == 3
+    assert [b.layer for b in model.bindings] == [0, 1, 2, 1] and [b.writes for b in model.bindings] == [True, True, True, False]
+    with pytest.raises(ValueError):
+        Model(dataclasses.replace(spec, order=(RunStep(0, cache_of=0),)), torch.float32, "cuda")
+    with pytest.raises(ValueError):
+        Model(dataclasses.replace(spec, order=(RunStep(5),)), torch.float32, "cuda")
+
+    from ayaka_py_b200.cache import CacheManager
+    from ayaka_py_b200.engine.step import StepEntry, StepRunner
+    from ayaka_py_b200.weights import DictStore, load_weights
+    weights = tiny_models.numpy_weights(tiny_models.TINY_A, 3, scale=4.0)
+    load_weights(model, DictStore({k: torch.from_numpy(v) for k, v in weights.items()}))
+    cache = CacheManager(model.groups, kv_pages=9, page_size=16, max_requests=2, max_len=128,
+                         dtype=torch.float32, device="cuda")
+    runner = StepRunner(model, cache, max_tokens=64)
+    toks = tiny_models.prompts(tiny_models.TINY_A, [19], 1)[0]
+
+    def plain_twice(tokens):
+        c = plain_gpt2.resolve_config(tiny_models.TINY_A)
+        w = {k: v.astype(np.float64) for k, v in weights.items()}
+        d, H = c["n_embd"], c["n_head"]
+        x = plain_gpt2.embed(tokens, np.arange(len(tokens)), w["transformer.wte.weight"], w["transformer.wpe.weight"])
+        x = plain_gpt2.block(x, w, c, 0)
+        entering_second = x
+        x = plain_gpt2.block(x, w, c, 1)
+        x = plain_gpt2.block(x, w, c, 0)
+        # fourth run step: layer 1's weights and queries, keys and values of the SECOND run step
+        p, eps, T = "transformer.h.1.", c["layer_norm_epsilon"], len(tokens)
+        qkv_now = plain_gpt2.linear(plain_gpt2.layer_norm(x, w[p + "ln_1.weight"], w[p + "ln_1.bias"], eps),
+                                    w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"])
+        qkv_then = plain_gpt2.linear(plain_gpt2.layer_norm(entering_second, w[p + "ln_1.weight"], w[p + "ln_1.bias"], eps),
+                                     w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"])
+        o = plain_gpt2.causal_attention(qkv_now[:, :d].reshape(T, H, -1), qkv_then[:, d:2 * d].reshape(T, H, -1),
+                                        qkv_then[:, 2 * d:].reshape(T, H, -1), plain_gpt2.attention_scale(c, 1))
+        x = x + plain_gpt2.linear(o.reshape(T, d), w[p + "attn.c_proj.weight"], w[p + "attn.c_proj.bias"])
+        x = x + plain_gpt2.mlp_part(plain_gpt2.layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], eps),
+                                    w[p + "mlp.c_fc.weight"], w[p + "mlp.c_fc.bias"], w[p + "mlp.c_proj.weight"],
+                                    w[p + "mlp.c_proj.bias"], c["activation_function"])
+        return plain_gpt2.head(x, w, c)
+
+    slot = cache.open("r")
+    res = cache.reserve([(slot, 0, 12)])
+    first = runner.run([StepEntry(slot, 0, toks[:12], list(range(12)))]).cpu().numpy()
+    cache.commit(res)
+    res = cache.reserve([(slot, 12, 7)])
+    second = runner.run([StepEntry(slot, 12, toks[12:], list(range(7)))]).cpu().numpy()
+    cache.commit(res)
+    # whole, in one step, in a fresh request: cutting must not matter
+    other = cache.open("s")
+    res = cache.reserve([(other, 0, 19)])
+    whole = runner.run([StepEntry(other, 0, toks, list(range(19)))]).cpu().numpy()
+    cache.commit(res)
+    assert np.abs(np.concatenate([first, second]) - whole).max() < 1e-4
+    assert np.abs(whole - plain_twice(toks)).max() < 1e-4
+
+
+# ------------------------------------------------------------------ toy parts --
+
+@dataclass(frozen=True)
+class ToyConfig:
+    """Configuration of a toy architecture that exists only in this test."""
+    ARCHITECTURE: ClassVar[str] = "ToyRunningMeanLM"
+    vocab_size: int = 50
+    width: int = 24
+    layers: int = 2
+    positions: int = 64
+
+    @classmethod
+    def from_dict(cls, values):
+        return cls(**{k: values[k] for k in ("vocab_size", "width", "layers", "positions") if k in values})
+
+    def to_dict(self):
+        return {"architectures": [self.ARCHITECTURE], "vocab_size": self.vocab_size, "width": self.width,
+                "layers": self.layers, "positions": self.positions}
+
+
+def register_toy():
+    from ayaka_py_b200.parts import (FeedForward, Init, LayerSpec, Mixer, ModelSpec, PartSpec, RunStep, Source,
+                                     StateNeed, TensorDecl, register_part)
+    from ayaka_py_b200.registry import Architecture, register_architecture
+
+    class RunningMeanMixer(Mixer):
+        """mix(h)_t = W . mean(h_0 .. h_t): the running sum is the state it
+        keeps per request, in the request's slot."""
+
+        def __init__(self, width, dtype, device):
+            self.width, self.dtype = width, dtype
+            self.weight = None
+
+        def tensors(self):
+            return {"weight": TensorDecl((self.width, self.width), "matrix")}
+
+        def cache_need(self):
+            return StateNeed((self.width,), torch.float32)
+
+        def forward(self, h, residual, ctx, cache):
+            state = ctx.cache.state_layer(cache.group, cache.layer)       # [slots, width]
+            out = torch.empty_like(residual)
+            for r in range(ctx.num_requests):
+                a, b = int(ctx.host["q_start"][r]), int(ctx.host["q_start"][r + 1])
+                slot, start = int(ctx.host["slots"][r]), int(ctx.host["pos0"][r])
+                sums = state[slot] + torch.cumsum(h[a:b].float(), dim=0)
+                counts = torch.arange(start + 1, start + 1 + (b - a), device=h.device, dtype=torch.float32)
+                out[a:b] = residual[a:b] + (sums / counts[:, None]) @ self.weight.float().t()
+                state[slot] = sums[-1]
+            return out
+
+    class ScaleFeedForward(FeedForward):
+        def __init__(self, width, dtype, device):
+            self.width = width
+            self.gain = None
+
+        def tensors(self):
+            return {"gain": TensorDecl((self.width,), "vector")}
+
+        def forward(self, h, residual, ctx):
+            return residual + torch.tanh(h.float()) * self.gain
+
+    register_part("toy_running_mean", RunningMeanMixer)
+    register_part("toy_scale_ffn", ScaleFeedForward)
+
+    def spec(cfg: ToyConfig) -> ModelSpec:
+        d = cfg.width
+        norm = lambda name: PartSpec("layernorm", {"width": d, "eps": 1e-5},
+                                     {"weight": Source(name + ".g", init=Init(0.1, 1.0)), "bias": Source(name + ".b", init=Init(0.1))})
+        layers = tuple(LayerSpec(
+            norm(f"l{i}.n1"), PartSpec("toy_running_mean", {"width": d}, {"weight": Source(f"l{i}.mix", init=Init(0.3))}),
+            norm(f"l{i}.n2"), PartSpec("toy_scale_ffn", {"width": d}, {"gain": Source(f"l{i}.gain", init=Init(0.5))}))
+            for i in range(cfg.layers))
+        return ModelSpec(cfg.vocab_size, d, cfg.positions,
+                         PartSpec("token_embedding", {"vocab": cfg.vocab_size, "width": d}, {"weight": Source("emb", init=Init(1.0))}),
+                         PartSpec("no_positions", {}, {}), layers, tuple(RunStep(i) for i in range(cfg.layers)),
+                         norm("final"), PartSpec("lm_head", {"vocab": cfg.vocab_size, "width": d}, {"weight": Source("emb", init=Init(1.0))}))
+
+    register_architecture(Architecture("ToyRunningMeanLM", "toy", ToyConfig, spec))
+
+
+def plain_toy(cfg, t, tokens):
+    x = t["emb"][tokens]
+    for i in range(cfg.layers):
+        h = plain_gpt2.layer_norm(x, t[f"l{i}.n1.g"], t[f"l{i}.n1.b"], 1e-5)
+        mean = np.cumsum(h, axis=0) / np.arange(1, len(tokens) + 1)[:, None]
+        x = x + mean @ t[f"l{i}.mix"].T
+        h = plain_gpt2.layer_norm(x, t[f"l{i}.n2.g"], t[f"l{i}.n2.b"], 1e-5)
+        x = x + np.tanh(h) * t[f"l{i}.gain"]
+    return plain_gpt2.layer_norm(x, t["final.g"], t["final.b"], 1e-5) @ t["emb"].T
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    import trace_tools
+    from ayaka_py_b200.replay import ReplaySession
+    from ayaka_py_b200.weights import write_random_model
+
+    register_toy()
+    cfg = ToyConfig()
+    folder = write_random_model(tmp_path / "toy", cfg, seed=5, dtype="float32")
+    assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyRunningMeanLM"]
+    tensors = {k: v.astype(np.float64) for k, v in plain_gpt2.read_safetensors(folder / "model.safetensors").items()}
+    rs = np.random.RandomState(0)
+    reqs = {f"t{i}": rs.randint(0, cfg.vocab_size, n).tolist() for i, n in enumerate([30, 7, 45, 18])}
+    want = {rid: plain_toy(cfg, tensors, toks) for rid, toks in reqs.items()}
+    for trace in (trace_tools.whole(reqs), trace_tools.portions(reqs), trace_tools.mixed(reqs, seed=2)):
+        session = ReplaySession(folder, "float32", max_tokens=256, page_size=16)
+        assert [type(g.need).__name__ for g in session.model.groups] == ["StateNeed"]
+        outs = [None if (o := session.step(rec)) is None or o.shape[0] == 0 else o.cpu().numpy() for rec in trace]
+        got = trace_tools.collect(trace, outs)
+        assert trace_tools.first_difference(got, want, 1e-4) is None
+        session.cache.assert_clean()

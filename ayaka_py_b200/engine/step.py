@@ -67,20 +67,26 @@ class StepRunner:
         self.rows_run = 0
 
     def _allocate(self, max_tokens: int) -> None:
-        T, R, C = max_tokens, self.max_requests, self.cache.columns
-        sizes = {"tokens": T, "positions": T, "row_req": T, "want_rows": T,
-                 "req_q_start": R + 1, "req_pos0": R, "req_slot": R, "req_kv_len": R}
-        for g in self.kv_groups:
-            sizes[f"table{g}"] = R * C
-        self.max_tokens = T
-        self.offsets, total = {}, 0
-        for name, n in sizes.items():
-            self.offsets[name] = (total, n)
-            total += (n + 3) // 4 * 4            # 16-byte aligned fields
+        self.max_tokens = max_tokens
+        total = self._layout(max_tokens, self.max_requests, max_tokens)[1]
         self.host_buf = torch.zeros(total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
         self.host_np = self.host_buf.numpy()
         self.dev_buf = torch.zeros(total, dtype=torch.int32, device=self.device)
         self._copied = None      # event after the last upload: the pinned buffer is free again
+        self.h2d_bytes = 0       # bytes of the last step's upload
+
+    def _layout(self, T: int, R: int, S: int):
+        """Offsets of the step's fields, packed back to back (16-byte aligned),
+        so that one copy of ``total`` ints brings exactly what the step needs."""
+        sizes = {"tokens": T, "positions": T, "row_req": T, "want_rows": S,
+                 "req_q_start": R + 1, "req_pos0": R, "req_slot": R, "req_kv_len": R}
+        for g in self.kv_groups:
+            sizes[f"table{g}"] = R * self.cache.columns
+        offsets, total = {}, 0
+        for name, n in sizes.items():
+            offsets[name] = (total, n)
+            total += (n + 3) // 4 * 4
+        return offsets, total
 
     def _field(self, buf, name: str, n: int):
         lo, cap = self.offsets[name]
@@ -114,6 +120,8 @@ class StepRunner:
         if int(ends.max()) > limit:
             raise ValueError(f"a request would reach {int(ends.max())} tokens, the model has {limit} positions")
 
+        S = sum(len(e.want) for e in entries)
+        self.offsets, total = self._layout(T, R, S)
         h = self.host_np
         q_start = np.zeros(R + 1, dtype=np.int64)
         np.cumsum(counts, out=q_start[1:])
@@ -132,7 +140,6 @@ class StepRunner:
                 wanted.append(a + int(w))
         if tok.min() < 0 or tok.max() >= self.model.vocab_size:
             raise ValueError(f"token id outside [0, {self.model.vocab_size})")
-        S = len(wanted)
         self._field(h, "want_rows", S)[:] = wanted
         self._field(h, "req_q_start", R + 1)[:] = q_start
         self._field(h, "req_pos0", R)[:] = starts
@@ -141,7 +148,8 @@ class StepRunner:
         C = self.cache.columns
         for g in self.kv_groups:
             self._field(h, f"table{g}", R * C)[:] = self.cache.table_rows(g, slots).reshape(-1)
-        self.dev_buf.copy_(self.host_buf, non_blocking=True)
+        self.dev_buf[:total].copy_(self.host_buf[:total], non_blocking=True)
+        self.h2d_bytes = total * 4
         if self.dev_buf.is_cuda:
             self._copied = torch.cuda.Event()
             self._copied.record()

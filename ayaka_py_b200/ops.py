@@ -63,6 +63,15 @@ def _check(code: int) -> None:
         raise KernelError(library().ayk_last_error().decode("utf-8", "replace"))
 
 
+launches = 0      # kernels of this library launched so far (graph replays are counted by their owner)
+
+
+def _launch(code: int) -> None:
+    global launches
+    launches += 1
+    _check(code)
+
+
 def _ptr(t: torch.Tensor | None):
     if t is None:
         return ctypes.c_void_p(0)
@@ -101,7 +110,7 @@ def embed(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor,
         raise KernelError("position table must match the token table in dtype and width")
     if not table.is_contiguous() or (position_table is not None and not position_table.is_contiguous()):
         raise KernelError("embedding tables must be contiguous")
-    _check(lib.ayk_embed(_ptr(out), _ptr(_i32(tokens, "tokens")), _ptr(_i32(positions, "positions")),
+    _launch(lib.ayk_embed(_ptr(out), _ptr(_i32(tokens, "tokens")), _ptr(_i32(positions, "positions")),
                          _ptr(table), _ptr(position_table), ctypes.c_int(T), ctypes.c_int(d),
                          ctypes.c_int(_tag(table.dtype)), _stream()))
     return out
@@ -120,7 +129,7 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor | None, e
         raise KernelError("layernorm weight and bias must be float32 of the row width")
     if out is None:
         out = torch.empty((n, d), dtype=out_dtype, device=x.device)
-    _check(lib.ayk_layernorm(_ptr(out), _ptr(x), _ptr(gamma), _ptr(beta),
+    _launch(lib.ayk_layernorm(_ptr(out), _ptr(x), _ptr(gamma), _ptr(beta),
                              _ptr(None if rows is None else _i32(rows, "rows")), ctypes.c_int(n),
                              ctypes.c_int(d), ctypes.c_float(eps), ctypes.c_int(_tag(out_dtype)), _stream()))
     return out
@@ -143,7 +152,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None
             raise KernelError(f"{name} must be contiguous float32")
     if residual is not None and tuple(residual.shape) != (M, N):
         raise KernelError("residual must have the output's shape")
-    _check(lib.ayk_gemm_simt(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
+    _launch(lib.ayk_gemm_simt(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
                              ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]),
                              ctypes.c_int(_tag(a.dtype)), ctypes.c_int(_tag(out_dtype)), _stream()))
     return out
@@ -159,7 +168,7 @@ def kv_append(kcache: torch.Tensor, vcache: torch.Tensor, k: torch.Tensor, v: to
         raise KernelError("kv_append: keys and values must be [T, kv_heads*head_dim] slices with one row stride")
     if k.dtype != kcache.dtype or not kcache.is_contiguous() or not vcache.is_contiguous():
         raise KernelError("kv_append: cache must be contiguous and of the rows' dtype")
-    _check(lib.ayk_kv_append(_ptr(kcache), _ptr(vcache), _ptr(k), _ptr(v), ctypes.c_int(k.stride(0)),
+    _launch(lib.ayk_kv_append(_ptr(kcache), _ptr(vcache), _ptr(k), _ptr(v), ctypes.c_int(k.stride(0)),
                              _ptr(_i32(row_req, "row_req")), _ptr(_i32(positions, "positions")),
                              _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)), ctypes.c_int(P),
                              ctypes.c_int(T), ctypes.c_int(width), ctypes.c_int(_tag(k.dtype)), _stream()))
@@ -177,7 +186,7 @@ def attention_simt(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
     if out is None:
         out = torch.empty((T, num_heads * Dh), dtype=q.dtype, device=q.device)
     R = req_pos0.numel()
-    _check(lib.ayk_attention_simt(_ptr(out), _ptr(q), ctypes.c_int(q.stride(0)), _ptr(kcache), _ptr(vcache),
+    _launch(lib.ayk_attention_simt(_ptr(out), _ptr(q), ctypes.c_int(q.stride(0)), _ptr(kcache), _ptr(vcache),
                                   _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)),
                                   _ptr(_i32(req_q_start, "req_q_start")), _ptr(_i32(req_pos0, "req_pos0")),
                                   ctypes.c_int(R), ctypes.c_int(total_rows), ctypes.c_int(num_heads),
@@ -203,7 +212,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None,
     for name, t, dt in (("top_k", top_k, torch.int64), ("top_p", top_p, torch.float32), ("min_p", min_p, torch.float32)):
         if t is not None and (t.dtype != dt or t.numel() != S or not t.is_contiguous()):
             raise KernelError(f"sample: {name} must be a contiguous {dt} tensor with one value per row")
-    _check(lib.ayk_sample(_ptr(out), _ptr(logits), ctypes.c_int(S), ctypes.c_int(V), _ptr(temperature),
+    _launch(lib.ayk_sample(_ptr(out), _ptr(logits), ctypes.c_int(S), ctypes.c_int(V), _ptr(temperature),
                           _ptr(seed), _ptr(offset), _ptr(top_k), _ptr(top_p), _ptr(min_p), _stream()))
     return out
 
@@ -262,7 +271,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         partials, counters = _tc_workspace(a.device, splits * M * N)
         if tiles > counters.numel():
             raise KernelError("gemm_tc: too many output tiles for split-K")
-    _check(lib.ayk_gemm_tc(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
+    _launch(lib.ayk_gemm_tc(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
                            ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]),
                            ctypes.c_int(_tag(out_dtype)), ctypes.c_int(splits), _ptr(partials), _ptr(counters),
                            ctypes.c_int(1 if static_weight else 0), _stream()))

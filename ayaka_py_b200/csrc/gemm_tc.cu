@@ -423,3 +423,112 @@ AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* b
     default: return launch<256>(mw, mx, args, splits, stream);
   }
 }
+
+// ------------------------------------------------------ no-allocation entry --
+// See no_alloc.h.  The scratch of the split-K product lives in the library image.
+#include "no_alloc.h"
+
+namespace {
+
+static __device__ __align__(256) float g_na_partials[AYK_NO_ALLOC_MAX_PARTIALS];
+static __device__ __align__(256) unsigned int g_na_counters[AYK_NO_ALLOC_MAX_TILES];
+static __device__ __align__(256) int g_na_error[64];
+
+constexpr int NA_MAX_DEVICES = 64;
+struct NoAllocDevice {
+  bool ready;
+  float* partials;
+  unsigned int* counters;
+  int* error;
+};
+NoAllocDevice g_na_devices[NA_MAX_DEVICES];   // zero-initialised; one entry per device ordinal
+EncodeTiledFn g_na_encode = nullptr;
+
+// Once per device, with that device current: the names of the __device__ arrays
+// are host-side stand-ins, so their device addresses are asked for here.
+int no_alloc_setup(int device) {
+  NoAllocDevice& d = g_na_devices[device];
+  if (d.ready) return 0;
+  if (g_na_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess)
+      return ayk_fail("ayk_gemm_tc_no_alloc: cuTensorMapEncodeTiled is not available from this driver");
+    g_na_encode = (EncodeTiledFn)fn;
+  }
+  cudaError_t e = cudaGetSymbolAddress((void**)&d.partials, g_na_partials);
+  if (e != cudaSuccess) return ayk_fail("ayk_gemm_tc_no_alloc: cudaGetSymbolAddress(partials): %s", cudaGetErrorString(e));
+  e = cudaGetSymbolAddress((void**)&d.counters, g_na_counters);
+  if (e != cudaSuccess) return ayk_fail("ayk_gemm_tc_no_alloc: cudaGetSymbolAddress(counters): %s", cudaGetErrorString(e));
+  e = cudaGetSymbolAddress((void**)&d.error, g_na_error);
+  if (e != cudaSuccess) return ayk_fail("ayk_gemm_tc_no_alloc: cudaGetSymbolAddress(error): %s", cudaGetErrorString(e));
+  d.ready = true;
+  return 0;
+}
+
+int no_alloc_encode(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = g_na_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return ayk_fail("ayk_gemm_tc_no_alloc: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+}  // namespace
+
+AYK_EXPORT int ayk_gemm_tc_no_alloc(void* C, const void* X, const void* W, const float* bias, const float* residual,
+                                    int M, int N, int K, int act, int out_dtype, int splits, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (ayk_gemm_tc_supported(M, N, K) != 0) return -1;
+  AYK_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "ayk_gemm_tc_no_alloc: operands must be 16-byte aligned");
+  AYK_REQUIRE(out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16, "ayk_gemm_tc_no_alloc: unknown output dtype %d", out_dtype);
+  const int BT = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+  const int tiles = ((N + BLOCK_N - 1) / BLOCK_N) * ((M + BT - 1) / BT);
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  if (splits <= 0) splits = tiles >= 74 ? 1 : 148 / tiles;
+  if (splits > total_kb) splits = total_kb;
+  const int kb_per_split = (total_kb + splits - 1) / splits;
+  splits = (total_kb + kb_per_split - 1) / kb_per_split;
+  AYK_REQUIRE((M + BT - 1) / BT <= 65535 && splits <= 65535, "ayk_gemm_tc_no_alloc: the grid would be too large");
+  if (splits > 1) {
+    AYK_REQUIRE((long long)splits * M * N <= (long long)AYK_NO_ALLOC_MAX_PARTIALS,
+                "ayk_gemm_tc_no_alloc: splits * M * N = %lld floats of scratch exceed the built-in %d; "
+                "use fewer splits or the allocating entry point", (long long)splits * M * N, AYK_NO_ALLOC_MAX_PARTIALS);
+    AYK_REQUIRE(tiles <= AYK_NO_ALLOC_MAX_TILES, "ayk_gemm_tc_no_alloc: %d output tiles exceed the built-in %d counters",
+                tiles, AYK_NO_ALLOC_MAX_TILES);
+  }
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return ayk_fail("ayk_gemm_tc_no_alloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  AYK_REQUIRE(device >= 0 && device < NA_MAX_DEVICES, "ayk_gemm_tc_no_alloc: device ordinal %d is out of range", device);
+  if (no_alloc_setup(device) != 0) return -1;
+  const NoAllocDevice& d = g_na_devices[device];
+  if (splits > 1) {
+    // The counters must start at zero; an earlier call that was cut short may have left them otherwise.
+    e = cudaMemsetAsync(d.counters, 0, sizeof(unsigned int) * (size_t)tiles, stream);
+    if (e != cudaSuccess) return ayk_fail("ayk_gemm_tc_no_alloc: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  }
+  CUtensorMap mw, mx;
+  if (no_alloc_encode(&mw, W, N, K, BLOCK_N) != 0) return -1;
+  if (no_alloc_encode(&mx, X, M, K, BT) != 0) return -1;
+  EpilogueArgs args{C, bias, residual, d.partials, d.counters, d.error, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split};
+  switch (BT) {
+    case 16: return launch<16>(mw, mx, args, splits, stream);
+    case 32: return launch<32>(mw, mx, args, splits, stream);
+    case 64: return launch<64>(mw, mx, args, splits, stream);
+    case 128: return launch<128>(mw, mx, args, splits, stream);
+    default: return launch<256>(mw, mx, args, splits, stream);
+  }
+}
+
+AYK_EXPORT int ayk_gemm_tc_no_alloc_error(void) {
+  int value = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&value, g_na_error, sizeof(int));
+  if (e != cudaSuccess) return -1;
+  return value;
+}

@@ -127,8 +127,9 @@ class CacheManager:
                 self.first_page.append(None)
                 self.num_pages.append(None)
                 self.kv.append(None)
+                # one spare slot at index max_requests: where padding lanes of a graph step write
                 self.state.append(None if device is None else torch.zeros(
-                    (g.layers, max_requests, *g.need.shape), dtype=g.need.dtype, device=device))
+                    (g.layers, max_requests + 1, *g.need.shape), dtype=g.need.dtype, device=device))
             else:
                 raise TypeError(f"group {g.name}: unknown need {g.need!r}")
 
@@ -290,7 +291,7 @@ class CacheManager:
         return slab[layer, 0], slab[layer, 1]
 
     def state_layer(self, g: int, layer: int) -> torch.Tensor:
-        """State of one layer: [max_requests, *shape], indexed by slot."""
+        """State of one layer: [max_requests + 1, *shape], indexed by slot (the last is a spare)."""
         return self.state[g][layer]
 
     def bytes_per_token(self) -> int:

@@ -179,15 +179,22 @@ AYK_EXPORT int ayk_attention_simt(void* out, const void* q, int q_stride, const 
   size_t smem = ((size_t)BQ * Dh + (size_t)BKEYS * (Dh + 1) + (size_t)BKEYS * Dh + (size_t)BQ * BKEYS) * sizeof(float);
   dim3 grid(max_tiles, H);
   cudaError_t err;
+  static size_t configured[2] = {0, 0};      // largest shared-memory size asked for so far, per dtype
   if (dtype == AYK_DTYPE_F32) {
-    err = cudaFuncSetAttribute(attention_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return ayk_fail("ayk_attention_simt: shared memory %zu: %s", smem, cudaGetErrorString(err));
+    if (smem > configured[0]) {
+      err = cudaFuncSetAttribute(attention_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return ayk_fail("ayk_attention_simt: shared memory %zu: %s", smem, cudaGetErrorString(err));
+      configured[0] = smem;
+    }
     attention_simt_kernel<float><<<grid, WARPS * 32, smem, stream>>>(
         (float*)out, (const float*)q, q_stride, (const float*)kcache, (const float*)vcache, table, table_stride,
         req_q_start, req_pos0, num_req, H, Hkv, Dh, page_size, scale, window);
   } else if (dtype == AYK_DTYPE_BF16) {
-    err = cudaFuncSetAttribute(attention_simt_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return ayk_fail("ayk_attention_simt: shared memory %zu: %s", smem, cudaGetErrorString(err));
+    if (smem > configured[1]) {
+      err = cudaFuncSetAttribute(attention_simt_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return ayk_fail("ayk_attention_simt: shared memory %zu: %s", smem, cudaGetErrorString(err));
+      configured[1] = smem;
+    }
     attention_simt_kernel<__nv_bfloat16><<<grid, WARPS * 32, smem, stream>>>(
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kcache,
         (const __nv_bfloat16*)vcache, table, table_stride, req_q_start, req_pos0, num_req, H, Hkv, Dh,

@@ -34,7 +34,7 @@ class Engine:
         self.decode_graphs = None
         if config.decode_graph:
             from .graphs import DecodeGraphs
-            self.decode_graphs = DecodeGraphs(self)
+            self.decode_graphs = DecodeGraphs(self.runner, model, config.max_requests)
 
     def submit(self, request: Request) -> None:
         self.scheduler.add(request)

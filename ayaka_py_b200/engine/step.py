@@ -74,6 +74,7 @@ class StepRunner:
         self.dev_buf = torch.zeros(total, dtype=torch.int32, device=self.device)
         self._copied = None      # event after the last upload: the pinned buffer is free again
         self.h2d_bytes = 0       # bytes of the last step's upload
+        self.generation = getattr(self, "generation", 0) + 1    # graphs captured on the old buffer are stale
 
     def _layout(self, T: int, R: int, S: int):
         """Offsets of the step's fields, packed back to back (16-byte aligned),
@@ -92,26 +93,37 @@ class StepRunner:
         lo, cap = self.offsets[name]
         return buf[lo:lo + n]
 
-    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
-        if not entries:
+    def prepare(self, entries: Sequence[StepEntry], pad_to: int | None = None) -> StepContext:
+        """Validates, packs and uploads a step.  ``pad_to``: for a pure-decode
+        step, add padding lanes up to that many requests (position 0, the
+        padding page, the spare state slot, token 0): they read nothing that
+        lives and write nothing, and keep the step's shape fixed for a graph."""
+        if not entries and not pad_to:
             raise ValueError("a step needs at least one entry")
         if self._copied is not None:
             self._copied.synchronize()
-        R = len(entries)
-        if R > self.max_requests:
+        n = len(entries)
+        R = max(n, pad_to or 0)
+        if R > max(self.max_requests, pad_to or 0):
             raise ValueError(f"{R} requests in one step, the engine was built for {self.max_requests}")
-        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=R)
+        counts = np.ones(R, dtype=np.int64)
+        counts[:n] = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=n)
         if (counts < 1).any():
             raise ValueError("every entry must bring at least one token")
+        if pad_to and (counts != 1).any():
+            raise ValueError("only steps of single tokens can be padded")
         T = int(counts.sum())
-        if T > self.max_tokens:
+        if T > self.max_tokens or R > self.max_requests:
+            self.max_requests = max(R, self.max_requests)
             self._allocate(max(T, 2 * self.max_tokens))
-        slots = np.fromiter((e.slot for e in entries), dtype=np.int64, count=R)
-        if len(set(slots.tolist())) != R:
+        slots = np.full(R, self.cache.max_requests, dtype=np.int64)        # padding lanes: the spare slot
+        slots[:n] = np.fromiter((e.slot for e in entries), dtype=np.int64, count=n)
+        if len(set(slots[:n].tolist())) != n:
             raise ValueError("a request appears twice in one step")
-        starts = np.fromiter((e.start for e in entries), dtype=np.int64, count=R)
+        starts = np.zeros(R, dtype=np.int64)
+        starts[:n] = np.fromiter((e.start for e in entries), dtype=np.int64, count=n)
         ends = starts + counts
-        for e, end in zip(entries, ends):
+        for e in entries:
             if e.slot not in self.cache.request_of or not self.cache.in_step[e.slot]:
                 raise RuntimeError(f"slot {e.slot} was not reserved for this step")
             if e.start != self.cache.length[e.slot]:
@@ -120,7 +132,7 @@ class StepRunner:
         if int(ends.max()) > limit:
             raise ValueError(f"a request would reach {int(ends.max())} tokens, the model has {limit} positions")
 
-        S = sum(len(e.want) for e in entries)
+        S = sum(len(e.want) for e in entries) + (R - n)
         self.offsets, total = self._layout(T, R, S)
         h = self.host_np
         q_start = np.zeros(R + 1, dtype=np.int64)
@@ -138,6 +150,10 @@ class StepRunner:
                 if not 0 <= w < b - a:
                     raise ValueError(f"want {w} is outside the entry's {b - a} tokens")
                 wanted.append(a + int(w))
+        for r in range(n, R):                      # padding lanes
+            a = int(q_start[r])
+            tok[a], pos[a], row_req[a] = 0, 0, r
+            wanted.append(a)
         if tok.min() < 0 or tok.max() >= self.model.vocab_size:
             raise ValueError(f"token id outside [0, {self.model.vocab_size})")
         self._field(h, "want_rows", S)[:] = wanted
@@ -147,7 +163,9 @@ class StepRunner:
         self._field(h, "req_kv_len", R)[:] = ends
         C = self.cache.columns
         for g in self.kv_groups:
-            self._field(h, f"table{g}", R * C)[:] = self.cache.table_rows(g, slots).reshape(-1)
+            rows = self._field(h, f"table{g}", R * C).reshape(R, C)
+            rows[:n] = self.cache.table_rows(g, slots[:n])
+            rows[n:] = 0                           # the padding page
         self.dev_buf[:total].copy_(self.host_buf[:total], non_blocking=True)
         self.h2d_bytes = total * 4
         if self.dev_buf.is_cuda:

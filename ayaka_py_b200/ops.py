@@ -294,8 +294,48 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return gemm_simt(a, w, bias, activation, residual, out_dtype, out)
 
 
+DECODE_PART = 128
+_decode_scratch: dict = {}
+
+
+def attention_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, table: torch.Tensor,
+                     req_pos0: torch.Tensor, num_heads: int, scale: float, window: int | None,
+                     max_context: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One query row per request over its pages, split along the context and
+    merged.  ``max_context``: the longest context the engine allows (fixes the grid)."""
+    lib = _ready()
+    pages, P, Hkv, Dh = kcache.shape
+    R = q.shape[0]
+    if q.shape[1] != num_heads * Dh or q.stride(1) != 1 or q.dtype != kcache.dtype:
+        raise KernelError("attention_decode: q must be a [R, heads*head_dim] slice of the cache's dtype")
+    if req_pos0.numel() != R:
+        raise KernelError("attention_decode: one row per request")
+    parts = -(-max_context // DECODE_PART)
+    need = R * num_heads * parts * (Dh + 2)
+    scratch = _decode_scratch.get(q.device)
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
+        _decode_scratch[q.device] = scratch
+    if out is None:
+        out = torch.empty((R, num_heads * Dh), dtype=q.dtype, device=q.device)
+    _launch(lib.ayk_attention_decode(_ptr(out), _ptr(q), ctypes.c_int(q.stride(0)), _ptr(kcache), _ptr(vcache),
+                                     _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)),
+                                     _ptr(_i32(req_pos0, "req_pos0")), ctypes.c_int(R), ctypes.c_int(num_heads),
+                                     ctypes.c_int(Hkv), ctypes.c_int(Dh), ctypes.c_int(P), ctypes.c_float(scale),
+                                     ctypes.c_int(window or 0), ctypes.c_int(parts), _ptr(scratch),
+                                     ctypes.c_int(_tag(q.dtype)), _stream()))
+    global launches
+    launches += 1            # the call launches two kernels (partitions, merge)
+    return out
+
+
 def attention(q, kcache, vcache, table, ctx, num_heads: int, scale: float,
               window: int | None = None) -> torch.Tensor:
-    """Attention of the step's rows (``ctx`` gives the rows of each request)."""
+    """Attention of the step's rows (``ctx`` gives the rows of each request): the
+    split-context decode kernels when every request brings one row, else the
+    general kernel."""
+    if ctx.max_q_len == 1:
+        return attention_decode(q, kcache, vcache, table, ctx.req_pos0, num_heads, scale, window,
+                                ctx.cache.max_len)
     return attention_simt(q, kcache, vcache, table, ctx.req_q_start, ctx.req_pos0, ctx.num_rows,
                           num_heads, scale, window)

@@ -115,3 +115,21 @@ def test_smoke_entry():
     sys.path.insert(0, str(ROOT))
     import __graft_entry__
     __graft_entry__.smoke()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_graphs_give_the_same_tokens(model_folders, dtype):
+    """Pure-decode steps replayed from CUDA graphs (padded to a bucket) against the eager engine."""
+    from ayaka_py_b200 import LLM, SamplingParams, StopCriteria
+    folder, cfg, weights = model_folders["B"]
+    prompts = tiny_models.prompts(cfg, [3, 20, 41], seed=26)
+    stop = [StopCriteria(max_tokens=n, ignore_eos=True) for n in (30, 12, 21)]     # the batch shrinks: 3 -> 2 -> 1
+    params = [SamplingParams(temperature=0.0), SamplingParams(temperature=0.7, seed=5), SamplingParams(temperature=0.0)]
+    eager = LLM(folder, dtype=dtype, page_size=8, kv_pages=64, batch_tokens=64, prefill_chunk=32)
+    graphs = LLM(folder, dtype=dtype, page_size=8, kv_pages=64, batch_tokens=64, prefill_chunk=32, decode_graph=True)
+    want = [r.token_ids for r in eager.generate(prompts, params, stop)]
+    got = [r.token_ids for r in graphs.generate(prompts, params, stop)]
+    assert got == want
+    assert sorted(graphs.engine.decode_graphs.graphs) == [1, 2, 4]
+    assert graphs.engine.decode_graphs.launches > 0
+    graphs.engine.cache.assert_clean()

@@ -275,3 +275,41 @@ def test_gemm_tcgen05_refuses_odd_k():
         ops.gemm_tc(torch.zeros(2, 12, device="cuda", dtype=torch.bfloat16), torch.zeros(4, 12, device="cuda", dtype=torch.bfloat16))
     out = ops.linear(torch.ones(2, 12, device="cuda", dtype=torch.bfloat16), torch.ones(4, 12, device="cuda", dtype=torch.bfloat16))
     assert float(out.float().max()) == 12.0      # the dispatcher takes the FP32-pipe kernel instead
+
+
+DECODE_CASES = [
+    # contexts (tokens cached before the row), H, Hkv, Dh, P, window
+    ([0, 17, 127, 128, 300], 4, 4, 64, 16, None),
+    ([5, 255, 256, 640], 25, 25, 64, 16, None),
+    ([1, 129, 400], 6, 2, 48, 8, None),
+    ([700], 2, 1, 256, 32, None),
+    ([3, 130, 500], 4, 2, 32, 16, 40),
+    ([63, 64, 200], 5, 5, 16, 64, 129),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", DECODE_CASES)
+def test_decode_attention_split_and_merge(dtype, case):
+    from ayaka_py_b200 import ops
+    ctxs, H, Hkv, Dh, P, window = case
+    rs = np.random.RandomState(8)
+    x, plain = paged_case(rs, [1] * len(ctxs), ctxs, H, Hkv, Dh, P, dtype)
+    scale = 1.3 / np.sqrt(Dh)
+    ops.kv_append(x["kc"], x["vc"], x["k"], x["v"], x["row_req"], x["pos"], x["table"])
+    out = ops.attention_decode(x["q"], x["kc"], x["vc"], x["table"], x["pos0"], H, scale, window, 1024)
+    assert np.abs(out.float().cpu().numpy() - plain(scale, window)).max() < tol(dtype)
+    general = ops.attention_simt(x["q"], x["kc"], x["vc"], x["table"], x["q_start"], x["pos0"], len(ctxs), H, scale, window)
+    assert np.abs(out.float().cpu().numpy() - general.float().cpu().numpy()).max() < tol(dtype)
+
+
+@pytest.mark.parametrize("kpos", [0, 127, 128, 383, 384])
+def test_decode_attention_far_key_at_a_partition_edge(kpos):
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(9)
+    x, plain = paged_case(rs, [1, 1], [500, 9], 2, 2, 64, 16, "bfloat16", sharp=(0, 500, kpos))
+    ops.kv_append(x["kc"], x["vc"], x["k"], x["v"], x["row_req"], x["pos"], x["table"])
+    out = ops.attention_decode(x["q"], x["kc"], x["vc"], x["table"], x["pos0"], 2, 1.0, None, 1024).float().cpu().numpy()
+    want = plain(1.0, None)
+    assert np.abs(want[0] - plain(0.0, None)[0]).max() > 0.5
+    assert np.abs(out - want).max() < tol("bfloat16")

@@ -53,6 +53,8 @@ decode_split_kernel(float* __restrict__ scratch, const T* __restrict__ q, int q_
                     const T* __restrict__ kcache, const T* __restrict__ vcache,
                     const int* __restrict__ table, int table_stride, const int* __restrict__ req_pos0,
                     int H, int Hkv, int Dh, int page_size, float scale, int window, int parts) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y, part = blockIdx.z;
   const int pos = req_pos0[r];                 // the query's position; keys 0..pos are visible
   int k_lo = part * PART, k_hi = min(pos + 1, k_lo + PART);
@@ -85,11 +87,18 @@ decode_split_kernel(float* __restrict__ scratch, const T* __restrict__ q, int q_
     if (page > 0) {
       const T* krow = kcache + ((size_t)page * page_size + (kp % page_size)) * row_elems + (size_t)kvh * Dh;
       float acc = 0.f;
-      for (int d = 0; d < Dh; d += VN) {
-        float kv[VN];
-        load_vec(krow + d, kv);
+      // Loads first, arithmetic after: several 16-byte loads in flight per thread.
+      for (int d0 = 0; d0 < Dh; d0 += 4 * VN) {
+        float kv[4][VN];
 #pragma unroll
-        for (int i = 0; i < VN; ++i) acc = fmaf(qs[d + i], kv[i], acc);
+        for (int u = 0; u < 4; ++u)
+          if (d0 + u * VN < Dh) load_vec(krow + d0 + u * VN, kv[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (d0 + u * VN < Dh) {
+#pragma unroll
+            for (int i = 0; i < VN; ++i) acc = fmaf(qs[d0 + u * VN + i], kv[u][i], acc);
+          }
       }
       s = acc;
     }
@@ -112,19 +121,30 @@ decode_split_kernel(float* __restrict__ scratch, const T* __restrict__ q, int q_
   for (int c = 0; c < MAX_DH / 64; ++c) acc[c] = make_float2(0.f, 0.f);
   const int pairs = Dh / 2;
   const int n_keys = k_hi - k_lo;
-  for (int j = warp; j < n_keys; j += WARPS) {
-    const float pj = ps[j];
-    if (pj == 0.f) continue;
-    const int key = k_lo + j;
-    const int page = my_table[key / page_size];
-    const T* vrow = vcache + ((size_t)page * page_size + (key % page_size)) * row_elems + (size_t)kvh * Dh;
+  constexpr int UNROLL = 8;            // keys whose rows are in flight at once per warp
+  for (int j0 = warp; j0 < n_keys; j0 += WARPS * UNROLL) {
+    float pj[UNROLL];
+    const T* vrow[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int j = j0 + u * WARPS;
+      pj[u] = j < n_keys ? ps[j] : 0.f;
+      const int key = k_lo + (j < n_keys ? j : 0);
+      const int page = pj[u] != 0.f ? my_table[key / page_size] : 0;
+      vrow[u] = vcache + ((size_t)page * page_size + (key % page_size)) * row_elems + (size_t)kvh * Dh;
+    }
 #pragma unroll
     for (int c = 0; c < MAX_DH / 64; ++c) {
       const int pp = lane + 32 * c;
       if (pp < pairs) {
-        float2 v = load_pair(vrow + 2 * pp);
-        acc[c].x = fmaf(pj, v.x, acc[c].x);
-        acc[c].y = fmaf(pj, v.y, acc[c].y);
+        float2 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) v[u] = pj[u] != 0.f ? load_pair(vrow[u] + 2 * pp) : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          acc[c].x = fmaf(pj[u], v[u].x, acc[c].x);
+          acc[c].y = fmaf(pj[u], v[u].y, acc[c].y);
+        }
       }
     }
   }
@@ -141,6 +161,8 @@ decode_split_kernel(float* __restrict__ scratch, const T* __restrict__ q, int q_
 
 template <typename T>
 __global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict__ scratch, int H, int Dh, int parts) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
   const float* base = scratch + (size_t)(r * H + h) * parts * (Dh + 2);
   float m = -INFINITY;
@@ -181,15 +203,16 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, cons
   dim3 grid(R, H, parts), mgrid(R, H);
   int mthreads = Dh <= 32 ? 32 : (Dh <= 64 ? 64 : 128);
   if (dtype == AYK_DTYPE_F32) {
-    decode_split_kernel<float><<<grid, WARPS * 32, 0, stream>>>(scratch, (const float*)q, q_stride, (const float*)kcache,
-                                                               (const float*)vcache, table, table_stride, req_pos0, H, Hkv,
-                                                               Dh, page_size, scale, window, parts);
-    decode_merge_kernel<float><<<mgrid, mthreads, 0, stream>>>((float*)out, scratch, H, Dh, parts);
+    ayk_launch(decode_split_kernel<float>, grid, dim3(WARPS * 32), 0, stream, scratch, (const float*)q, q_stride,
+               (const float*)kcache, (const float*)vcache, table, table_stride, req_pos0, H, Hkv, Dh, page_size, scale,
+               window, parts);
+    ayk_launch(decode_merge_kernel<float>, mgrid, dim3(mthreads), 0, stream, (float*)out, (const float*)scratch, H, Dh, parts);
   } else if (dtype == AYK_DTYPE_BF16) {
-    decode_split_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(
-        scratch, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, table,
-        table_stride, req_pos0, H, Hkv, Dh, page_size, scale, window, parts);
-    decode_merge_kernel<__nv_bfloat16><<<mgrid, mthreads, 0, stream>>>((__nv_bfloat16*)out, scratch, H, Dh, parts);
+    ayk_launch(decode_split_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), 0, stream, scratch, (const __nv_bfloat16*)q,
+               q_stride, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, table, table_stride, req_pos0, H, Hkv,
+               Dh, page_size, scale, window, parts);
+    ayk_launch(decode_merge_kernel<__nv_bfloat16>, mgrid, dim3(mthreads), 0, stream, (__nv_bfloat16*)out,
+               (const float*)scratch, H, Dh, parts);
   } else {
     return ayk_fail("ayk_attention_decode: unknown dtype %d", dtype);
   }

@@ -33,6 +33,8 @@ attention_simt_kernel(T* __restrict__ out, const T* __restrict__ q, int q_stride
                       const int* __restrict__ table, int table_stride,
                       const int* __restrict__ req_q_start, const int* __restrict__ req_pos0,
                       int num_req, int H, int Hkv, int Dh, int page_size, float scale, int window) {
+  pdl_trigger();
+  pdl_wait();
   // Which request and which of its row tiles is this block?
   int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
   for (int r = 0; r < num_req; ++r) {
@@ -186,7 +188,7 @@ AYK_EXPORT int ayk_attention_simt(void* out, const void* q, int q_stride, const 
       if (err != cudaSuccess) return ayk_fail("ayk_attention_simt: shared memory %zu: %s", smem, cudaGetErrorString(err));
       configured[0] = smem;
     }
-    attention_simt_kernel<float><<<grid, WARPS * 32, smem, stream>>>(
+    ayk_launch(attention_simt_kernel<float>, grid, dim3(WARPS * 32), smem, stream,
         (float*)out, (const float*)q, q_stride, (const float*)kcache, (const float*)vcache, table, table_stride,
         req_q_start, req_pos0, num_req, H, Hkv, Dh, page_size, scale, window);
   } else if (dtype == AYK_DTYPE_BF16) {
@@ -195,7 +197,7 @@ AYK_EXPORT int ayk_attention_simt(void* out, const void* q, int q_stride, const 
       if (err != cudaSuccess) return ayk_fail("ayk_attention_simt: shared memory %zu: %s", smem, cudaGetErrorString(err));
       configured[1] = smem;
     }
-    attention_simt_kernel<__nv_bfloat16><<<grid, WARPS * 32, smem, stream>>>(
+    ayk_launch(attention_simt_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), smem, stream,
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kcache,
         (const __nv_bfloat16*)vcache, table, table_stride, req_q_start, req_pos0, num_req, H, Hkv, Dh,
         page_size, scale, window);

@@ -29,6 +29,11 @@ int ayk_check_launch(const char* what) {
 
 AYK_EXPORT const char* ayk_last_error() { return g_error; }
 
+static int g_pdl = 0;
+int ayk_pdl_enabled() { return g_pdl; }
+// Launch kernels with programmatic stream serialization (1) or plainly (0).
+AYK_EXPORT void ayk_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
 AYK_EXPORT int ayk_init(int device) {
   cudaError_t err = cudaSetDevice(device);
   if (err != cudaSuccess) return ayk_fail("cudaSetDevice(%d): %s", device, cudaGetErrorString(err));
@@ -44,6 +49,8 @@ template <typename W>
 __global__ void embed_kernel(float* __restrict__ out, const int* __restrict__ tok,
                              const int* __restrict__ pos, const W* __restrict__ wte,
                              const W* __restrict__ wpe, int d) {
+  pdl_trigger();
+  pdl_wait();
   int t = blockIdx.x;
   const W* e = wte + (size_t)tok[t] * d;
   const W* p = wpe ? wpe + (size_t)pos[t] * d : nullptr;
@@ -62,10 +69,10 @@ AYK_EXPORT int ayk_embed(float* out, const int* tok, const int* pos, const void*
   if (T == 0) return 0;
   int threads = d >= 256 ? 256 : 128;
   if (dtype == AYK_DTYPE_F32)
-    embed_kernel<float><<<T, threads, 0, stream>>>(out, tok, pos, (const float*)wte, (const float*)wpe, d);
+    ayk_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, out, tok, pos, (const float*)wte, (const float*)wpe, d);
   else if (dtype == AYK_DTYPE_BF16)
-    embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(out, tok, pos, (const __nv_bfloat16*)wte,
-                                                          (const __nv_bfloat16*)wpe, d);
+    ayk_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, out, tok, pos,
+               (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, d);
   else
     return ayk_fail("ayk_embed: unknown dtype %d", dtype);
   return ayk_check_launch("ayk_embed");
@@ -89,6 +96,8 @@ __global__ void layernorm_kernel(O* __restrict__ out, const float* __restrict__ 
                                  const int* __restrict__ rows, int d, float eps) {
   extern __shared__ float row[];
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   int r = blockIdx.x;
   const float* src = x + (size_t)(rows ? rows[r] : r) * d;
   float s = 0.f;
@@ -122,9 +131,9 @@ AYK_EXPORT int ayk_layernorm(void* out, const float* x, const float* gamma, cons
   int threads = d >= 1024 ? 256 : 128;
   size_t smem = (size_t)d * sizeof(float);
   if (out_dtype == AYK_DTYPE_F32)
-    layernorm_kernel<float><<<n_rows, threads, smem, stream>>>((float*)out, x, gamma, beta, rows, d, eps);
+    ayk_launch(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, (float*)out, x, gamma, beta, rows, d, eps);
   else if (out_dtype == AYK_DTYPE_BF16)
-    layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>((__nv_bfloat16*)out, x, gamma, beta, rows, d, eps);
+    ayk_launch(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, (__nv_bfloat16*)out, x, gamma, beta, rows, d, eps);
   else
     return ayk_fail("ayk_layernorm: unknown dtype %d", out_dtype);
   return ayk_check_launch("ayk_layernorm");
@@ -137,6 +146,8 @@ __global__ void kv_append_kernel(T* __restrict__ kcache, T* __restrict__ vcache,
                                  const int* __restrict__ row_req, const int* __restrict__ pos,
                                  const int* __restrict__ table, int table_stride, int page_size,
                                  int width) {
+  pdl_trigger();
+  pdl_wait();
   int t = blockIdx.x;
   int p = pos[t];
   int page = table[(size_t)row_req[t] * table_stride + p / page_size];
@@ -160,13 +171,12 @@ AYK_EXPORT int ayk_kv_append(void* kcache, void* vcache, const void* k, const vo
   if (T == 0) return 0;
   int threads = width >= 512 ? 256 : 128;
   if (dtype == AYK_DTYPE_F32)
-    kv_append_kernel<float><<<T, threads, 0, stream>>>((float*)kcache, (float*)vcache, (const float*)k,
-                                                       (const float*)v, row_stride, row_req, pos, table,
-                                                       table_stride, page_size, width);
+    ayk_launch(kv_append_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)kcache, (float*)vcache,
+               (const float*)k, (const float*)v, row_stride, row_req, pos, table, table_stride, page_size, width);
   else if (dtype == AYK_DTYPE_BF16)
-    kv_append_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
-        (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
-        row_stride, row_req, pos, table, table_stride, page_size, width);
+    ayk_launch(kv_append_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)kcache,
+               (__nv_bfloat16*)vcache, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride, row_req, pos,
+               table, table_stride, page_size, width);
   else
     return ayk_fail("ayk_kv_append: unknown dtype %d", dtype);
   return ayk_check_launch("ayk_kv_append");

@@ -36,6 +36,8 @@ gemm_simt_kernel(TO* __restrict__ C, const TA* __restrict__ A, const TW* __restr
                  int M, int N, int K, int act) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int lr = tid >> 2, lk = (tid & 3) * 4;       // loader: row of the tile, k offset
@@ -96,11 +98,11 @@ int launch(void* C, const void* A, const void* W, const float* bias, const float
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   bool vec = (K % 4 == 0) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
   if (vec)
-    gemm_simt_kernel<TA, TW, TO, true><<<grid, 256, 0, stream>>>((TO*)C, (const TA*)A, (const TW*)W, bias,
-                                                                 residual, M, N, K, act);
+    ayk_launch(gemm_simt_kernel<TA, TW, TO, true>, grid, dim3(256), 0, stream, (TO*)C, (const TA*)A, (const TW*)W, bias,
+               residual, M, N, K, act);
   else
-    gemm_simt_kernel<TA, TW, TO, false><<<grid, 256, 0, stream>>>((TO*)C, (const TA*)A, (const TW*)W, bias,
-                                                                  residual, M, N, K, act);
+    ayk_launch(gemm_simt_kernel<TA, TW, TO, false>, grid, dim3(256), 0, stream, (TO*)C, (const TA*)A, (const TW*)W, bias,
+               residual, M, N, K, act);
   return ayk_check_launch("ayk_gemm_simt");
 }
 

@@ -189,12 +189,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_trigger();     // the next kernel may be scheduled; it waits for this one before it touches its data
 
   if (warp == 0) {
     if (lane == 0) {
-      int issued = 0;
       bool ok = true;
-      for (int i = 0; i < num_kb && ok; ++i) {
+      // The weight does not depend on the kernels before this one: its first
+      // stages start streaming at once; the rows X wait for the predecessor.
+      const int pre = min(num_kb, STAGES);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full_bar(i), STAGE_BYTES);
+        tma_load_2d(tiles + i * STAGE_BYTES, &map_w, (kb_begin + i) * BLOCK_K, n0, full_bar(i));
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(tiles + i * STAGE_BYTES + A_BYTES, &map_x, (kb_begin + i) * BLOCK_K, t0, full_bar(i));
+      int issued = pre;
+      for (int i = pre; i < num_kb && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
         ok = mbar_wait(empty_bar(s), phase ^ 1u, args.error, 1);
@@ -238,6 +249,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // Epilogue: warp w may read TMEM lanes 32 * (w % 4) ... + 31.
     const int quarter = warp & 3;
     const int n = n0 + quarter * 32 + lane;
+    pdl_wait();        // residual, partials and C belong to kernels before this one until here
     const bool ok = mbar_wait(tmem_full_bar, 0u, args.error, 4);
     tc_fence_after();
     const int splits = gridDim.z;
@@ -353,7 +365,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& arg
     configured = true;
   }
   dim3 grid((args.N + BLOCK_N - 1) / BLOCK_N, (args.M + BT - 1) / BT, splits);
-  gemm_tc_kernel<BT><<<grid, THREADS, SMEM, stream>>>(mw, mx, args);
+  ayk_launch(gemm_tc_kernel<BT>, grid, dim3(THREADS), SMEM, stream, mw, mx, args);
   return ayk_check_launch("ayk_gemm_tc");
 }
 

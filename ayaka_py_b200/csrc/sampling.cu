@@ -169,6 +169,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
   __shared__ double partial[THREADS];
   __shared__ int chosen_thread;
   __shared__ double chosen_base, target_s;
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * V;
   MaxIdx top = block_argmax(row, V, red);
@@ -246,6 +248,6 @@ AYK_EXPORT int ayk_sample(int* out, const float* logits, int S, int V, const flo
   AYK_REQUIRE(V >= 1, "ayk_sample: empty vocabulary");
   AYK_REQUIRE(temperature == nullptr || (seed != nullptr && offset != nullptr),
               "ayk_sample: temperature sampling needs seeds and offsets");
-  sample_kernel<<<S, THREADS, 0, stream>>>(out, logits, V, temperature, seed, offset, top_k, top_p, min_p);
+  ayk_launch(sample_kernel, dim3(S), dim3(THREADS), 0, stream, out, logits, V, temperature, seed, offset, top_k, top_p, min_p);
   return ayk_check_launch("ayk_sample");
 }

@@ -9,6 +9,7 @@ raises.  Every function launches on torch's current stream.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 
 import torch
@@ -54,8 +55,17 @@ def _ready():
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: this package runs its kernels on a B200 and has no CPU path")
         _check(lib.ayk_init(ctypes.c_int(torch.cuda.current_device())))
+        lib.ayk_set_pdl(ctypes.c_int(0 if os.environ.get("AYAKA_B200_PDL", "1") == "0" else 1))
         _initialised = True
     return lib
+
+
+def set_pdl(on: bool) -> None:
+    """Launch kernels with programmatic stream serialization (the default; the
+    environment variable AYAKA_B200_PDL=0 switches it off): a kernel may be
+    scheduled while its predecessor still runs and waits, on the device, for
+    the predecessor's results before it touches them."""
+    _ready().ayk_set_pdl(ctypes.c_int(1 if on else 0))
 
 
 def _check(code: int) -> None:

@@ -133,3 +133,19 @@ def test_decode_graphs_give_the_same_tokens(model_folders, dtype):
     assert sorted(graphs.engine.decode_graphs.graphs) == [1, 2, 4]
     assert graphs.engine.decode_graphs.launches > 0
     graphs.engine.cache.assert_clean()
+
+
+def test_programmatic_dependent_launch_on_and_off_agree(model_folders):
+    from ayaka_py_b200 import LLM, SamplingParams, StopCriteria, ops
+    folder, cfg, weights = model_folders["A"]
+    prompts = tiny_models.prompts(cfg, [11, 30], seed=27)
+    stop = StopCriteria(max_tokens=12, ignore_eos=True)
+    out = {}
+    try:
+        for on in (False, True):
+            ops.set_pdl(on)
+            llm = LLM(folder, dtype="bfloat16", page_size=16, kv_pages=32, decode_graph=on)
+            out[on] = [r.token_ids for r in llm.generate(prompts, SamplingParams(temperature=0.0), stop)]
+    finally:
+        ops.set_pdl(True)
+    assert out[False] == out[True]

@@ -1,0 +1,447 @@
+// Causal attention of prompt portions over the paged cache on the 5th-generation
+// tensor cores (tcgen05), bfloat16, head size 64.
+//
+// One CTA takes up to 128 consecutive rows of one request and one head.  The
+// keys and values of the request are walked 128 at a time: TMA brings each page
+// (page_size keys x 64 x bf16, 128-byte swizzle) straight from the cache into a
+// K tile and a V tile; S = Q K^T (128 x 128, float32) is made in tensor memory;
+// four warps hold one row each per thread, read their row of S, apply scale and
+// mask, keep the running maximum and sum in 32-bit (online softmax, natural
+// exp), write P as bfloat16 into shared memory in the MMA's swizzled layout;
+// O_tile = P V (128 x 64) is made in tensor memory and added, per thread, to the
+// row's running output in registers.  Formula and masking as in the general
+// kernel (kernel/triton/paged_attention.py:295-355 in the reference, which walks
+// the keys per query token without tensor cores).
+//
+// Warps 0..3: softmax and output (warp w owns TMEM lanes 32w..32w+31); warp 4:
+// TMA producer; warp 5: MMA issue and TMEM allocation.  K/V tiles are double
+// buffered.  Every mbarrier wait is bounded; a wait that runs out records a code
+// in the error word and the CTA winds down.
+#include <cuda.h>
+#include <math.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BQ = 128;          // rows per CTA
+constexpr int BKV = 128;         // keys per iteration
+constexpr int DH = 64;           // head size
+constexpr int THREADS = 192;
+constexpr int TILE_BYTES = 128 * 128;            // 128 rows x 64 bf16
+constexpr int TMEM_COLS = 256;                   // S: columns 0..127, O: columns 128..191
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try(bar, parity)) return true;
+  atomicExch(error, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
+// The same bits describe a K-major operand (rows = M or N, 64 elements of K per
+// row) and an MN-major operand (rows = K, 64 elements of N per row); which one
+// is meant is said in the instruction descriptor.
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// kind::f16: D float32, A and B bfloat16; b_mn: B is MN-major.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct AttnArgs {
+  __nv_bfloat16* out;            // [T, H * 64]
+  const int* table;              // [R, table_stride]
+  const int* req_q_start;        // [R + 1]
+  const int* req_pos0;           // [R]
+  int* error;
+  int table_stride, num_req, H, Hkv, page_size, window;
+  float scale;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const AttnArgs args) {
+  pdl_trigger();
+  pdl_wait();
+  // Which request and which of its 128-row tiles?
+  int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
+  for (int r = 0; r < args.num_req; ++r) {
+    const int len = args.req_q_start[r + 1] - args.req_q_start[r];
+    const int tiles = (len + BQ - 1) / BQ;
+    if (tile < tiles) { req = r; q0 = tile * BQ; q_len = len; break; }
+    tile -= tiles;
+  }
+  if (req < 0) return;
+  const int h = blockIdx.y, kvh = h / (args.H / args.Hkv);
+  const int rows = min(BQ, q_len - q0);
+  const int row0 = args.req_q_start[req] + q0;
+  const int pos0 = args.req_pos0[req] + q0;
+  const int last_pos = pos0 + rows - 1;
+  int k_begin = 0;
+  if (args.window > 0) k_begin = max(0, pos0 - args.window + 1) / BKV * BKV;
+  const int num_tiles = (last_pos - k_begin) / BKV + 1;
+  const int* my_table = args.table + (size_t)req * args.table_stride;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t q_tile = base;                                  // 16 KB
+  const uint32_t kv_tile = base + TILE_BYTES;                    // 2 x (K 16 KB + V 16 KB)
+  const uint32_t p_tile = kv_tile + 4 * TILE_BYTES;              // 2 x 16 KB (keys 0..63, 64..127)
+  const uint32_t bars = p_tile + 2 * TILE_BYTES;
+  const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = bars + 24, s_full = bars + 40,
+                 p_full = bars + 48, o_full = bars + 56, tmem_slot = bars + 64;
+  uint8_t* generic_base = smem_raw + (base - raw);
+  volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(generic_base + (tmem_slot - base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(kv_full0, 1); mbar_init(kv_full0 + 8, 1);
+    mbar_init(kv_empty0, 1); mbar_init(kv_empty0 + 8, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, TILE_BYTES);
+      tma_load_2d(q_tile, &map_q, h * DH, row0, q_full);
+      const int pages_per_tile = BKV / args.page_size;
+      const uint32_t page_bytes = (uint32_t)args.page_size * 128u;
+      bool ok = true;
+      int issued = 0;
+      for (int i = 0; i < num_tiles && ok; ++i) {
+        const int b = i & 1;
+        if (i >= 2) {
+          ok = mbar_wait(kv_empty0 + 8 * b, (uint32_t)((i >> 1) & 1) ^ 1u, args.error, 11);
+          if (!ok) break;
+        }
+        mbar_expect_tx(kv_full0 + 8 * b, 2 * TILE_BYTES);
+        const uint32_t k_dst = kv_tile + b * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
+        const int key0 = k_begin + i * BKV;
+        for (int p = 0; p < pages_per_tile; ++p) {
+          const int logical = key0 / args.page_size + p;
+          const int page = logical < args.table_stride ? my_table[logical] : 0;   // beyond the table: the padding page
+          tma_load_3d(k_dst + p * page_bytes, &map_k, 0, kvh, page * args.page_size, kv_full0 + 8 * b);
+          tma_load_3d(v_dst + p * page_bytes, &map_v, 0, kvh, page * args.page_size, kv_full0 + 8 * b);
+        }
+        issued = i + 1;
+      }
+      if (!ok) {
+        for (int i = max(0, issued - 2); i < issued; ++i)
+          mbar_wait(kv_full0 + 8 * (i & 1), (uint32_t)(i >> 1) & 1u, args.error, 12);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = make_idesc(BQ, BKV, 0);
+      constexpr uint32_t IDESC_O = make_idesc(BQ, DH, 1);
+      bool ok = mbar_wait(q_full, 0u, args.error, 13);
+      for (int i = 0; i < num_tiles && ok; ++i) {
+        const int b = i & 1;
+        ok = mbar_wait(kv_full0 + 8 * b, (uint32_t)(i >> 1) & 1u, args.error, 14);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t k_src = kv_tile + b * 2 * TILE_BYTES, v_src = k_src + TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k)           // S = Q K^T over the head dimension
+          umma(tmem_s, make_desc(q_tile + k * 32), make_desc(k_src + k * 32), IDESC_S, k > 0 ? 1u : 0u);
+        umma_commit(s_full);
+        ok = mbar_wait(p_full, (uint32_t)i & 1u, args.error, 15);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k)          // O_tile = P V over the keys
+          umma(tmem_o, make_desc(p_tile + (k >> 2) * TILE_BYTES + (k & 3) * 32), make_desc(v_src + k * 2048), IDESC_O,
+               k > 0 ? 1u : 0u);
+        umma_commit(o_full);
+        umma_commit(kv_empty0 + 8 * b);
+      }
+    }
+    __syncwarp();
+  } else {
+    // Softmax: thread = row of the tile = TMEM lane.
+    const int row = threadIdx.x;
+    const int qpos = pos0 + row;
+    const bool live = row < rows;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    float o_acc[DH];
+#pragma unroll
+    for (int d = 0; d < DH; ++d) o_acc[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    uint8_t* p_row = generic_base + (p_tile - base) + row * 128;
+    bool ok = true;
+    for (int i = 0; i < num_tiles && ok; ++i) {
+      ok = mbar_wait(s_full, (uint32_t)i & 1u, args.error, 16);
+      if (!ok) break;
+      tc_fence_after();
+      const int key0 = k_begin + i * BKV;
+      // The keys this row may see in this tile: key0 + j with lo <= j < hi.
+      int hi = live ? min(BKV, qpos - key0 + 1) : 0;
+      int lo = (args.window > 0) ? max(0, qpos - args.window + 1 - key0) : 0;
+      if (hi < 0) hi = 0;
+      // Pass 1 over the row of S in tensor memory: its maximum.
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_s + lane_addr + c, r);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c + j >= lo && c + j < hi) m_tile = fmaxf(m_tile, __uint_as_float(r[j]) * args.scale);
+      }
+      const float m_new = fmaxf(m_run, m_tile);
+      float alpha = 1.f, l_tile = 0.f;
+      if (m_new > -INFINITY) alpha = expf(m_run - m_new);
+      // Pass 2: exponentials, rounded to bfloat16, into the swizzled rows of P.
+#pragma unroll
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_s + lane_addr + c, r);
+#pragma unroll
+        for (int g = 0; g < 32; g += 8) {           // 8 keys = one 16-byte chunk of the row of P
+          uint32_t packed[4];
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            const int k0i = c + g + j;
+            const float p0 = (k0i >= lo && k0i < hi) ? expf(__uint_as_float(r[g + j]) * args.scale - m_new) : 0.f;
+            const float p1 = (k0i + 1 >= lo && k0i + 1 < hi) ? expf(__uint_as_float(r[g + j + 1]) * args.scale - m_new) : 0.f;
+            __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            // The sum must match what the MMA will multiply: the rounded values.
+            l_tile += __bfloat162float(pb.x) + __bfloat162float(pb.y);
+            packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+          }
+          const int chunk = (c + g) >> 3;           // 0..15: tile = chunk / 8, 16-byte column = chunk % 8
+          uint8_t* dst = p_row + (chunk >> 3) * TILE_BYTES + (((chunk & 7) ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+      }
+      l_run = l_run * alpha + l_tile;
+      m_run = m_new;
+#pragma unroll
+      for (int d = 0; d < DH; ++d) o_acc[d] *= alpha;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
+      tc_fence_before();
+      mbar_arrive(p_full);
+      ok = mbar_wait(o_full, (uint32_t)i & 1u, args.error, 17);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < DH; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_o + lane_addr + c, r);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o_acc[c + j] += __uint_as_float(r[j]);
+      }
+    }
+    if (live && ok) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* o = args.out + (size_t)(row0 + row) * ((size_t)args.H * DH) + h * DH;
+#pragma unroll
+      for (int d = 0; d < DH; d += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(o_acc[d + j] * inv, o_acc[d + j + 1] * inv);
+          w[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+        }
+        *reinterpret_cast<uint4*>(o + d) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------- host --
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+int* g_error_host = nullptr;
+int* g_error_dev = nullptr;
+std::mutex g_mutex;
+bool g_configured = false;
+
+struct CacheKey {
+  const void* ptr; int tokens, heads, page;
+  bool operator==(const CacheKey& o) const { return ptr == o.ptr && tokens == o.tokens && heads == o.heads && page == o.page; }
+};
+struct CacheHash {
+  size_t operator()(const CacheKey& k) const { return std::hash<const void*>()(k.ptr) ^ ((size_t)k.tokens * 31u) ^ ((size_t)k.heads << 20) ^ (size_t)k.page; }
+};
+std::unordered_map<CacheKey, CUtensorMap, CacheHash> g_cache_maps;
+
+constexpr size_t SMEM_BYTES = 1024 + 7 * TILE_BYTES + 128;
+
+int setup() {
+  if (g_encode && g_error_host && g_configured) return 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (err != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess)
+    return ayk_fail("ayk_attention_tc: cuTensorMapEncodeTiled is not available from this driver");
+  g_encode = (EncodeTiledFn)fn;
+  if (!g_error_host) {
+    err = cudaHostAlloc((void**)&g_error_host, sizeof(int), cudaHostAllocMapped);
+    if (err != cudaSuccess) return ayk_fail("ayk_attention_tc: cudaHostAlloc: %s", cudaGetErrorString(err));
+    *g_error_host = 0;
+    err = cudaHostGetDevicePointer((void**)&g_error_dev, g_error_host, 0);
+    if (err != cudaSuccess) return ayk_fail("ayk_attention_tc: cudaHostGetDevicePointer: %s", cudaGetErrorString(err));
+  }
+  err = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  if (err != cudaSuccess) return ayk_fail("ayk_attention_tc: shared memory %zu: %s", SMEM_BYTES, cudaGetErrorString(err));
+  g_configured = true;
+  return 0;
+}
+
+// The cache of one layer as a 3-D tensor [tokens = pages * page_size][kv heads][64]; box = one page of one head.
+int encode_cache(CUtensorMap* map, const void* ptr, int tokens, int heads, int page_size) {
+  cuuint64_t dims[3] = {(cuuint64_t)DH, (cuuint64_t)heads, (cuuint64_t)tokens};
+  cuuint64_t strides[2] = {(cuuint64_t)DH * 2, (cuuint64_t)heads * DH * 2};
+  cuuint32_t box[3] = {(cuuint32_t)DH, 1, (cuuint32_t)page_size};
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return ayk_fail("ayk_attention_tc: cuTensorMapEncodeTiled(cache) failed with %d", (int)r);
+  return 0;
+}
+
+int cache_map(CUtensorMap* map, const void* ptr, int tokens, int heads, int page_size) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  CacheKey key{ptr, tokens, heads, page_size};
+  auto it = g_cache_maps.find(key);
+  if (it != g_cache_maps.end()) { *map = it->second; return 0; }
+  if (encode_cache(map, ptr, tokens, heads, page_size) != 0) return -1;
+  g_cache_maps.emplace(key, *map);
+  return 0;
+}
+
+}  // namespace
+
+// 0 when the tensor-core kernel takes this geometry, else a text in ayk_last_error().
+AYK_EXPORT int ayk_attention_tc_supported(int Dh, int page_size, int q_stride) {
+  if (Dh != DH) return ayk_fail("ayk_attention_tc: head size %d (only 64)", Dh);
+  if (page_size < 8 || page_size > BKV || (page_size & (page_size - 1)))
+    return ayk_fail("ayk_attention_tc: page size %d is not a power of two in [8, 128]", page_size);
+  if (q_stride % 8 != 0) return ayk_fail("ayk_attention_tc: query rows of %d elements are not 16-byte aligned", q_stride);
+  return 0;
+}
+
+AYK_EXPORT int ayk_attention_tc_error() { return g_error_host ? *g_error_host : 0; }
+
+// out [T, H*64] bf16; q: rows of q_stride elements (head h at column h*64) of a
+// matrix with q_cols columns in total; caches [pages, page_size, Hkv, 64] bf16.
+AYK_EXPORT int ayk_attention_tc(void* out, const void* q, int q_stride, int total_rows, const void* kcache,
+                                const void* vcache, int pages, const int* table, int table_stride,
+                                const int* req_q_start, const int* req_pos0, int num_req, int H, int Hkv, int Dh,
+                                int page_size, float scale, int window, cudaStream_t stream) {
+  if (num_req == 0 || total_rows == 0) return 0;
+  if (ayk_attention_tc_supported(Dh, page_size, q_stride) != 0) return -1;
+  AYK_REQUIRE(Hkv >= 1 && H % Hkv == 0 && H <= 65535, "ayk_attention_tc: %d heads cannot share %d key/value heads", H, Hkv);
+  AYK_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0 && (uintptr_t)out % 16 == 0,
+              "ayk_attention_tc: operands must be 16-byte aligned");
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (setup() != 0) return -1;
+  }
+  CUtensorMap mq, mk, mv;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)H * DH, (cuuint64_t)total_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)q_stride * 2};
+    cuuint32_t box[2] = {(cuuint32_t)DH, (cuuint32_t)BQ};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = g_encode(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ayk_fail("ayk_attention_tc: cuTensorMapEncodeTiled(q) failed with %d", (int)r);
+  }
+  if (cache_map(&mk, kcache, pages * page_size, Hkv, page_size) != 0) return -1;
+  if (cache_map(&mv, vcache, pages * page_size, Hkv, page_size) != 0) return -1;
+  AttnArgs args{(__nv_bfloat16*)out, table, req_q_start, req_pos0, g_error_dev, table_stride, num_req, H, Hkv, page_size,
+                window, scale};
+  dim3 grid(total_rows / BQ + num_req, H);
+  ayk_launch(attention_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, args);
+  return ayk_check_launch("ayk_attention_tc");
+}

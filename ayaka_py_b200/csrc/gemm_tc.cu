@@ -136,13 +136,29 @@ struct EpilogueArgs {
   int kb_per_split;
 };
 
-__device__ __forceinline__ void store_out(const EpilogueArgs& a, int tok, int n, float v) {
-  if (a.bias) v += a.bias[n];
-  v = apply_activation(v, a.act);
-  size_t idx = (size_t)tok * a.N + n;
-  if (a.residual) v += a.residual[idx];
-  if (a.out_bf16) ((__nv_bfloat16*)a.C)[idx] = __float2bfloat16_rn(v);
-  else ((float*)a.C)[idx] = v;
+// Epilogue of CNT consecutive tokens of one out feature.  All loads come first,
+// arithmetic and stores after: the residual may alias C, so the compiler cannot
+// move the loads ahead of the stores itself, and one load at a time would leave
+// the epilogue waiting on memory latency CNT times over.
+template <int CNT>
+__device__ __forceinline__ void store_chunk(const EpilogueArgs& a, int tok0, int n, const float (&v)[CNT]) {
+  const float b = a.bias ? a.bias[n] : 0.f;
+  float res[CNT];
+#pragma unroll
+  for (int j = 0; j < CNT; ++j) {
+    const int tok = tok0 + j;
+    res[j] = (a.residual && tok < a.M) ? a.residual[(size_t)tok * a.N + n] : 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < CNT; ++j) {
+    const int tok = tok0 + j;
+    if (tok < a.M) {
+      const float y = apply_activation(v[j] + b, a.act) + res[j];
+      const size_t idx = (size_t)tok * a.N + n;
+      if (a.out_bf16) ((__nv_bfloat16*)a.C)[idx] = __float2bfloat16_rn(y);
+      else ((float*)a.C)[idx] = y;
+    }
+  }
 }
 
 template <int BT>
@@ -258,14 +274,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (int c = 0; c < BT; c += 16) {
         uint32_t r[16];
         tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
-        if (n < args.N) {
+        if (n < args.N && t0 + c < args.M) {
+          if (splits == 1) {
+            float v[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int tok = t0 + c + j;
-            if (tok >= args.M) break;
-            const float v = __uint_as_float(r[j]);
-            if (splits == 1) store_out(args, tok, n, v);
-            else args.partials[((size_t)blockIdx.z * args.M + tok) * args.N + n] = v;
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+            store_chunk<16>(args, t0 + c, n, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int tok = t0 + c + j;
+              if (tok < args.M) args.partials[((size_t)blockIdx.z * args.M + tok) * args.N + n] = __uint_as_float(r[j]);
+            }
           }
         }
       }
@@ -284,12 +304,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (*flag_ptr && ok) {
         __threadfence();
         if (n < args.N) {
-          for (int j = 0; j < BT; ++j) {
-            const int tok = t0 + j;
-            if (tok >= args.M) break;
-            float v = 0.f;
-            for (int z = 0; z < splits; ++z) v += __ldcg(&args.partials[((size_t)z * args.M + tok) * args.N + n]);
-            store_out(args, tok, n, v);
+          for (int c = 0; c < BT && t0 + c < args.M; c += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = 0.f;
+            for (int z = 0; z < splits; ++z) {          // split order: the sum does not depend on arrival order
+              float p[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const int tok = t0 + c + u;
+                p[u] = tok < args.M ? __ldcg(&args.partials[((size_t)z * args.M + tok) * args.N + n]) : 0.f;
+              }
+#pragma unroll
+              for (int u = 0; u < 8; ++u) v[u] += p[u];
+            }
+            store_chunk<8>(args, t0 + c, n, v);
           }
         }
       }

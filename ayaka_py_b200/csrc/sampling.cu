@@ -56,9 +56,19 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
 
 __device__ MaxIdx block_argmax(const float* row, int V, MaxIdx* red) {
   MaxIdx best = {-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = row[i];
-    if (v > best.v) { best.v = v; best.i = i; }   // ascending i: the first maximum stays
+  // Eight independent loads in flight per thread; compared in ascending index
+  // order, so that the first maximum stays.
+  for (int base = threadIdx.x; base < V; base += blockDim.x * 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * blockDim.x;
+      v[u] = i < V ? row[i] : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (v[u] > best.v) { best.v = v[u]; best.i = base + u * blockDim.x; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

@@ -288,11 +288,6 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return out
 
 
-def tc_error() -> int:
-    """0, or the code of the bounded wait that ran out in a tensor-core kernel."""
-    return int(library().ayk_gemm_tc_error())
-
-
 def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            activation: str = "none", residual: torch.Tensor | None = None,
            out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -339,13 +334,55 @@ def attention_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor
     return out
 
 
+def attention_tc_takes(q: torch.Tensor, kcache: torch.Tensor) -> bool:
+    """Whether the tensor-core attention kernel takes this geometry: bfloat16,
+    head size 64, pages of 8 to 128 tokens, 16-byte aligned query rows."""
+    pages, P, Hkv, Dh = kcache.shape
+    return (q.dtype == torch.bfloat16 and Dh == 64 and 8 <= P <= 128 and P & (P - 1) == 0
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def attention_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, table: torch.Tensor,
+                 req_q_start: torch.Tensor, req_pos0: torch.Tensor, total_rows: int, num_heads: int,
+                 scale: float, window: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of prompt portions over the paged cache on tcgen05 (bfloat16, head size 64)."""
+    lib = _ready()
+    pages, P, Hkv, Dh = kcache.shape
+    T = q.shape[0]
+    if q.shape[1] != num_heads * Dh or q.stride(1) != 1 or q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
+        raise KernelError("attention_tc: q must be a bfloat16 [T, heads*head_dim] slice, the cache bfloat16")
+    if not kcache.is_contiguous() or not vcache.is_contiguous():
+        raise KernelError("attention_tc: the cache must be contiguous")
+    if out is None:
+        out = torch.empty((T, num_heads * Dh), dtype=q.dtype, device=q.device)
+    R = req_pos0.numel()
+    _launch(lib.ayk_attention_tc(_ptr(out), _ptr(q), ctypes.c_int(q.stride(0)), ctypes.c_int(total_rows),
+                                 _ptr(kcache), _ptr(vcache), ctypes.c_int(pages), _ptr(_i32(table, "table")),
+                                 ctypes.c_int(table.stride(0)), _ptr(_i32(req_q_start, "req_q_start")),
+                                 _ptr(_i32(req_pos0, "req_pos0")), ctypes.c_int(R), ctypes.c_int(num_heads),
+                                 ctypes.c_int(Hkv), ctypes.c_int(Dh), ctypes.c_int(P), ctypes.c_float(scale),
+                                 ctypes.c_int(window or 0), _stream()))
+    return out
+
+
+def tc_error() -> int:
+    """0, or the code of the bounded wait that ran out in a tensor-core kernel
+    (1-4: matrix product, 11-17: attention)."""
+    lib = library()
+    return int(lib.ayk_gemm_tc_error()) or int(lib.ayk_attention_tc_error())
+
+
 def attention(q, kcache, vcache, table, ctx, num_heads: int, scale: float,
               window: int | None = None) -> torch.Tensor:
     """Attention of the step's rows (``ctx`` gives the rows of each request): the
-    split-context decode kernels when every request brings one row, else the
-    general kernel."""
+    split-context decode kernels when every request brings one row; the
+    tensor-core kernel for prompt portions in bfloat16 with head size 64; else
+    the general kernel."""
     if ctx.max_q_len == 1:
         return attention_decode(q, kcache, vcache, table, ctx.req_pos0, num_heads, scale, window,
                                 ctx.cache.max_len)
+    if attention_tc_takes(q, kcache):
+        return attention_tc(q, kcache, vcache, table, ctx.req_q_start, ctx.req_pos0, ctx.num_rows,
+                            num_heads, scale, window)
     return attention_simt(q, kcache, vcache, table, ctx.req_q_start, ctx.req_pos0, ctx.num_rows,
                           num_heads, scale, window)

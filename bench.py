@@ -209,6 +209,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-graph", action="store_true", help="run decode steps eagerly")
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 and the prefill")
+    parser.add_argument("--prefill-only", action="store_true",
+                        help="run only the 2,048-token prefill step and print its numbers (for profiling)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -229,6 +231,12 @@ def main() -> int:
     graph = not args.no_graph
     sizes = [args.batch] if args.no_points else sorted({1, args.batch, 64})
     config, model, engine = build_engine(args.layers, max(sizes), graph)
+    if args.prefill_only:
+        p = run_prefill(engine, config, repeats=max(1, args.steps))
+        print(json.dumps({"prefill": {"value": round(p["tokens"] / (p["ms"] / 1e3), 1), "tokens": p["tokens"],
+                                      "ms": round(p["ms"], 3), "n_layer": args.layers,
+                                      "frac": round(p["flops"] / (p["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}}))
+        return 0
     sampler = ClockSampler()
     sampler.start()
     main_run = run_decode(engine, config, args.batch, args.steps, args.warmup)

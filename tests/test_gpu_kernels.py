@@ -313,3 +313,43 @@ def test_decode_attention_far_key_at_a_partition_edge(kpos):
     want = plain(1.0, None)
     assert np.abs(want[0] - plain(0.0, None)[0]).max() > 0.5
     assert np.abs(out - want).max() < tol("bfloat16")
+
+
+TC_ATTENTION_CASES = [
+    # lens_q, lens_ctx, H, Hkv, P, window
+    ([5, 1, 40], [0, 17, 3], 2, 2, 16, None),
+    ([128, 129, 1], [0, 0, 300], 3, 3, 16, None),
+    ([300], [0], 2, 1, 8, None),
+    ([70, 200], [250, 57], 4, 2, 64, None),
+    ([33, 260], [100, 0], 2, 2, 128, None),
+    ([150, 9], [140, 300], 2, 2, 16, 100),
+]
+
+
+@pytest.mark.parametrize("case", TC_ATTENTION_CASES)
+def test_attention_tcgen05(case):
+    from ayaka_py_b200 import ops
+    lens_q, lens_ctx, H, Hkv, P, window = case
+    rs = np.random.RandomState(10)
+    x, plain = paged_case(rs, lens_q, lens_ctx, H, Hkv, 64, P, "bfloat16")
+    scale = 0.9 / 8.0
+    ops.kv_append(x["kc"], x["vc"], x["k"], x["v"], x["row_req"], x["pos"], x["table"])
+    assert ops.attention_tc_takes(x["q"], x["kc"])
+    out = ops.attention_tc(x["q"], x["kc"], x["vc"], x["table"], x["q_start"], x["pos0"], sum(lens_q), H, scale, window)
+    torch.cuda.synchronize()
+    assert ops.tc_error() == 0
+    assert np.abs(out.float().cpu().numpy() - plain(scale, window)).max() < tol("bfloat16")
+
+
+@pytest.mark.parametrize("qpos,kpos", [(299, 0), (299, 127), (299, 128), (255, 15), (256, 16), (130, 129)])
+def test_attention_tcgen05_far_key_stands_out(qpos, kpos):
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(11)
+    x, plain = paged_case(rs, [300, 2], [0, 20], 2, 2, 64, 16, "bfloat16", sharp=(0, qpos, kpos))
+    ops.kv_append(x["kc"], x["vc"], x["k"], x["v"], x["row_req"], x["pos"], x["table"])
+    out = ops.attention_tc(x["q"], x["kc"], x["vc"], x["table"], x["q_start"], x["pos0"], 302, 2, 1.0).float().cpu().numpy()
+    torch.cuda.synchronize()
+    assert ops.tc_error() == 0
+    want = plain(1.0, None)
+    assert np.abs(want[qpos] - plain(0.0, None)[qpos]).max() > 0.5
+    assert np.abs(out - want).max() < tol("bfloat16")

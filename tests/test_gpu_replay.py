@@ -16,8 +16,8 @@ import trace_tools
 pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
-LENGTHS = {"A": [5, 17, 40, 75, 128], "B": [1, 9, 33, 64, 120, 201], "C": [37, 90]}
-PAGE = {"A": 16, "B": 8, "C": 16}
+LENGTHS = {"A": [5, 17, 40, 75, 128], "B": [1, 9, 33, 64, 120, 201], "C": [37, 90], "D": [3, 130, 260, 77, 401]}
+PAGE = {"A": 16, "B": 8, "C": 16, "D": 16}
 
 
 def tolerance(dtype, want):
@@ -65,25 +65,25 @@ def check(tag, dtype, trace, model_folders, oracles, **kw):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B"])
+@pytest.mark.parametrize("tag", ["A", "B", "D"])
 def test_each_request_alone_and_whole(tag, dtype, model_folders, oracles):
     check(tag, dtype, trace_tools.whole(oracles[tag][0]), model_folders, oracles)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B"])
+@pytest.mark.parametrize("tag", ["A", "B", "D"])
 def test_last_32_tokens_one_by_one(tag, dtype, model_folders, oracles):
     check(tag, dtype, trace_tools.tail_decoded(oracles[tag][0], 32), model_folders, oracles)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B"])
+@pytest.mark.parametrize("tag", ["A", "B", "D"])
 def test_portions_of_changing_size(tag, dtype, model_folders, oracles):
     check(tag, dtype, trace_tools.portions(oracles[tag][0]), model_folders, oracles)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B"])
+@pytest.mark.parametrize("tag", ["A", "B", "D"])
 def test_mixed_with_pages_used_again(tag, dtype, model_folders, oracles):
     for seed in (0, 1):
         trace = trace_tools.mixed(oracles[tag][0], seed=seed)

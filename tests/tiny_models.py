@@ -41,6 +41,16 @@ TINY_C = {
 }
 
 
+# Head size 64 (the tensor-core attention kernel's), three heads, width 192.
+TINY_D = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 2, "n_embd": 192, "n_head": 3, "n_inner": 264, "vocab_size": 300,
+    "n_positions": 512, "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new",
+    "scale_attn_weights": True, "scale_attn_by_inverse_layer_idx": True,
+    "tie_word_embeddings": True,
+}
+
+
 def tensor_shapes(cfg: dict) -> dict[str, tuple]:
     d, L, V = cfg["n_embd"], cfg["n_layer"], cfg["vocab_size"]
     inner = cfg.get("n_inner") or 4 * d

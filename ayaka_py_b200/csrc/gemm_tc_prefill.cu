@@ -1,0 +1,411 @@
+// bfloat16 matrix product for many rows (prompt portions) on tcgen05: persistent
+// CTAs, two accumulators in tensor memory so that the epilogue of one tile runs
+// under the main loop of the next.
+//
+//   C[M, N] = act(X[M, K] * W[N, K]^T + bias[N]) (+ residual[M, N])
+//
+// A tile is 128 rows of X (the MMA's M side, one row per TMEM lane) by BN out
+// features (its N side, BN = 64 ... 256 in steps of 32, chosen by the host so
+// that the tiles fill whole waves of the 148 SMs).  Operands come by TMA in
+// 64-element K blocks with the 128-byte swizzle through a ring of stages.
+// Warp 0: TMA producer; warp 1: MMA issue and TMEM allocation; warps 2..9:
+// epilogue, two warps per TMEM lane quarter, each taking half of the tile's
+// columns.  An epilogue thread owns one row: it reads 32 accumulator columns
+// with tcgen05.ld, adds the bias, applies the activation in 32-bit, adds the
+// 32-bit residual (all loads of a chunk issued before its stores: the residual
+// may alias C) and stores 128 contiguous bytes.
+//
+// Every mbarrier wait is bounded; a wait that runs out records a code (21..26)
+// in the error word of the tensor-core kernels and the CTA winds down.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BLOCK_K = 64;
+constexpr int A_BYTES = BM * BLOCK_K * 2;
+constexpr int THREADS = 320;
+constexpr int EPI_WARPS = 8;
+constexpr int MAX_STAGES = 8;
+constexpr int SMEM_TILES = 196608;             // bytes available to the stage ring
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try(bar, parity)) return true;
+  atomicExch(error, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr) {     // K-major, 128-byte swizzle, sm_100 version
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+struct PrefillArgs {
+  void* C;
+  const float* bias;
+  const float* residual;
+  int* error;
+  int M, N, K;
+  int act, out_bf16;
+  int BN, stages, m_tiles, n_tiles;
+};
+
+// One row, W consecutive columns (W = 16 or 32) starting at column n.
+template <int W>
+__device__ __forceinline__ void epilogue_chunk(const PrefillArgs& a, uint32_t taddr, int row, int n, bool row_ok) {
+  uint32_t r[W];
+  tmem_ld16(taddr, r);
+  if (W == 32) tmem_ld16(taddr + 16, r + 16);
+  float res[W];
+  const bool full = row_ok && n + W <= a.N && (a.N & 7) == 0;    // 16-byte aligned row segments
+  const size_t idx = (size_t)row * a.N + n;
+  if (a.residual && full) {
+#pragma unroll
+    for (int j = 0; j < W; j += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(a.residual + idx + j);
+      res[j] = v.x; res[j + 1] = v.y; res[j + 2] = v.z; res[j + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < W; ++j) res[j] = (a.residual && row_ok && n + j < a.N) ? a.residual[idx + j] : 0.f;
+  }
+  tmem_ld_wait();
+  float y[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    const float b = (a.bias && n + j < a.N) ? __ldg(a.bias + n + j) : 0.f;
+    y[j] = apply_activation(__uint_as_float(r[j]) + b, a.act) + res[j];
+  }
+  if (!row_ok) return;
+  if (full) {
+    if (a.out_bf16) {
+      __nv_bfloat16* dst = (__nv_bfloat16*)a.C + idx;
+#pragma unroll
+      for (int j = 0; j < W; j += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int u = 0; u < 8; u += 2) {
+          __nv_bfloat162 p = __floats2bfloat162_rn(y[j + u], y[j + u + 1]);
+          w[u >> 1] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+      float* dst = (float*)a.C + idx;
+#pragma unroll
+      for (int j = 0; j < W; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      if (n + j < a.N) {
+        if (a.out_bf16) ((__nv_bfloat16*)a.C)[idx + j] = __float2bfloat16_rn(y[j]);
+        else ((float*)a.C)[idx + j] = y[j];
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                       const PrefillArgs args) {
+  const int BN = args.BN, STAGES = args.stages;
+  const uint32_t B_BYTES = (uint32_t)BN * BLOCK_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  const uint32_t bars = tiles + SMEM_TILES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
+  auto tmem_full = [&](int b) { return bars + 8u * (2 * MAX_STAGES + b); };
+  auto tmem_empty = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * MAX_STAGES + 4);
+  volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = args.m_tiles * args.n_tiles;
+  const int num_kb = (args.K + BLOCK_K - 1) / BLOCK_K;
+  const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < MAX_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tmem_full(b), 1); mbar_init(tmem_empty(b), EPI_WARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_trigger();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // Iteration `it` over all of this CTA's tiles: tile it / num_kb, K block it % num_kb.
+      const int total_it = my_tiles * num_kb;
+      auto load = [&](int it, bool weight) {
+        const int tile = blockIdx.x + (it / num_kb) * gridDim.x, kx = (it % num_kb) * BLOCK_K;
+        const uint32_t dst = tiles + (it % STAGES) * STAGE_BYTES;
+        if (weight) tma_load_2d(dst + A_BYTES, &map_w, kx, (tile % args.n_tiles) * BN, full_bar(it % STAGES));
+        else tma_load_2d(dst, &map_x, kx, (tile / args.n_tiles) * BM, full_bar(it % STAGES));
+      };
+      // The weight does not depend on the kernels before this one: its first
+      // stages start streaming at once; the rows X wait for the predecessor.
+      const int pre = min(STAGES, total_it);
+      for (int it = 0; it < pre; ++it) {
+        mbar_expect_tx(full_bar(it), STAGE_BYTES);
+        load(it, true);
+      }
+      pdl_wait();
+      for (int it = 0; it < pre; ++it) load(it, false);
+      bool ok = true;
+      int issued = pre;
+      for (int it = pre; it < total_it; ++it) {
+        const int s = it % STAGES;
+        ok = mbar_wait(empty_bar(s), (uint32_t)((it / STAGES) & 1) ^ 1u, args.error, 21);
+        if (!ok) break;
+        mbar_expect_tx(full_bar(s), STAGE_BYTES);
+        load(it, true);
+        load(it, false);
+        issued = it + 1;
+      }
+      if (!ok) {
+        for (int j = max(0, issued - STAGES); j < issued; ++j)
+          mbar_wait(full_bar(j % STAGES), (uint32_t)(j / STAGES) & 1u, args.error, 22);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      int it = 0;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        const int b = t & 1;
+        if (t >= 2) {
+          ok = mbar_wait(tmem_empty(b), (uint32_t)((t >> 1) & 1) ^ 1u, args.error, 23);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        const uint32_t acc = tmem_base + (uint32_t)b * 256u;
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(full_bar(s), (uint32_t)(it / STAGES) & 1u, args.error, 24);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_src = tiles + s * STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / 16; ++k)
+            umma(acc, make_desc(a_src + k * 32), make_desc(a_src + A_BYTES + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty_bar(s));
+        }
+        umma_commit(tmem_full(b));
+      }
+    }
+    __syncwarp();
+  } else {
+    pdl_wait();            // residual and C belong to earlier kernels until here
+    const int e = warp - 2;
+    const int quarter = warp & 3, half = e >> 2;
+    const int half_cols = BN >> 1;
+    bool ok = true;
+    for (int t = 0; t < my_tiles && ok; ++t) {
+      const int b = t & 1;
+      const int tile = blockIdx.x + t * gridDim.x;
+      const int m0 = (tile / args.n_tiles) * BM, n0 = (tile % args.n_tiles) * BN;
+      ok = mbar_wait(tmem_full(b), (uint32_t)(t >> 1) & 1u, args.error, 25);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < args.M;
+      const uint32_t taddr = tmem_base + (uint32_t)b * 256u + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
+      int c = 0;
+      for (; c + 32 <= half_cols; c += 32) epilogue_chunk<32>(args, taddr + c, row, n0 + half * half_cols + c, row_ok);
+      if (c < half_cols) epilogue_chunk<16>(args, taddr + c, row, n0 + half * half_cols + c, row_ok);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty(b));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------- host --
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+int* g_error_host = nullptr;
+int* g_error_dev = nullptr;
+bool g_configured = false;
+std::mutex g_mutex;
+constexpr size_t SMEM_BYTES = 1024 + SMEM_TILES + 8 * (2 * MAX_STAGES + 5);
+
+struct MapKey {
+  const void* ptr; int rows, k, box;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box == o.box; }
+};
+struct MapHash {
+  size_t operator()(const MapKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows * 1000003u ^ (size_t)k.k * 10007u ^ (size_t)k.box; }
+};
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_weight_maps;
+
+int setup() {
+  if (g_configured) return 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (err != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess)
+    return ayk_fail("ayk_gemm_tc_prefill: cuTensorMapEncodeTiled is not available from this driver");
+  g_encode = (EncodeTiledFn)fn;
+  err = cudaHostAlloc((void**)&g_error_host, sizeof(int), cudaHostAllocMapped);
+  if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc_prefill: cudaHostAlloc: %s", cudaGetErrorString(err));
+  *g_error_host = 0;
+  err = cudaHostGetDevicePointer((void**)&g_error_dev, g_error_host, 0);
+  if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc_prefill: cudaHostGetDevicePointer: %s", cudaGetErrorString(err));
+  err = cudaFuncSetAttribute(gemm_tc_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc_prefill: shared memory %zu: %s", SMEM_BYTES, cudaGetErrorString(err));
+  g_configured = true;
+  return 0;
+}
+
+int encode(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return ayk_fail("ayk_gemm_tc_prefill: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+}  // namespace
+
+AYK_EXPORT int ayk_gemm_tc_prefill_error() { return g_error_host ? *g_error_host : 0; }
+
+// The tile width (out features per tile) that fills whole waves of `sms` SMs best.
+AYK_EXPORT int ayk_gemm_tc_prefill_tile(int M, int N, int sms) {
+  int best = 256;
+  long best_cost = -1;
+  const int m_tiles = (M + BM - 1) / BM;
+  for (int bn = 64; bn <= 256; bn += 32) {
+    const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
+    const long waves = (tiles + sms - 1) / sms;
+    const long cost = waves * (bn + 24);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+// X [M, K], W [N, K] bfloat16, contiguous, 16-byte aligned, K a multiple of 8; C [M, N]
+// float32 or bfloat16 with N a multiple of 8 (16-byte row segments); bias, residual
+// float32 or null (residual may alias a float32 C).  tile_n: 0 lets the library choose.
+AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const float* bias, const float* residual,
+                                   int M, int N, int K, int act, int out_dtype, int tile_n, int sms,
+                                   cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  AYK_REQUIRE(K >= 8 && K % 8 == 0, "ayk_gemm_tc_prefill: K = %d must be a positive multiple of 8", K);
+  AYK_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)C % 16 == 0) &&
+              (residual == nullptr || (uintptr_t)residual % 16 == 0), "ayk_gemm_tc_prefill: operands must be 16-byte aligned");
+  AYK_REQUIRE(out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16, "ayk_gemm_tc_prefill: unknown output dtype %d", out_dtype);
+  AYK_REQUIRE(sms >= 1, "ayk_gemm_tc_prefill: sms must be positive");
+  int BN = tile_n > 0 ? tile_n : ayk_gemm_tc_prefill_tile(M, N, sms);
+  AYK_REQUIRE(BN >= 64 && BN <= 256 && BN % 32 == 0, "ayk_gemm_tc_prefill: tile width %d is not a multiple of 32 in [64, 256]", BN);
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (setup() != 0) return -1;
+  }
+  CUtensorMap mx, mw;
+  if (encode(&mx, X, M, K, BM) != 0) return -1;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    MapKey key{W, N, K, BN};
+    auto it = g_weight_maps.find(key);
+    if (it == g_weight_maps.end()) {
+      if (encode(&mw, W, N, K, BN) != 0) return -1;
+      g_weight_maps.emplace(key, mw);
+    } else {
+      mw = it->second;
+    }
+  }
+  PrefillArgs args{};
+  args.C = C; args.bias = bias; args.residual = residual; args.error = g_error_dev;
+  args.M = M; args.N = N; args.K = K; args.act = act; args.out_bf16 = out_dtype == AYK_DTYPE_BF16;
+  args.BN = BN;
+  args.m_tiles = (M + BM - 1) / BM;
+  args.n_tiles = (N + BN - 1) / BN;
+  int stages = SMEM_TILES / (A_BYTES + BN * BLOCK_K * 2);
+  args.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
+  // Rows whose 16-byte segments are not aligned take the scalar path of the epilogue; N % 8 keeps them aligned.
+  const int total = args.m_tiles * args.n_tiles;
+  dim3 grid(total < sms ? total : sms);
+  ayk_launch(gemm_tc_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mx, mw, args);
+  return ayk_check_launch("ayk_gemm_tc_prefill");
+}

@@ -288,6 +288,36 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return out
 
 
+PREFILL_ROWS = 128       # more rows than this: the persistent many-row kernel
+
+
+def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+                    activation: str = "none", residual: torch.Tensor | None = None,
+                    out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
+                    tile_n: int = 0) -> torch.Tensor:
+    """act(a[M,K] @ w[N,K]^T + bias) (+ residual) for many rows: persistent tcgen05
+    kernel, epilogue of a tile under the main loop of the next."""
+    lib = _ready()
+    M, K = a.shape
+    N = w.shape[0]
+    if (w.shape[1] != K or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
+            or not a.is_contiguous() or not w.is_contiguous()):
+        raise KernelError(f"gemm_tc_prefill operands do not fit: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}")
+    out_dtype = out_dtype or a.dtype
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    for name, t in (("bias", bias), ("residual", residual)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError(f"{name} must be contiguous float32")
+    if residual is not None and tuple(residual.shape) != (M, N):
+        raise KernelError("residual must have the output's shape")
+    _launch(lib.ayk_gemm_tc_prefill(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
+                                    ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]),
+                                    ctypes.c_int(_tag(out_dtype)), ctypes.c_int(tile_n), ctypes.c_int(SM_COUNT),
+                                    _stream()))
+    return out
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            activation: str = "none", residual: torch.Tensor | None = None,
            out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -295,6 +325,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     pipes (true 32-bit); bfloat16 operands on the tensor cores (tcgen05) when
     K is a multiple of 8, else on the FP32 pipes with 32-bit accumulation."""
     if a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[0] > 0:
+        if a.shape[0] > PREFILL_ROWS:
+            return gemm_tc_prefill(a, w, bias, activation, residual, out_dtype, out)
         return gemm_tc(a, w, bias, activation, residual, out_dtype, out)
     return gemm_simt(a, w, bias, activation, residual, out_dtype, out)
 
@@ -369,7 +401,8 @@ def tc_error() -> int:
     """0, or the code of the bounded wait that ran out in a tensor-core kernel
     (1-4: matrix product, 11-17: attention)."""
     lib = library()
-    return int(lib.ayk_gemm_tc_error()) or int(lib.ayk_attention_tc_error())
+    return (int(lib.ayk_gemm_tc_error()) or int(lib.ayk_attention_tc_error())
+            or int(lib.ayk_gemm_tc_prefill_error()))
 
 
 def attention(q, kcache, vcache, table, ctx, num_heads: int, scale: float,

@@ -353,3 +353,35 @@ def test_attention_tcgen05_far_key_stands_out(qpos, kpos):
     want = plain(1.0, None)
     assert np.abs(want[qpos] - plain(0.0, None)[qpos]).max() > 0.5
     assert np.abs(out - want).max() < tol("bfloat16")
+
+
+PREFILL_GEMM_CASES = [
+    # M, N, K, tile_n (0: chosen by the library)
+    (129, 64, 64, 0), (300, 200, 1600, 0), (2048, 1600, 1600, 0), (2048, 4800, 1600, 192), (1000, 1003, 328, 96),
+    (513, 6400, 256, 256), (640, 1600, 6400, 128), (257, 330, 72, 160), (4096, 264, 192, 64), (150, 1000, 1000, 224),
+]
+
+
+@pytest.mark.parametrize("M,N,K,tile_n", PREFILL_GEMM_CASES)
+@pytest.mark.parametrize("act,out_dtype", [("none", "float32"), ("gelu_tanh", "bfloat16")])
+def test_gemm_tcgen05_many_rows(M, N, K, tile_n, act, out_dtype):
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(12)
+    a, w = rs.randn(M, K).astype(np.float32), (rs.randn(N, K) / np.sqrt(K)).astype(np.float32)
+    bias, res = rs.randn(N).astype(np.float32), rs.randn(M, N).astype(np.float32)
+    A, W = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    y = (A.float() @ W.float().t()).double().cpu().numpy() + bias            # float32 products are exact for bf16 operands
+    if act != "none":
+        y = plain_gpt2.activation("gelu_new", y)
+    want = y + res
+    R = dev(res)
+    out = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=DTYPES[out_dtype], tile_n=tile_n)
+    torch.cuda.synchronize()
+    assert ops.tc_error() == 0
+    err = np.abs(out.float().cpu().numpy() - want).max()
+    assert err < (1e-3 if out_dtype == "float32" else 5e-2), err
+    if out_dtype == "float32":
+        again = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=torch.float32, out=R, tile_n=tile_n)   # in place
+        assert torch.equal(again, out) and ops.tc_error() == 0
+        few = ops.gemm_tc(A[:64].contiguous(), W, dev(bias), act, dev(res[:64]), out_dtype=torch.float32, splits=1)
+        assert float((few - out[:64]).abs().max()) < 1e-4                     # the few-row kernel agrees

@@ -109,6 +109,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct AttnArgs {
   __nv_bfloat16* out;            // [T, H * 64]
   const int* table;              // [R, table_stride]
@@ -119,7 +125,7 @@ struct AttnArgs {
   float scale;
 };
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const AttnArgs args) {
   pdl_trigger();
@@ -129,7 +135,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   for (int r = 0; r < args.num_req; ++r) {
     const int len = args.req_q_start[r + 1] - args.req_q_start[r];
     const int tiles = (len + BQ - 1) / BQ;
-    if (tile < tiles) { req = r; q0 = tile * BQ; q_len = len; break; }
+    // Late tiles of a request see the most keys: they are handed out first.
+    if (tile < tiles) { req = r; q0 = (tiles - 1 - tile) * BQ; q_len = len; break; }
     tile -= tiles;
   }
   if (req < 0) return;
@@ -143,9 +150,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int num_tiles = (last_pos - k_begin) / BKV + 1;
   const int* my_table = args.table + (size_t)req * args.table_stride;
 
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
+  if (raw & 1023u) {                 // the swizzled tiles need 1024-byte alignment; no slack is reserved for it
+    if (threadIdx.x == 0) atomicExch(args.error, 18);
+    return;
+  }
+  const uint32_t base = raw;
   const uint32_t q_tile = base;                                  // 16 KB
   const uint32_t kv_tile = base + TILE_BYTES;                    // 2 x (K 16 KB + V 16 KB)
   const uint32_t p_tile = kv_tile + 4 * TILE_BYTES;              // 2 x 16 KB (keys 0..63, 64..127)
@@ -243,7 +254,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     float o_acc[DH];
 #pragma unroll
     for (int d = 0; d < DH; ++d) o_acc[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;          // the maximum is kept in units of log2(e)
+    const float scale_log2 = args.scale * 1.4426950408889634f;
     uint8_t* p_row = generic_base + (p_tile - base) + row * 128;
     bool ok = true;
     for (int i = 0; i < num_tiles && ok; ++i) {
@@ -255,19 +267,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       int hi = live ? min(BKV, qpos - key0 + 1) : 0;
       int lo = (args.window > 0) ? max(0, qpos - args.window + 1 - key0) : 0;
       if (hi < 0) hi = 0;
+      const bool unmasked = lo <= 0 && hi >= BKV;  // every key of the tile is visible to this row
+      // Scores are kept times log2(e), so that exp(s - m) is one ex2 each
+      // (32-bit; the result is rounded to bfloat16 for the second product anyway).
       // Pass 1 over the row of S in tensor memory: its maximum.
       float m_tile = -INFINITY;
 #pragma unroll
       for (int c = 0; c < BKV; c += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_s + lane_addr + c, r);
+        if (unmasked) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (c + j >= lo && c + j < hi) m_tile = fmaxf(m_tile, __uint_as_float(r[j]) * args.scale);
+          for (int j = 0; j < 32; ++j) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c + j >= lo && c + j < hi) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
+        }
       }
+      m_tile *= scale_log2;                        // the scale is positive: the maximum commutes with it
       const float m_new = fmaxf(m_run, m_tile);
       float alpha = 1.f, l_tile = 0.f;
-      if (m_new > -INFINITY) alpha = expf(m_run - m_new);
+      if (m_new > -INFINITY) alpha = fast_exp2(m_run - m_new);
       // Pass 2: exponentials, rounded to bfloat16, into the swizzled rows of P.
 #pragma unroll
       for (int c = 0; c < BKV; c += 32) {
@@ -279,8 +300,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 8; j += 2) {
             const int k0i = c + g + j;
-            const float p0 = (k0i >= lo && k0i < hi) ? expf(__uint_as_float(r[g + j]) * args.scale - m_new) : 0.f;
-            const float p1 = (k0i + 1 >= lo && k0i + 1 < hi) ? expf(__uint_as_float(r[g + j + 1]) * args.scale - m_new) : 0.f;
+            float p0 = fast_exp2(fmaf(__uint_as_float(r[g + j]), scale_log2, -m_new));
+            float p1 = fast_exp2(fmaf(__uint_as_float(r[g + j + 1]), scale_log2, -m_new));
+            if (!unmasked) {
+              if (!(k0i >= lo && k0i < hi)) p0 = 0.f;
+              if (!(k0i + 1 >= lo && k0i + 1 < hi)) p1 = 0.f;
+            }
             __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
             // The sum must match what the MMA will multiply: the rounded values.
             l_tile += __bfloat162float(pb.x) + __bfloat162float(pb.y);
@@ -352,7 +377,7 @@ struct CacheHash {
 };
 std::unordered_map<CacheKey, CUtensorMap, CacheHash> g_cache_maps;
 
-constexpr size_t SMEM_BYTES = 1024 + 7 * TILE_BYTES + 128;
+constexpr size_t SMEM_BYTES = 7 * TILE_BYTES + 128;      // two CTAs fit one SM
 
 int setup() {
   if (g_encode && g_error_host && g_configured) return 0;

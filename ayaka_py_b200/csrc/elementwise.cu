@@ -7,6 +7,7 @@
 // KV scatter kernel/triton/cache/paged_kv.py:141-214.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -121,6 +122,66 @@ __global__ void layernorm_kernel(O* __restrict__ out, const float* __restrict__ 
   }
 }
 
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 w;
+  w.x = *reinterpret_cast<uint32_t*>(&lo);
+  w.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = w;
+}
+
+// One warp per row, the row held in registers (width a multiple of 4, at most
+// 128 * MAXV): one pass over memory, no shared memory, no block barrier.  Same
+// arithmetic: mean, then the mean of squared deviations, in 32-bit.
+template <typename O, int MAXV>
+__global__ void __launch_bounds__(256)
+layernorm_warp_kernel(O* __restrict__ out, const float* __restrict__ x, const float* __restrict__ gamma,
+                      const float* __restrict__ beta, const int* __restrict__ rows, int n_rows, int d, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + warp;
+  if (r >= n_rows) return;
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
+  const int nv = d >> 2;
+  float4 v[MAXV];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int idx = lane + 32 * i;
+    if (idx < nv) {
+      v[i] = src[idx];
+      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  const float mean = warp_sum(s) / (float)d;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    if (lane + 32 * i < nv) {
+      const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, e = v[i].w - mean;
+      q += (a * a + b * b) + (c * c + e * e);
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / (float)d + eps);
+  const float4* g4 = reinterpret_cast<const float4*>(gamma);
+  const float4* b4 = reinterpret_cast<const float4*>(beta);
+  O* dst = out + (size_t)r * d;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int idx = lane + 32 * i;
+    if (idx < nv) {
+      const float4 g = g4[idx];
+      const float4 b = beta ? b4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+      store4(dst + 4 * idx, (v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y,
+             (v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
+    }
+  }
+}
+
 // out[r, :] = LayerNorm(x[rows ? rows[r] : r, :]); x float32, statistics and
 // affine in 32-bit, result stored as out_dtype.
 AYK_EXPORT int ayk_layernorm(void* out, const float* x, const float* gamma, const float* beta,
@@ -128,6 +189,21 @@ AYK_EXPORT int ayk_layernorm(void* out, const float* x, const float* gamma, cons
                              cudaStream_t stream) {
   if (n_rows == 0) return 0;
   AYK_REQUIRE(d >= 1 && (size_t)d * 4 <= 48 * 1024, "ayk_layernorm: width %d is not in [1, 12288]", d);
+  const bool aligned = (d % 4 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)gamma % 16 == 0) &&
+                       (beta == nullptr || (uintptr_t)beta % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  // Many rows: one warp per row (one pass over memory).  Few rows (decode): one block per
+  // row measured faster inside a step (1,845 against 1,713 tokens/s at 8 requests).
+  if (n_rows >= 512 && aligned && d <= 2048 && (out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16)) {
+    dim3 grid((n_rows + 7) / 8);
+    if (out_dtype == AYK_DTYPE_F32) {
+      if (d <= 512) ayk_launch(layernorm_warp_kernel<float, 4>, grid, dim3(256), 0, stream, (float*)out, x, gamma, beta, rows, n_rows, d, eps);
+      else ayk_launch(layernorm_warp_kernel<float, 16>, grid, dim3(256), 0, stream, (float*)out, x, gamma, beta, rows, n_rows, d, eps);
+    } else {
+      if (d <= 512) ayk_launch(layernorm_warp_kernel<__nv_bfloat16, 4>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out, x, gamma, beta, rows, n_rows, d, eps);
+      else ayk_launch(layernorm_warp_kernel<__nv_bfloat16, 16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out, x, gamma, beta, rows, n_rows, d, eps);
+    }
+    return ayk_check_launch("ayk_layernorm");
+  }
   int threads = d >= 1024 ? 256 : 128;
   size_t smem = (size_t)d * sizeof(float);
   if (out_dtype == AYK_DTYPE_F32)

@@ -35,7 +35,7 @@ def test_embed(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width,eps", [(72, 1e-5), (1600, 1e-6), (1000, 3e-2), (8, 1e-5)])
+@pytest.mark.parametrize("width,eps", [(72, 1e-5), (1600, 1e-6), (1000, 3e-2), (8, 1e-5), (2050, 1e-5), (4096, 1e-5), (2048, 1e-5)])
 def test_layernorm(dtype, width, eps):
     from ayaka_py_b200 import ops
     rs = np.random.RandomState(1)
@@ -385,3 +385,18 @@ def test_gemm_tcgen05_many_rows(M, N, K, tile_n, act, out_dtype):
         assert torch.equal(again, out) and ops.tc_error() == 0
         few = ops.gemm_tc(A[:64].contiguous(), W, dev(bias), act, dev(res[:64]), out_dtype=torch.float32, splits=1)
         assert float((few - out[:64]).abs().max()) < 1e-4                     # the few-row kernel agrees
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width", [64, 1600, 2048])
+def test_layernorm_many_rows_one_warp_per_row(dtype, width):
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(13)
+    x = (rs.randn(777, width) * 2 - 0.5).astype(np.float32)
+    g, b = rs.randn(width).astype(np.float32), rs.randn(width).astype(np.float32)
+    want = plain_gpt2.layer_norm(x.astype(np.float64), g, b, 1e-5)
+    out = ops.layernorm(dev(x), dev(g), dev(b), 1e-5, DTYPES[dtype]).float().cpu().numpy()
+    assert np.abs(out - want).max() < tol(dtype, 4.0)
+    rows = np.arange(776, -1, -1).astype(np.int32)
+    picked = ops.layernorm(dev(x), dev(g), None, 1e-5, DTYPES[dtype], rows=dev(rows)).float().cpu().numpy()
+    assert np.abs(picked - (want[rows] - b)).max() < tol(dtype, 4.0)

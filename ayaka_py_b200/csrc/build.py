@@ -33,6 +33,10 @@ NVCC_FLAGS = [
 ]
 
 
+if os.environ.get("AYAKA_B200_TRACE"):      # cycle marks inside the tensor-core kernels (debugging aid)
+    NVCC_FLAGS.append("-DAYK_TRACE")
+
+
 def _log(message: str) -> None:
     print(f"[ayaka_b200 build] {message}", file=sys.stderr, flush=True)
 

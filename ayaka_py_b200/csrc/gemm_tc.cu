@@ -43,7 +43,11 @@ constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2;
 constexpr int THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
-constexpr int stages_for(int bt) { return bt >= 256 ? 4 : (bt >= 128 ? 6 : 8); }
+// Up to 32 rows: 4 stages of 18-20 KB leave room for three CTAs per SM, so that the next
+// kernel's CTAs (launched early, see pdl_wait) can start streaming their weights beside
+// the CTAs of the kernel before them.  64 rows are not split along K (the partial sums
+// would cost more than they save), so few CTAs stream a lot each: a deep ring of 8 stages.
+constexpr int stages_for(int bt) { return bt >= 256 ? 4 : (bt >= 128 ? 6 : (bt >= 64 ? 8 : 4)); }
 constexpr int tmem_cols_for(int bt) { return bt < 32 ? 32 : bt; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -134,7 +138,17 @@ struct EpilogueArgs {
   int M, N, K;
   int act, out_bf16;
   int kb_per_split;
+  long long* trace;          // cycle marks of CTA (0,0,0) when built with -DAYK_TRACE, else unused
 };
+
+#ifdef AYK_TRACE
+__device__ __forceinline__ void mark(const EpilogueArgs& a, int slot) {
+  if (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) a.trace[slot] = clock64();
+}
+#else
+__device__ __forceinline__ void mark(const EpilogueArgs&, int) {}
+#endif
+long long* g_trace = nullptr;
 
 // Epilogue of CNT consecutive tokens of one out feature.  All loads come first,
 // arithmetic and stores after: the residual may alias C, so the compiler cannot
@@ -149,6 +163,22 @@ __device__ __forceinline__ void store_chunk(const EpilogueArgs& a, int tok0, int
     const int tok = tok0 + j;
     res[j] = (a.residual && tok < a.M) ? a.residual[(size_t)tok * a.N + n] : 0.f;
   }
+#pragma unroll
+  for (int j = 0; j < CNT; ++j) {
+    const int tok = tok0 + j;
+    if (tok < a.M) {
+      const float y = apply_activation(v[j] + b, a.act) + res[j];
+      const size_t idx = (size_t)tok * a.N + n;
+      if (a.out_bf16) ((__nv_bfloat16*)a.C)[idx] = __float2bfloat16_rn(y);
+      else ((float*)a.C)[idx] = y;
+    }
+  }
+}
+
+// The same with bias and residual already in registers (fetched while the main loop ran).
+template <int CNT>
+__device__ __forceinline__ void store_chunk_pre(const EpilogueArgs& a, int tok0, int n, const float (&v)[CNT], float b,
+                                                const float* res) {
 #pragma unroll
   for (int j = 0; j < CNT; ++j) {
     const int tok = tok0 + j;
@@ -182,6 +212,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
   volatile int* flag_ptr = (volatile int*)(smem_raw + (tmem_slot + 4 - raw));
 
+  if (threadIdx.x == 0) mark(args, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BLOCK_N, t0 = blockIdx.y * BT;
   const int total_kb = (args.K + BLOCK_K - 1) / BLOCK_K;
@@ -205,6 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (threadIdx.x == 0) mark(args, 1);
   pdl_trigger();     // the next kernel may be scheduled; it waits for this one before it touches its data
 
   if (warp == 0) {
@@ -217,7 +249,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         mbar_expect_tx(full_bar(i), STAGE_BYTES);
         tma_load_2d(tiles + i * STAGE_BYTES, &map_w, (kb_begin + i) * BLOCK_K, n0, full_bar(i));
       }
+      mark(args, 2);
       pdl_wait();
+      mark(args, 3);
       for (int i = 0; i < pre; ++i)
         tma_load_2d(tiles + i * STAGE_BYTES + A_BYTES, &map_x, (kb_begin + i) * BLOCK_K, t0, full_bar(i));
       int issued = pre;
@@ -248,6 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
         ok = mbar_wait(full_bar(s), phase, args.error, 3);
         if (!ok) break;
+        if (i == 0) mark(args, 4);
         tc_fence_after();
         const uint32_t a_src = tiles + s * STAGE_BYTES;
 #pragma unroll
@@ -259,6 +294,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
       }
       umma_commit(tmem_full_bar);           // arrives when every MMA issued so far is done
+      mark(args, 5);
     }
     __syncwarp();
   } else {
@@ -266,7 +302,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int quarter = warp & 3;
     const int n = n0 + quarter * 32 + lane;
     pdl_wait();        // residual, partials and C belong to kernels before this one until here
+    // Bias and the residual of the first 16 tokens are fetched while the main loop runs.
+    const float bias_pre = (args.bias && n < args.N) ? args.bias[n] : 0.f;
+    float res_pre[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int tok = t0 + j;
+      res_pre[j] = (args.residual && n < args.N && tok < args.M) ? args.residual[(size_t)tok * args.N + n] : 0.f;
+    }
     const bool ok = mbar_wait(tmem_full_bar, 0u, args.error, 4);
+    if (threadIdx.x == 64) mark(args, 6);
     tc_fence_after();
     const int splits = gridDim.z;
     if (ok) {
@@ -279,7 +324,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             float v[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-            store_chunk<16>(args, t0 + c, n, v);
+            if (c == 0) store_chunk_pre<16>(args, t0, n, v, bias_pre, res_pre);
+            else store_chunk<16>(args, t0 + c, n, v);
           } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -290,6 +336,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
       }
     }
+    if (threadIdx.x == 64) mark(args, 9);
     if (splits > 1) {
       // The last CTA of this tile to arrive sums the partials in split order.
       __threadfence();
@@ -304,29 +351,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (*flag_ptr && ok) {
         __threadfence();
         if (n < args.N) {
-          for (int c = 0; c < BT && t0 + c < args.M; c += 8) {
-            float v[8];
+          // 4 tokens x 8 splits = 32 loads in flight per thread; summed in split
+          // order, so the result does not depend on which CTA arrived last.
+          constexpr int TK = 4;
+          auto reduce = [&](int c, float (&v)[TK]) {
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = 0.f;
-            for (int z = 0; z < splits; ++z) {          // split order: the sum does not depend on arrival order
-              float p[8];
+            for (int u = 0; u < TK; ++u) v[u] = 0.f;
+            for (int z0 = 0; z0 < splits; z0 += 8) {
+              float p[8][TK];
 #pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                const int tok = t0 + c + u;
-                p[u] = tok < args.M ? __ldcg(&args.partials[((size_t)z * args.M + tok) * args.N + n]) : 0.f;
+              for (int zz = 0; zz < 8; ++zz) {
+#pragma unroll
+                for (int u = 0; u < TK; ++u) {
+                  const int z = z0 + zz, tok = t0 + c + u;
+                  p[zz][u] = (z < splits && tok < args.M)
+                                 ? __ldcg(&args.partials[((size_t)z * args.M + tok) * args.N + n]) : 0.f;
+                }
               }
 #pragma unroll
-              for (int u = 0; u < 8; ++u) v[u] += p[u];
+              for (int zz = 0; zz < 8; ++zz) {
+#pragma unroll
+                for (int u = 0; u < TK; ++u) v[u] += p[zz][u];
+              }
             }
-            store_chunk<8>(args, t0 + c, n, v);
+          };
+          // The first 16 tokens use the bias and residual fetched before the main loop ended.
+#pragma unroll
+          for (int c = 0; c < 16; c += TK) {
+            if (t0 + c < args.M) {
+              float v[TK];
+              reduce(c, v);
+              float res[TK];
+#pragma unroll
+              for (int u = 0; u < TK; ++u) res[u] = res_pre[c + u];
+              store_chunk_pre<TK>(args, t0 + c, n, v, bias_pre, res);
+            }
+          }
+          for (int c = 16; c < BT && t0 + c < args.M; c += TK) {
+            float v[TK];
+            reduce(c, v);
+            store_chunk<TK>(args, t0 + c, n, v);
           }
         }
       }
     }
   }
 
+  if (threadIdx.x == 64) mark(args, 7);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) mark(args, 8);
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TCOLS) : "memory");
   }
@@ -408,6 +482,8 @@ AYK_EXPORT int ayk_gemm_tc_supported(int M, int N, int K) {
 }
 
 // The error word of the tensor-core kernels: 0, or the code of the wait that ran out.
+// Where the cycle marks of the next launches go (device memory, 16 int64); only read by builds with -DAYK_TRACE.
+AYK_EXPORT void ayk_gemm_tc_set_trace(long long* p) { g_trace = p; }
 AYK_EXPORT int ayk_gemm_tc_error() { return g_error_host ? *g_error_host : 0; }
 AYK_EXPORT void ayk_gemm_tc_clear_error() { if (g_error_host) *g_error_host = 0; }
 
@@ -455,7 +531,7 @@ AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* b
     return -1;
   }
   if (encode(&mx, X, M, K, BT) != 0) return -1;
-  EpilogueArgs args{C, bias, residual, partials, counters, g_error_dev, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split};
+  EpilogueArgs args{C, bias, residual, partials, counters, g_error_dev, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split, g_trace};
   switch (BT) {
     case 16: return launch<16>(mw, mx, args, splits, stream);
     case 32: return launch<32>(mw, mx, args, splits, stream);
@@ -557,7 +633,7 @@ AYK_EXPORT int ayk_gemm_tc_no_alloc(void* C, const void* X, const void* W, const
   CUtensorMap mw, mx;
   if (no_alloc_encode(&mw, W, N, K, BLOCK_N) != 0) return -1;
   if (no_alloc_encode(&mx, X, M, K, BT) != 0) return -1;
-  EpilogueArgs args{C, bias, residual, d.partials, d.counters, d.error, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split};
+  EpilogueArgs args{C, bias, residual, d.partials, d.counters, d.error, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split, g_trace};
   switch (BT) {
     case 16: return launch<16>(mw, mx, args, splits, stream);
     case 32: return launch<32>(mw, mx, args, splits, stream);

@@ -355,10 +355,13 @@ AYK_EXPORT int ayk_gemm_tc_prefill_tile(int M, int N, int sms) {
   int best = 256;
   long best_cost = -1;
   const int m_tiles = (M + BM - 1) / BM;
-  for (int bn = 64; bn <= 256; bn += 32) {
+  for (int bn = 32; bn <= 256; bn += 32) {
     const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
     const long waves = (tiles + sms - 1) / sms;
-    const long cost = waves * (bn + 24);
+    // Many rows: the main loop's MMA time, proportional to the tile width, plus a fixed cost per
+    // tile.  One row tile (up to 128 rows): a tile is bound by the bytes an SM can take in, its
+    // rows of X plus bn rows of W per K block, so narrow tiles on many SMs win.
+    const long cost = m_tiles > 1 ? waves * (bn + 24) : waves * (bn + (M < BM ? M : BM));
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
   }
   return best;
@@ -377,7 +380,7 @@ AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const 
   AYK_REQUIRE(out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16, "ayk_gemm_tc_prefill: unknown output dtype %d", out_dtype);
   AYK_REQUIRE(sms >= 1, "ayk_gemm_tc_prefill: sms must be positive");
   int BN = tile_n > 0 ? tile_n : ayk_gemm_tc_prefill_tile(M, N, sms);
-  AYK_REQUIRE(BN >= 64 && BN <= 256 && BN % 32 == 0, "ayk_gemm_tc_prefill: tile width %d is not a multiple of 32 in [64, 256]", BN);
+  AYK_REQUIRE(BN >= 32 && BN <= 256 && BN % 32 == 0, "ayk_gemm_tc_prefill: tile width %d is not a multiple of 32 in [32, 256]", BN);
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (setup() != 0) return -1;

@@ -249,9 +249,9 @@ def tc_splits(M: int, N: int, K: int) -> int:
     bt = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
     tiles = -(-N // 128) * -(-M // bt)
     blocks = -(-K // 64)
-    if tiles >= SM_COUNT // 2 or blocks < 4:
-        return 1
-    return max(1, min(SM_COUNT // tiles, blocks // 2))
+    if tiles >= SM_COUNT // 2 or blocks < 4 or M > 16:
+        return 1          # more than 16 rows: the partial sums cost more than the split saves (measured)
+    return max(1, min(SM_COUNT // tiles, blocks // 2, 8))
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
@@ -288,7 +288,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return out
 
 
-PREFILL_ROWS = 128       # more rows than this: the persistent many-row kernel
+PREFILL_ROWS = 16        # more rows than this: the kernel with 128-row tiles and no split along K
 
 
 def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
@@ -325,7 +325,10 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     pipes (true 32-bit); bfloat16 operands on the tensor cores (tcgen05) when
     K is a multiple of 8, else on the FP32 pipes with 32-bit accumulation."""
     if a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[0] > 0:
-        if a.shape[0] > PREFILL_ROWS:
+        # More than a few rows: tiles of 128 rows by a width that fills the SMs, no split along K.
+        # (Up to 128 rows with an out width that is no multiple of 8 stay with the other kernel,
+        # whose stores run along the features.)
+        if a.shape[0] > PREFILL_ROWS and (w.shape[0] % 8 == 0 or a.shape[0] > 128):
             return gemm_tc_prefill(a, w, bias, activation, residual, out_dtype, out)
         return gemm_tc(a, w, bias, activation, residual, out_dtype, out)
     return gemm_simt(a, w, bias, activation, residual, out_dtype, out)

@@ -248,7 +248,8 @@ def test_gemm_tcgen05(M, N, K, splits, act, out_dtype):
     torch.cuda.synchronize()
     assert ops.tc_error() == 0
     err = np.abs(out.float().cpu().numpy() - want).max()
-    assert err < (2e-5 if out_dtype == "float32" else 4e-2), err
+    # The tensor core adds K products of ~unit size in 32-bit: the rounding error grows like sqrt(K).
+    assert err < (2e-5 * max(1.0, K / 1600.0) ** 0.5 if out_dtype == "float32" else 4e-2), err
     if out_dtype == "float32":
         R = dev(res)
         again = ops.gemm_tc(A, W, dev(bias), act, R, out_dtype=torch.float32, out=R, splits=splits, static_weight=False)

@@ -73,7 +73,24 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and records `code`) when the barrier did not
 // complete within WAIT_LIMIT polls.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error, int code) {
+  // A few non-blocking tests first: a phase that is complete already, or nearly, is seen at once
+  // (the possibly suspending try_wait cost ~290 cycles per K block on the MMA thread).
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i) {
+    if (mbar_test(bar, parity)) return true;
+  }
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     if (mbar_try(bar, parity)) return true;
   }
@@ -260,11 +277,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
         ok = mbar_wait(empty_bar(s), phase ^ 1u, args.error, 1);
         if (!ok) break;
+        if (i < 12) mark(args, 32 + 4 * i);
         mbar_expect_tx(full_bar(s), STAGE_BYTES);
         const uint32_t a_dst = tiles + s * STAGE_BYTES;
         const int kx = (kb_begin + i) * BLOCK_K;
+        if (i < 12) mark(args, 33 + 4 * i);
         tma_load_2d(a_dst, &map_w, kx, n0, full_bar(s));
+        if (i < 12) mark(args, 34 + 4 * i);
         tma_load_2d(a_dst + A_BYTES, &map_x, kx, t0, full_bar(s));
+        if (i < 12) mark(args, 35 + 4 * i);
         issued = i + 1;
       }
       if (!ok) {
@@ -283,15 +304,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         ok = mbar_wait(full_bar(s), phase, args.error, 3);
         if (!ok) break;
         if (i == 0) mark(args, 4);
+        if (i < 12) mark(args, 96 + 4 * i);
         tc_fence_after();
         const uint32_t a_src = tiles + s * STAGE_BYTES;
+        const uint64_t da0 = make_desc(a_src), db0 = make_desc(a_src + A_BYTES);
 #pragma unroll
         for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-          const uint64_t da = make_desc(a_src + k * UMMA_K * 2);
-          const uint64_t db = make_desc(a_src + A_BYTES + k * UMMA_K * 2);
+          // 32 bytes further along K inside the swizzle atom: the address field counts 16-byte units
+          const uint64_t da = da0 + (uint64_t)(k * UMMA_K * 2 / 16), db = db0 + (uint64_t)(k * UMMA_K * 2 / 16);
           umma(tmem_base, da, db, IDESC, (i > 0 || k > 0) ? 1u : 0u);
         }
+        if (i < 12) mark(args, 97 + 4 * i);
         umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+        if (i < 12) mark(args, 98 + 4 * i);
       }
       umma_commit(tmem_full_bar);           // arrives when every MMA issued so far is done
       mark(args, 5);

@@ -102,6 +102,7 @@ struct PrefillArgs {
   int M, N, K;
   int act, out_bf16;
   int BN, stages, m_tiles, n_tiles;
+  int box_m;                 // rows of X that one TMA copy brings (128, fewer when M is small)
 };
 
 // One row, W consecutive columns (W = 16 or 32) starting at column n.
@@ -165,6 +166,9 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
                        const PrefillArgs args) {
   const int BN = args.BN, STAGES = args.stages;
   const uint32_t B_BYTES = (uint32_t)BN * BLOCK_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  // With fewer than 128 rows in all, only those rows are copied; the rest of the A tile keeps
+  // whatever it held: its products land in accumulator rows that the epilogue never stores.
+  const uint32_t TX_BYTES = (uint32_t)args.box_m * BLOCK_K * 2 + B_BYTES;
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
   extern __shared__ uint8_t smem_raw[];
@@ -201,33 +205,51 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 
   if (warp == 0) {
     if (lane == 0) {
-      // Iteration `it` over all of this CTA's tiles: tile it / num_kb, K block it % num_kb.
+      // A cursor walks this CTA's tiles and their K blocks; no division or modulo per K block
+      // (one thread issues every copy, and its arithmetic set the pace of the whole pipeline).
       const int total_it = my_tiles * num_kb;
-      auto load = [&](int it, bool weight) {
-        const int tile = blockIdx.x + (it / num_kb) * gridDim.x, kx = (it % num_kb) * BLOCK_K;
-        const uint32_t dst = tiles + (it % STAGES) * STAGE_BYTES;
-        if (weight) tma_load_2d(dst + A_BYTES, &map_w, kx, (tile % args.n_tiles) * BN, full_bar(it % STAGES));
-        else tma_load_2d(dst, &map_x, kx, (tile / args.n_tiles) * BM, full_bar(it % STAGES));
+      struct Cursor { int tile, kx, m0, n0, kb; };
+      auto start = [&]() {
+        Cursor c; c.tile = blockIdx.x; c.kb = 0; c.kx = 0;
+        c.m0 = (c.tile / args.n_tiles) * BM; c.n0 = (c.tile % args.n_tiles) * BN;
+        return c;
+      };
+      auto advance = [&](Cursor& c) {
+        c.kx += BLOCK_K;
+        if (++c.kb == num_kb) {
+          c.kb = 0; c.kx = 0; c.tile += gridDim.x;
+          c.m0 = (c.tile / args.n_tiles) * BM; c.n0 = (c.tile % args.n_tiles) * BN;
+        }
       };
       // The weight does not depend on the kernels before this one: its first
       // stages start streaming at once; the rows X wait for the predecessor.
       const int pre = min(STAGES, total_it);
-      for (int it = 0; it < pre; ++it) {
-        mbar_expect_tx(full_bar(it), STAGE_BYTES);
-        load(it, true);
+      Cursor cw = start();
+      for (int s = 0; s < pre; ++s) {
+        mbar_expect_tx(full_bar(s), TX_BYTES);
+        tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &map_w, cw.kx, cw.n0, full_bar(s));
+        advance(cw);
       }
       pdl_wait();
-      for (int it = 0; it < pre; ++it) load(it, false);
+      Cursor cx = start();
+      for (int s = 0; s < pre; ++s) {
+        tma_load_2d(tiles + s * STAGE_BYTES, &map_x, cx.kx, cx.m0, full_bar(s));
+        advance(cx);
+      }
       bool ok = true;
       int issued = pre;
+      int s = pre == STAGES ? 0 : pre;              // the stage of iteration `pre`
+      uint32_t wait_parity = 0;                     // the first refill of a stage waits for its first release
       for (int it = pre; it < total_it; ++it) {
-        const int s = it % STAGES;
-        ok = mbar_wait(empty_bar(s), (uint32_t)((it / STAGES) & 1) ^ 1u, args.error, 21);
+        ok = mbar_wait(empty_bar(s), wait_parity, args.error, 21);
         if (!ok) break;
-        mbar_expect_tx(full_bar(s), STAGE_BYTES);
-        load(it, true);
-        load(it, false);
+        mbar_expect_tx(full_bar(s), TX_BYTES);
+        const uint32_t dst = tiles + s * STAGE_BYTES;
+        tma_load_2d(dst + A_BYTES, &map_w, cx.kx, cx.n0, full_bar(s));
+        tma_load_2d(dst, &map_x, cx.kx, cx.m0, full_bar(s));
+        advance(cx);
         issued = it + 1;
+        if (++s == STAGES) { s = 0; wait_parity ^= 1u; }
       }
       if (!ok) {
         for (int j = max(0, issued - STAGES); j < issued; ++j)
@@ -238,7 +260,8 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true;
-      int it = 0;
+      int s = 0;
+      uint32_t full_parity = 0;
       for (int t = 0; t < my_tiles && ok; ++t) {
         const int b = t & 1;
         if (t >= 2) {
@@ -247,16 +270,17 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           tc_fence_after();
         }
         const uint32_t acc = tmem_base + (uint32_t)b * 256u;
-        for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(full_bar(s), (uint32_t)(it / STAGES) & 1u, args.error, 24);
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = mbar_wait(full_bar(s), full_parity, args.error, 24);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_src = tiles + s * STAGE_BYTES;
+          const uint64_t da0 = make_desc(a_src), db0 = make_desc(a_src + A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BLOCK_K / 16; ++k)
-            umma(acc, make_desc(a_src + k * 32), make_desc(a_src + A_BYTES + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BLOCK_K / 16; ++k)     // 32 bytes further along K: two 16-byte units of the address field
+            umma(acc, da0 + (uint64_t)(2 * k), db0 + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(empty_bar(s));
+          if (++s == STAGES) { s = 0; full_parity ^= 1u; }
         }
         umma_commit(tmem_full(b));
       }
@@ -272,7 +296,9 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       const int b = t & 1;
       const int tile = blockIdx.x + t * gridDim.x;
       const int m0 = (tile / args.n_tiles) * BM, n0 = (tile % args.n_tiles) * BN;
-      ok = mbar_wait(tmem_full(b), (uint32_t)(t >> 1) & 1u, args.error, 25);
+      // One lane per warp watches the barrier; 256 threads polling it slow the producer and MMA warps down.
+      if (lane == 0) ok = mbar_wait(tmem_full(b), (uint32_t)(t >> 1) & 1u, args.error, 25);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
@@ -386,7 +412,8 @@ AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const 
     if (setup() != 0) return -1;
   }
   CUtensorMap mx, mw;
-  if (encode(&mx, X, M, K, BM) != 0) return -1;
+  const int box_m = M >= BM ? BM : (M + 7) / 8 * 8;
+  if (encode(&mx, X, M, K, box_m) != 0) return -1;
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     MapKey key{W, N, K, BN};
@@ -402,6 +429,7 @@ AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const 
   args.C = C; args.bias = bias; args.residual = residual; args.error = g_error_dev;
   args.M = M; args.N = N; args.K = K; args.act = act; args.out_bf16 = out_dtype == AYK_DTYPE_BF16;
   args.BN = BN;
+  args.box_m = box_m;
   args.m_tiles = (M + BM - 1) / BM;
   args.n_tiles = (N + BN - 1) / BN;
   int stages = SMEM_TILES / (A_BYTES + BN * BLOCK_K * 2);

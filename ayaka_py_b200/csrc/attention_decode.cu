@@ -4,17 +4,23 @@
 // The reference's decode path is a split-KV kernel over partitions of 512 keys
 // with partial outputs and log-sum-exps in 32-bit scratch and a reduce kernel
 // (kernel/triton/paged_attention.py:474-736).  Here a partition is 128 keys
-// (PART), the grid is (request, head, partition) with a fixed number of
-// partitions (those beyond a request's context return at once, so the launch
-// does not depend on the context lengths and can be replayed from a CUDA graph),
-// and nothing but the block table is needed to find the keys.
+// (PART) and the number of partitions is fixed per engine (those beyond a
+// request's context return at once), so the launch does not depend on the
+// context lengths and can be replayed from a CUDA graph; nothing but the block
+// table is needed to find the keys.  Partials (unnormalised sum, running
+// maximum, sum of exponentials) go to scratch [request, head, partition, Dh + 2]
+// and a second kernel combines them in partition order.  (Letting the CTA that
+// finishes last do the merge was measured slower: 70 against 59 us at 64
+// requests, since every CTA then waits for its stores to become visible.)
 //
-// Scores, softmax and the weighted sum are 32-bit.  Per partition: scores with
-// one key per lane (16-byte loads along the head dimension), then the weighted
-// sum with one pair of head-dim columns per lane (coalesced rows of V).
-// Partials (unnormalised sum, running max, sum of exponentials) go to scratch
-// [request, head, partition, Dh + 2]; the merge kernel combines them in
-// partition order.
+// Two kernels.  bfloat16 with head sizes 32, 64, 128 runs on the tensor cores
+// (decode_mma_kernel, below); measured on B200 at 64 requests x 25 heads x 570
+// keys it moves 4.0 TB/s against 2.1 TB/s of the kernel that does the products
+// on the FP32 pipe, which is bound by instruction issue (about 10,000 warp
+// instructions per partition against under 1,000).  Everything else (32-bit,
+// other head sizes) takes decode_split_kernel: scores with one key per lane,
+// the weighted sum with one pair of head-dim columns per lane, then
+// decode_merge_kernel.  Softmax, maxima and sums are 32-bit in both.
 #include <math.h>
 
 #include "common.cuh"
@@ -159,6 +165,210 @@ decode_split_kernel(float* __restrict__ scratch, const T* __restrict__ q, int q_
   if (threadIdx.x == 0) { out[Dh] = m; out[Dh + 1] = l; }
 }
 
+// bfloat16 on the tensor cores (mma.sync m16n8k16; one query row per head leaves
+// no work for a 128-row tcgen05 tile).  One CTA per (request, key/value head, up to 8
+// query heads that share it, partition); each of its 4 warps owns 32 keys.  A warp
+// copies its keys and values into shared memory with cp.async (16-byte pieces,
+// swizzled so that ldmatrix meets no bank conflict; rows outside the context are
+// zero-filled), computes the scores of its keys as soon as the keys have landed
+// (the query heads are rows 0..7 of the A operand, rows 8..15 stay zero), the
+// softmax of its 32 keys in 32-bit, and the weighted sum with the values read
+// through ldmatrix.trans.  The four warps' results are joined through shared
+// memory into one partial per partition.  Probabilities are rounded to bfloat16
+// for the second product, as in prefill.
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// cp.async of 16 bytes, or 16 bytes of zeros when !valid (src must still be a mapped address)
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
+}
+// 16-byte piece `piece` of row `row` (PPR pieces per row) sits at this piece index of the row:
+// eight consecutive rows at one logical piece fall into eight different 16-byte bank groups.
+template <int PPR> __device__ __forceinline__ int swizzled_piece(int row, int piece) {
+  if constexpr (PPR >= 8) return piece ^ (row & 7);
+  else return piece ^ ((row >> 1) & 3);          // PPR == 4: two rows per 128 bytes
+}
+
+template <int DH>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__ q, int q_stride,
+                  const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
+                  const int* __restrict__ table, int table_stride, const int* __restrict__ req_pos0,
+                  int H, int Hkv, int page_shift, float scale_log2, int window, int parts, int chunks, int rows) {
+  pdl_trigger();
+  pdl_wait();
+  static_assert(WARPS * 32 == PART, "each warp owns 32 keys of the partition");
+  constexpr int KS = DH / 16;                    // k steps of the first product
+  constexpr int PPR = DH / 8;                    // 16-byte pieces per row
+  constexpr int NT = DH / 8;                     // output tiles of the second product
+  constexpr int ROW_BYTES = DH * 2;
+  const long item = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int part = (int)(item % parts);
+  const int chunk = (int)((item / parts) % chunks);
+  const int kvh = (int)((item / ((long)parts * chunks)) % Hkv);
+  const int r = (int)(item / ((long)parts * chunks * Hkv));
+  const int group = H / Hkv;
+  const int head0 = kvh * group + chunk * 8;               // the query head of A row 0
+  const int rows_here = min(rows, group - chunk * 8);
+  const int pos = req_pos0[r];
+  const int page_size = 1 << page_shift;
+  int k_lo = part * PART;
+  const int k_hi = min(pos + 1, k_lo + PART);
+  if (window > 0) k_lo = max(k_lo, pos - window + 1);
+  const bool empty = k_lo >= k_hi;               // the same for the whole CTA
+  if (empty && (int)threadIdx.x < rows_here) {
+    float* dst = scratch + ((size_t)(r * H + head0 + threadIdx.x) * parts + part) * (DH + 2);
+    dst[DH] = -INFINITY; dst[DH + 1] = 0.f;
+  }
+  extern __shared__ __align__(128) unsigned char smem_dyn[];
+  const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(smem_dyn);
+  const uint32_t vs_base = ks_base + PART * ROW_BYTES;
+  float* comb = reinterpret_cast<float*>(smem_dyn + 2 * PART * ROW_BYTES);      // [WARPS][rows][DH + 2]
+
+  const int wk0 = part * PART + warp * 32;       // this warp's first key
+  const int w_lo = max(k_lo, wk0), w_hi = min(k_hi, wk0 + 32);
+  const bool warp_has_keys = !empty && w_lo < w_hi;
+  float m_w = -INFINITY, l_w = 0.f;
+  float o[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
+
+  if (warp_has_keys) {
+    // pages of this warp's keys: lane l holds the page of keys [wk0 + l * page_size, ...)
+    const int first_logical = wk0 >> page_shift;
+    int my_page = 0;
+    if (lane < ((32 + page_size - 1) >> page_shift) && first_logical + lane < table_stride)
+      my_page = table[(size_t)r * table_stride + first_logical + lane];
+    const size_t row_elems = (size_t)Hkv * DH;
+    const size_t head_off = (size_t)kvh * DH;
+    // copies: lane covers piece (lane % PPR) of rows (lane / PPR) + i * (32 / PPR)   [PPR <= 32]
+    constexpr int RPI = 32 / PPR;                // rows per instruction
+    const int my_piece = lane % PPR, my_row0 = lane / PPR;
+#pragma unroll
+    for (int mat = 0; mat < 2; ++mat) {
+      const __nv_bfloat16* cache = mat == 0 ? kcache : vcache;
+      const uint32_t base = mat == 0 ? ks_base : vs_base;
+#pragma unroll
+      for (int i = 0; i < 32 / RPI; ++i) {
+        const int row = my_row0 + i * RPI;       // within the warp's 32 keys
+        const int key = wk0 + row;
+        const int page = __shfl_sync(0xffffffffu, my_page, (key >> page_shift) - first_logical);
+        const bool ok = key >= w_lo && key < w_hi && page > 0;
+        const size_t off = ok ? ((((size_t)page) << page_shift) + (key & (page_size - 1))) * row_elems + head_off + my_piece * 8 : 0;
+        cp_async16_zfill(base + (warp * 32 + row) * ROW_BYTES + swizzled_piece<PPR>(row, my_piece) * 16, cache + off, ok);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    // the query rows as A operands (rows beyond the group stay zero)
+    uint32_t qa[KS][2];
+    {
+      const bool row_ok = g < rows_here;
+      const __nv_bfloat16* qrow = q + (size_t)r * q_stride + (size_t)(head0 + g) * DH;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        qa[ks][0] = row_ok ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+        qa[ks][1] = row_ok ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+      }
+    }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncwarp();
+    // scores: 4 tiles of 8 keys
+    float sc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sc[j][0] = 0.f; sc[j][1] = 0.f; sc[j][2] = 0.f; sc[j][3] = 0.f;
+      const int row = j * 8 + (lane & 7);        // the row whose address this lane supplies
+#pragma unroll
+      for (int h = 0; h < PPR / 4; ++h) {
+        uint32_t kb[4];
+        ldmatrix_x4(kb, ks_base + (warp * 32 + row) * ROW_BYTES + swizzled_piece<PPR>(row, 4 * h + (lane >> 3)) * 16);
+        mma_bf16(sc[j], qa[2 * h][0], qa[2 * h][1], kb[0], kb[1]);
+        mma_bf16(sc[j], qa[2 * h + 1][0], qa[2 * h + 1][1], kb[2], kb[3]);
+      }
+    }
+    float mb = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = wk0 + j * 8 + 2 * t + e;
+        sc[j][e] = (key >= w_lo && key < w_hi) ? sc[j][e] * scale_log2 : -INFINITY;
+        mb = fmaxf(mb, sc[j][e]);
+      }
+    }
+    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+    m_w = mb;                                    // finite: the warp has a visible key
+    uint32_t pa[2][2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float p0 = exp2f(sc[j][0] - m_w), p1 = exp2f(sc[j][1] - m_w);
+      l_w += p0 + p1;
+      pa[j >> 1][j & 1] = pack_bf16(p0, p1);
+    }
+    l_w += __shfl_xor_sync(0xffffffffu, l_w, 1);
+    l_w += __shfl_xor_sync(0xffffffffu, l_w, 2);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int row = s * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, vs_base + (warp * 32 + row) * ROW_BYTES + swizzled_piece<PPR>(row, 2 * np + (lane >> 4)) * 16);
+        mma_bf16(o[2 * np], pa[s][0], pa[s][1], vb[0], vb[1]);
+        mma_bf16(o[2 * np + 1], pa[s][0], pa[s][1], vb[2], vb[3]);
+      }
+    }
+  }
+  // join the warps
+  if (!empty) {
+    if (g < rows_here) {
+      float* mine = comb + ((size_t)warp * rows + g) * (DH + 2);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) *reinterpret_cast<float2*>(mine + j * 8 + 2 * t) = make_float2(o[j][0], o[j][1]);
+      if (t == 0) { mine[DH] = m_w; mine[DH + 1] = l_w; }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows_here * DH; idx += WARPS * 32) {
+      const int row = idx / DH, d = idx % DH;
+      float mw[WARPS], m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) { mw[w] = comb[((size_t)w * rows + row) * (DH + 2) + DH]; m = fmaxf(m, mw[w]); }
+      float acc = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        if (mw[w] > -INFINITY) {
+          const float f = exp2f(mw[w] - m);
+          acc = fmaf(comb[((size_t)w * rows + row) * (DH + 2) + d], f, acc);
+          l = fmaf(comb[((size_t)w * rows + row) * (DH + 2) + DH + 1], f, l);
+        }
+      }
+      float* dst = scratch + ((size_t)(r * H + head0 + row) * parts + part) * (DH + 2);
+      dst[d] = acc;
+      if (d == 0) { dst[DH] = m * 0.6931471805599453f; dst[DH + 1] = l; }    // the merge works with natural exponentials
+    }
+  }
+}
+
 template <typename T>
 __global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict__ scratch, int H, int Dh, int parts) {
   pdl_trigger();
@@ -200,21 +410,50 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, cons
   AYK_REQUIRE(Dh >= 16 && Dh % 16 == 0 && Dh <= MAX_DH, "ayk_attention_decode: head size %d is not a multiple of 16 in [16, %d]", Dh, MAX_DH);
   AYK_REQUIRE(Hkv >= 1 && H % Hkv == 0, "ayk_attention_decode: %d heads cannot share %d key/value heads", H, Hkv);
   AYK_REQUIRE(parts >= 1 && parts <= 65535 && H <= 65535, "ayk_attention_decode: grid too large (heads %d, parts %d)", H, parts);
+  AYK_REQUIRE(dtype == AYK_DTYPE_F32 || dtype == AYK_DTYPE_BF16, "ayk_attention_decode: unknown dtype %d", dtype);
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  const bool mma_ok = dtype == AYK_DTYPE_BF16 && (Dh == 32 || Dh == 64 || Dh == 128) && (1 << page_shift) == page_size &&
+                      page_size >= 4 && q_stride % 2 == 0 && (uintptr_t)q % 4 == 0 && (uintptr_t)kcache % 16 == 0 &&
+                      (uintptr_t)vcache % 16 == 0;
+  if (mma_ok) {
+    const int group = H / Hkv, chunks = (group + 7) / 8, rows = group < 8 ? group : 8;
+    const long items = (long)R * Hkv * chunks * parts;
+    AYK_REQUIRE(items <= 0x7fffffffL, "ayk_attention_decode: too many partitions (%ld)", items);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const size_t smem = 2 * (size_t)PART * Dh * 2 + (size_t)WARPS * rows * (Dh + 2) * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+      const int most = 2 * PART * 128 * 2 + WARPS * 8 * (128 + 2) * 4;
+      if (cudaFuncSetAttribute(decode_mma_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+          cudaFuncSetAttribute(decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+          cudaFuncSetAttribute(decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess)
+        return ayk_fail("ayk_attention_decode: cannot reserve %d bytes of shared memory", most);
+      configured = true;
+    }
+#define AYK_DECODE_MMA(D)                                                                                              \
+  ayk_launch(decode_mma_kernel<D>, dim3((unsigned)items), dim3(WARPS * 32), smem, stream, scratch,                      \
+             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, table,      \
+             table_stride, req_pos0, H, Hkv, page_shift, scale_log2, window, parts, chunks, rows)
+    if (Dh == 32) AYK_DECODE_MMA(32); else if (Dh == 64) AYK_DECODE_MMA(64); else AYK_DECODE_MMA(128);
+#undef AYK_DECODE_MMA
+    ayk_launch(decode_merge_kernel<__nv_bfloat16>, dim3(R, H), dim3(Dh <= 32 ? 32 : (Dh <= 64 ? 64 : 128)), 0, stream,
+               (__nv_bfloat16*)out, (const float*)scratch, H, Dh, parts);
+    return ayk_check_launch("ayk_attention_decode");
+  }
   dim3 grid(R, H, parts), mgrid(R, H);
-  int mthreads = Dh <= 32 ? 32 : (Dh <= 64 ? 64 : 128);
+  const int mthreads = Dh <= 32 ? 32 : (Dh <= 64 ? 64 : 128);
   if (dtype == AYK_DTYPE_F32) {
     ayk_launch(decode_split_kernel<float>, grid, dim3(WARPS * 32), 0, stream, scratch, (const float*)q, q_stride,
                (const float*)kcache, (const float*)vcache, table, table_stride, req_pos0, H, Hkv, Dh, page_size, scale,
                window, parts);
     ayk_launch(decode_merge_kernel<float>, mgrid, dim3(mthreads), 0, stream, (float*)out, (const float*)scratch, H, Dh, parts);
-  } else if (dtype == AYK_DTYPE_BF16) {
+  } else {
     ayk_launch(decode_split_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), 0, stream, scratch, (const __nv_bfloat16*)q,
                q_stride, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, table, table_stride, req_pos0, H, Hkv,
                Dh, page_size, scale, window, parts);
     ayk_launch(decode_merge_kernel<__nv_bfloat16>, mgrid, dim3(mthreads), 0, stream, (__nv_bfloat16*)out,
                (const float*)scratch, H, Dh, parts);
-  } else {
-    return ayk_fail("ayk_attention_decode: unknown dtype %d", dtype);
   }
   return ayk_check_launch("ayk_attention_decode");
 }

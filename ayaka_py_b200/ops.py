@@ -335,7 +335,18 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
 
 
 DECODE_PART = 128
-_decode_scratch: dict = {}
+_decode_scratch: dict = {}      # device -> partials; outgrown buffers stay alive below
+_decode_retired: list = []      # a captured CUDA graph may still write to an outgrown buffer
+
+
+def _decode_buffer(device, floats: int) -> torch.Tensor:
+    have = _decode_scratch.get(device)
+    if have is None or have.numel() < floats:
+        if have is not None:
+            _decode_retired.append(have)
+        have = torch.empty(max(floats, 1 << 21), dtype=torch.float32, device=device)
+        _decode_scratch[device] = have
+    return have
 
 
 def attention_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, table: torch.Tensor,
@@ -351,11 +362,7 @@ def attention_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor
     if req_pos0.numel() != R:
         raise KernelError("attention_decode: one row per request")
     parts = -(-max_context // DECODE_PART)
-    need = R * num_heads * parts * (Dh + 2)
-    scratch = _decode_scratch.get(q.device)
-    if scratch is None or scratch.numel() < need:
-        scratch = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
-        _decode_scratch[q.device] = scratch
+    scratch = _decode_buffer(q.device, R * num_heads * parts * (Dh + 2))
     if out is None:
         out = torch.empty((R, num_heads * Dh), dtype=q.dtype, device=q.device)
     _launch(lib.ayk_attention_decode(_ptr(out), _ptr(q), ctypes.c_int(q.stride(0)), _ptr(kcache), _ptr(vcache),

@@ -286,6 +286,9 @@ DECODE_CASES = [
     ([700], 2, 1, 256, 32, None),
     ([3, 130, 500], 4, 2, 32, 16, 40),
     ([63, 64, 200], 5, 5, 16, 64, 129),
+    ([9, 200, 333], 20, 2, 128, 4, None),      # groups of 10 heads: two passes of rows; small pages
+    ([150, 31, 0], 8, 1, 64, 64, 70),          # 8 heads on one key/value head; a page larger than a warp's keys
+    ([1000, 513], 3, 3, 32, 32, None),
 ]
 
 

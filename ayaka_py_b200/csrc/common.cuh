@@ -52,6 +52,27 @@ __device__ __forceinline__ float apply_activation(float x, int act) {
   return x;
 }
 
+// The same activations for the epilogues of the bfloat16 tensor-core products, where a
+// row of the tile costs issue slots that the main loop cannot hide: tanh-GELU as
+// x / (1 + 2^(-2 log2(e) u)), u = sqrt(2/pi) (x + 0.044715 x^3), with ex2.approx and a fast
+// division (a few ulp in 32-bit, far inside a bfloat16 operand's rounding); the others as above.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <int ACT>
+__device__ __forceinline__ float apply_activation_tc(float x, int act) {
+  if (ACT == AYK_ACT_NONE) return x;
+  if (ACT == AYK_ACT_GELU_TANH) {
+    const float x2 = x * x;
+    const float t = x * fmaf(x2, -2.0f * 1.4426950408889634f * 0.7978845608028654f * 0.044715f,
+                             -2.0f * 1.4426950408889634f * 0.7978845608028654f);
+    return __fdividef(x, 1.0f + fast_exp2(t));
+  }
+  return apply_activation(x, act);
+}
+
 // Programmatic dependent launch: a kernel launched with the attribute may start
 // while its predecessor in the stream still runs; it must not touch memory that
 // the predecessor writes (or write memory that it reads) before pdl_wait().

@@ -5,7 +5,7 @@
 //   C[M, N] = act(X[M, K] * W[N, K]^T + bias[N]) (+ residual[M, N])
 //
 // A tile is 128 rows of X (the MMA's M side, one row per TMEM lane) by BN out
-// features (its N side, BN = 64 ... 256 in steps of 32, chosen by the host so
+// features (its N side, BN = 32 ... 256 in steps of 32, chosen by the host so
 // that the tiles fill whole waves of the 148 SMs).  Operands come by TMA in
 // 64-element K blocks with the 128-byte swizzle through a ring of stages.
 // Warp 0: TMA producer; warp 1: MMA issue and TMEM allocation; warps 2..9:
@@ -15,10 +15,12 @@
 // 32-bit residual (all loads of a chunk issued before its stores: the residual
 // may alias C) and stores 128 contiguous bytes.
 //
-// Every mbarrier wait is bounded; a wait that runs out records a code (21..26)
-// in the error word of the tensor-core kernels and the CTA winds down.
+// Every mbarrier wait is bounded; a wait that runs out records a code (21..25,
+// 31..35 in the two-SM form) in the error word of the tensor-core kernels and
+// the CTA winds down.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -103,62 +105,105 @@ struct PrefillArgs {
   int act, out_bf16;
   int BN, stages, m_tiles, n_tiles;
   int box_m;                 // rows of X that one TMA copy brings (128, fewer when M is small)
+  int mode;                  // which compiled form of the epilogue (see epilogue_chunk)
+  int vec_ok;                // N % 8 == 0 and bias, residual, C 16-byte aligned: whole chunks move in 16-byte pieces
 };
 
-// One row, W consecutive columns (W = 16 or 32) starting at column n.
-template <int W>
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+// One row, W consecutive columns (W = 16 or 32) starting at column n.  The epilogue competes
+// with nothing for memory but it does for issue slots and registers, and with 25 K blocks per
+// tile it is as long as the main loop.  So whole chunks inside the matrix take 16-byte loads of
+// bias and residual and no test per element, and the three combinations that a transformer block
+// uses are compiled on their own (MODE): 0 = bfloat16 out, no activation, no residual; 1 = float32
+// out with residual; 2 = bfloat16 out with tanh-GELU; 3 = anything, decided at run time.
+template <int W, int MODE>
 __device__ __forceinline__ void epilogue_chunk(const PrefillArgs& a, uint32_t taddr, int row, int n, bool row_ok) {
+  constexpr int ACT = MODE == 2 ? AYK_ACT_GELU_TANH : (MODE == 3 ? -1 : AYK_ACT_NONE);
   uint32_t r[W];
-  tmem_ld16(taddr, r);
-  if (W == 32) tmem_ld16(taddr + 16, r + 16);
-  float res[W];
-  const bool full = row_ok && n + W <= a.N && (a.N & 7) == 0;    // 16-byte aligned row segments
+  if (W == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
   const size_t idx = (size_t)row * a.N + n;
-  if (a.residual && full) {
+  const bool out_bf16 = MODE == 3 ? a.out_bf16 != 0 : MODE != 1;
+  if (a.vec_ok && n + W <= a.N) {
+    const bool with_res = (MODE == 1 || MODE == 3) && a.residual != nullptr && row_ok;
+    float4 res[(MODE == 1 || MODE == 3) ? W / 4 : 1];
+    if (MODE == 1 || MODE == 3) {
+      if (with_res) {     // every load of the chunk before its first store: the residual may be C itself
 #pragma unroll
-    for (int j = 0; j < W; j += 4) {
-      const float4 v = *reinterpret_cast<const float4*>(a.residual + idx + j);
-      res[j] = v.x; res[j + 1] = v.y; res[j + 2] = v.z; res[j + 3] = v.w;
+        for (int j = 0; j < W / 4; ++j) res[j] = *reinterpret_cast<const float4*>(a.residual + idx + 4 * j);
+      }
     }
-  } else {
+    tmem_ld_wait();
+    if (!row_ok) return;
 #pragma unroll
-    for (int j = 0; j < W; ++j) res[j] = (a.residual && row_ok && n + j < a.N) ? a.residual[idx + j] : 0.f;
-  }
-  tmem_ld_wait();
-  float y[W];
+    for (int j = 0; j < W; j += 8) {
+      float y[8];
 #pragma unroll
-  for (int j = 0; j < W; ++j) {
-    const float b = (a.bias && n + j < a.N) ? __ldg(a.bias + n + j) : 0.f;
-    y[j] = apply_activation(__uint_as_float(r[j]) + b, a.act) + res[j];
-  }
-  if (!row_ok) return;
-  if (full) {
-    if (a.out_bf16) {
-      __nv_bfloat16* dst = (__nv_bfloat16*)a.C + idx;
-#pragma unroll
-      for (int j = 0; j < W; j += 8) {
+      for (int u = 0; u < 8; u += 4) {
+        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a.bias) bv = __ldg(reinterpret_cast<const float4*>(a.bias + n + j + u));
+        y[u] = apply_activation_tc<ACT>(__uint_as_float(r[j + u]) + bv.x, a.act);
+        y[u + 1] = apply_activation_tc<ACT>(__uint_as_float(r[j + u + 1]) + bv.y, a.act);
+        y[u + 2] = apply_activation_tc<ACT>(__uint_as_float(r[j + u + 2]) + bv.z, a.act);
+        y[u + 3] = apply_activation_tc<ACT>(__uint_as_float(r[j + u + 3]) + bv.w, a.act);
+        if (MODE == 1 || MODE == 3) {
+          if (with_res) {
+            const float4 rv = res[(j + u) / 4];
+            y[u] += rv.x; y[u + 1] += rv.y; y[u + 2] += rv.z; y[u + 3] += rv.w;
+          }
+        }
+      }
+      if (out_bf16) {
         uint32_t w[4];
 #pragma unroll
         for (int u = 0; u < 8; u += 2) {
-          __nv_bfloat162 p = __floats2bfloat162_rn(y[j + u], y[j + u + 1]);
+          __nv_bfloat162 p = __floats2bfloat162_rn(y[u], y[u + 1]);
           w[u >> 1] = *reinterpret_cast<uint32_t*>(&p);
         }
-        *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>((__nv_bfloat16*)a.C + idx + j) = make_uint4(w[0], w[1], w[2], w[3]);
+      } else {
+        float* dst = (float*)a.C + idx + j;
+        *reinterpret_cast<float4*>(dst) = make_float4(y[0], y[1], y[2], y[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(y[4], y[5], y[6], y[7]);
       }
-    } else {
-      float* dst = (float*)a.C + idx;
-#pragma unroll
-      for (int j = 0; j < W; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
     }
-  } else {
+    return;
+  }
+  // the ragged edge of the matrix, or rows whose 16-byte pieces are not aligned: element by element
+  tmem_ld_wait();
 #pragma unroll
-    for (int j = 0; j < W; ++j) {
-      if (n + j < a.N) {
-        if (a.out_bf16) ((__nv_bfloat16*)a.C)[idx + j] = __float2bfloat16_rn(y[j]);
-        else ((float*)a.C)[idx + j] = y[j];
-      }
+  for (int j = 0; j < W; ++j) {
+    if (row_ok && n + j < a.N) {
+      const float b = a.bias ? __ldg(a.bias + n + j) : 0.f;
+      const float res = a.residual ? a.residual[idx + j] : 0.f;
+      const float y = apply_activation_tc<ACT>(__uint_as_float(r[j]) + b, a.act) + res;
+      if (a.out_bf16) ((__nv_bfloat16*)a.C)[idx + j] = __float2bfloat16_rn(y);
+      else ((float*)a.C)[idx + j] = y;
     }
   }
+}
+
+// `cols` columns of one row, from column n on (cols a multiple of 16)
+template <int MODE>
+__device__ __forceinline__ void epilogue_row(const PrefillArgs& a, uint32_t taddr, int row, int n, int cols, bool row_ok) {
+  int c = 0;
+  for (; c + 32 <= cols; c += 32) epilogue_chunk<32, MODE>(a, taddr + c, row, n + c, row_ok);
+  if (c < cols) epilogue_chunk<16, MODE>(a, taddr + c, row, n + c, row_ok);
+}
+__device__ __forceinline__ void epilogue_row_any(const PrefillArgs& a, uint32_t taddr, int row, int n, int cols, bool row_ok) {
+  if (a.mode == 0) epilogue_row<0>(a, taddr, row, n, cols, row_ok);
+  else if (a.mode == 1) epilogue_row<1>(a, taddr, row, n, cols, row_ok);
+  else if (a.mode == 2) epilogue_row<2>(a, taddr, row, n, cols, row_ok);
+  else epilogue_row<3>(a, taddr, row, n, cols, row_ok);
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -304,9 +349,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < args.M;
       const uint32_t taddr = tmem_base + (uint32_t)b * 256u + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
-      int c = 0;
-      for (; c + 32 <= half_cols; c += 32) epilogue_chunk<32>(args, taddr + c, row, n0 + half * half_cols + c, row_ok);
-      if (c < half_cols) epilogue_chunk<16>(args, taddr + c, row, n0 + half * half_cols + c, row_ok);
+      epilogue_row_any(args, taddr, row, n0 + half * half_cols, half_cols, row_ok);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty(b));
@@ -317,6 +360,207 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// ------------------------------------------------- two SMs on one tile --
+//
+// From 129 rows on, two CTAs of a cluster share a tile of 256 rows by BN out features
+// (tcgen05.mma.cta_group::2): each holds its own 128 rows of X and HALF of the tile's rows of
+// W, so per 64-wide K block an SM takes in 16 KB + BN * 64 bytes instead of 16 KB + BN * 128.
+// The product is bound by that traffic, not by the tensor pipe.  CTA 0 of the pair issues every
+// MMA; both CTAs' copies signal CTA 0's "full" barrier (one arrival, the bytes of both);
+// tcgen05.commit with a cluster multicast frees the stage in both CTAs and announces a finished
+// accumulator to both epilogues; both epilogues release an accumulator at CTA 0's barrier.
+// Each CTA's tensor memory holds its own 128 rows of the two accumulators.
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {     // the same offset in CTA `rank`
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// destination in this CTA, completion counted at `cluster_bar` (this CTA's or its partner's barrier)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives at the barrier of this offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+
+constexpr int PAIR_ROWS = 2 * BM;
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const PrefillArgs args) {
+  const int BN = args.BN, STAGES = args.stages;
+  const int HALF_N = BN >> 1;                                   // rows of W per CTA
+  const uint32_t B_BYTES = (uint32_t)HALF_N * BLOCK_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  const uint32_t TX_BYTES = 2u * STAGE_BYTES;                   // both CTAs' copies of a stage
+  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(PAIR_ROWS >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  const uint32_t bars = tiles + SMEM_TILES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
+  auto tmem_full = [&](int b) { return bars + 8u * (2 * MAX_STAGES + b); };
+  auto tmem_empty = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * MAX_STAGES + 4);
+  volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();                          // 0 issues the MMAs
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int total_tiles = args.m_tiles * args.n_tiles;           // m_tiles counts 256-row tiles here
+  const int num_kb = (args.K + BLOCK_K - 1) / BLOCK_K;
+  const int my_tiles = (pair < total_tiles) ? (total_tiles - 1 - pair) / pairs + 1 : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < MAX_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tmem_full(b), 1); mbar_init(tmem_empty(b), 2 * EPI_WARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {      // the same warp in both CTAs: the pair allocates together
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the partner's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_trigger();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int total_it = my_tiles * num_kb;
+      struct Cursor { int tile, kx, m0, n0, kb; };
+      auto place = [&](Cursor& c) {
+        c.m0 = (c.tile / args.n_tiles) * PAIR_ROWS + (int)rank * BM;
+        c.n0 = (c.tile % args.n_tiles) * BN + (int)rank * HALF_N;
+      };
+      auto start = [&]() { Cursor c; c.tile = pair; c.kb = 0; c.kx = 0; place(c); return c; };
+      auto advance = [&](Cursor& c) {
+        c.kx += BLOCK_K;
+        if (++c.kb == num_kb) { c.kb = 0; c.kx = 0; c.tile += pairs; place(c); }
+      };
+      uint32_t full_at_leader[MAX_STAGES];
+#pragma unroll
+      for (int s = 0; s < MAX_STAGES; ++s) full_at_leader[s] = map_to_cta(full_bar(s), 0);
+      const int pre = min(STAGES, total_it);
+      Cursor cw = start();
+      for (int s = 0; s < pre; ++s) {           // weights first: they do not depend on the kernel before
+        if (rank == 0) mbar_expect_tx(full_bar(s), TX_BYTES);
+        tma_load_2d_pair(tiles + s * STAGE_BYTES + A_BYTES, &map_w, cw.kx, cw.n0, full_at_leader[s]);
+        advance(cw);
+      }
+      pdl_wait();
+      Cursor cx = start();
+      for (int s = 0; s < pre; ++s) {
+        tma_load_2d_pair(tiles + s * STAGE_BYTES, &map_x, cx.kx, cx.m0, full_at_leader[s]);
+        advance(cx);
+      }
+      bool ok = true;
+      int s = pre == STAGES ? 0 : pre;
+      uint32_t wait_parity = 0;
+      for (int it = pre; it < total_it; ++it) {
+        ok = mbar_wait(empty_bar(s), wait_parity, args.error, 31);
+        if (!ok) break;
+        if (rank == 0) mbar_expect_tx(full_bar(s), TX_BYTES);
+        const uint32_t dst = tiles + s * STAGE_BYTES;
+        tma_load_2d_pair(dst + A_BYTES, &map_w, cx.kx, cx.n0, full_at_leader[s]);
+        tma_load_2d_pair(dst, &map_x, cx.kx, cx.m0, full_at_leader[s]);
+        advance(cx);
+        if (++s == STAGES) { s = 0; wait_parity ^= 1u; }
+      }
+      // Copies still in flight are waited for by the MMA thread of CTA 0 (it consumes every stage);
+      // if that thread gave up, the epilogues time out, and the cluster barrier at the end holds
+      // both CTAs until every thread has arrived.
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      bool ok = true;
+      int s = 0;
+      uint32_t full_parity = 0;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        const int b = t & 1;
+        if (t >= 2) {
+          ok = mbar_wait(tmem_empty(b), (uint32_t)((t >> 1) & 1) ^ 1u, args.error, 33);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        const uint32_t acc = tmem_base + (uint32_t)b * 256u;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = mbar_wait(full_bar(s), full_parity, args.error, 34);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_src = tiles + s * STAGE_BYTES;
+          const uint64_t da0 = make_desc(a_src), db0 = make_desc(a_src + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / 16; ++k)
+            umma_pair(acc, da0 + (uint64_t)(2 * k), db0 + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(empty_bar(s));
+          if (++s == STAGES) { s = 0; full_parity ^= 1u; }
+        }
+        umma_commit_pair(tmem_full(b));
+      }
+    }
+    __syncwarp();
+  } else {
+    pdl_wait();
+    const int e = warp - 2;
+    const int quarter = warp & 3, half = e >> 2;
+    const int half_cols = BN >> 1;
+    uint32_t empty_at_leader[2] = {map_to_cta(tmem_empty(0), 0), map_to_cta(tmem_empty(1), 0)};
+    bool ok = true;
+    for (int t = 0; t < my_tiles && ok; ++t) {
+      const int b = t & 1;
+      const int tile = pair + t * pairs;
+      const int m0 = (tile / args.n_tiles) * PAIR_ROWS + (int)rank * BM, n0 = (tile % args.n_tiles) * BN;
+      if (lane == 0) ok = mbar_wait(tmem_full(b), (uint32_t)(t >> 1) & 1u, args.error, 35);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < args.M;
+      const uint32_t taddr = tmem_base + (uint32_t)b * 256u + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
+      epilogue_row_any(args, taddr, row, n0 + half * half_cols, half_cols, row_ok);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(empty_at_leader[b]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // neither CTA frees tensor memory, or leaves, while its partner may still use it
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
 }
 
@@ -356,6 +600,8 @@ int setup() {
   if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc_prefill: cudaHostGetDevicePointer: %s", cudaGetErrorString(err));
   err = cudaFuncSetAttribute(gemm_tc_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
   if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc_prefill: shared memory %zu: %s", SMEM_BYTES, cudaGetErrorString(err));
+  err = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc_prefill: shared memory %zu: %s", SMEM_BYTES, cudaGetErrorString(err));
   g_configured = true;
   return 0;
 }
@@ -370,6 +616,13 @@ int encode(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return ayk_fail("ayk_gemm_tc_prefill: cuTensorMapEncodeTiled failed with %d", (int)r);
   return 0;
+}
+
+int epilogue_mode(int act, bool with_residual, bool out_bf16) {
+  if (act == AYK_ACT_NONE && !with_residual && out_bf16) return 0;
+  if (act == AYK_ACT_NONE && !out_bf16) return 1;
+  if (act == AYK_ACT_GELU_TANH && !with_residual && out_bf16) return 2;
+  return 3;
 }
 
 }  // namespace
@@ -393,11 +646,29 @@ AYK_EXPORT int ayk_gemm_tc_prefill_tile(int M, int N, int sms) {
   return best;
 }
 
+// The same for pairs of SMs on tiles of 256 rows (sms / 2 pairs).
+AYK_EXPORT int ayk_gemm_tc_pair_tile(int M, int N, int sms) {
+  int best = 256;
+  long best_cost = -1;
+  const int m_tiles = (M + PAIR_ROWS - 1) / PAIR_ROWS, pairs = sms / 2 > 0 ? sms / 2 : 1;
+  for (int bn = 64; bn <= 256; bn += 32) {
+    const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
+    const long waves = (tiles + pairs - 1) / pairs;
+    // per K block an SM takes in 128 rows of X and bn / 2 rows of W (the bound), plus a fixed cost per tile
+    const long cost = waves * (bn / 2 + 128 + 16);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
 // X [M, K], W [N, K] bfloat16, contiguous, 16-byte aligned, K a multiple of 8; C [M, N]
 // float32 or bfloat16 with N a multiple of 8 (16-byte row segments); bias, residual
 // float32 or null (residual may alias a float32 C).  tile_n: 0 lets the library choose.
+// pair: 1 = two SMs per 256-row tile, 0 = one SM per 128-row tile, -1 = one SM unless the environment
+// variable AYAKA_B200_GEMM_PAIR=1 asks for pairs from 129 rows on (measured equal on the XL shapes:
+// both forms are bound by the tensor pipe's rate per instruction, not by operand traffic).
 AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const float* bias, const float* residual,
-                                   int M, int N, int K, int act, int out_dtype, int tile_n, int sms,
+                                   int M, int N, int K, int act, int out_dtype, int tile_n, int sms, int pair,
                                    cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   AYK_REQUIRE(K >= 8 && K % 8 == 0, "ayk_gemm_tc_prefill: K = %d must be a positive multiple of 8", K);
@@ -405,6 +676,58 @@ AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const 
               (residual == nullptr || (uintptr_t)residual % 16 == 0), "ayk_gemm_tc_prefill: operands must be 16-byte aligned");
   AYK_REQUIRE(out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16, "ayk_gemm_tc_prefill: unknown output dtype %d", out_dtype);
   AYK_REQUIRE(sms >= 1, "ayk_gemm_tc_prefill: sms must be positive");
+  static const int pair_default = getenv("AYAKA_B200_GEMM_PAIR") ? atoi(getenv("AYAKA_B200_GEMM_PAIR")) : 0;
+  const bool use_pair = pair > 0 || (pair < 0 && pair_default && M > BM && sms >= 2);
+  if (use_pair) {
+    AYK_REQUIRE(M > 8 && sms >= 2, "ayk_gemm_tc_prefill: pairs of SMs need more than 8 rows and 2 SMs (got %d, %d)", M, sms);
+    const int BN = tile_n > 0 ? tile_n : ayk_gemm_tc_pair_tile(M, N, sms);
+    AYK_REQUIRE(BN >= 64 && BN <= 256 && BN % 32 == 0, "ayk_gemm_tc_prefill: pair tile width %d is not a multiple of 32 in [64, 256]", BN);
+    {
+      std::lock_guard<std::mutex> lock(g_mutex);
+      if (setup() != 0) return -1;
+    }
+    CUtensorMap mx, mw;
+    const int box_m = M >= BM ? BM : (M + 7) / 8 * 8;
+    AYK_REQUIRE(box_m == BM, "ayk_gemm_tc_prefill: pairs of SMs need at least %d rows", BM);
+    if (encode(&mx, X, M, K, BM) != 0) return -1;
+    {
+      std::lock_guard<std::mutex> lock(g_mutex);
+      MapKey key{W, N, K, BN / 2};
+      auto it = g_weight_maps.find(key);
+      if (it == g_weight_maps.end()) {
+        if (encode(&mw, W, N, K, BN / 2) != 0) return -1;
+        g_weight_maps.emplace(key, mw);
+      } else {
+        mw = it->second;
+      }
+    }
+    PrefillArgs args{};
+    args.C = C; args.bias = bias; args.residual = residual; args.error = g_error_dev;
+    args.M = M; args.N = N; args.K = K; args.act = act; args.out_bf16 = out_dtype == AYK_DTYPE_BF16;
+    args.BN = BN;
+    args.vec_ok = (N % 8 == 0) && (bias == nullptr || (uintptr_t)bias % 16 == 0);
+    args.mode = epilogue_mode(act, residual != nullptr, args.out_bf16);
+    args.box_m = BM;
+    args.m_tiles = (M + PAIR_ROWS - 1) / PAIR_ROWS;
+    args.n_tiles = (N + BN - 1) / BN;
+    const int stages = SMEM_TILES / (A_BYTES + (BN / 2) * BLOCK_K * 2);
+    args.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
+    const int total = args.m_tiles * args.n_tiles, pairs = sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (total < pairs ? total : pairs));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ayk_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mx, mw, args);
+    return ayk_check_launch("ayk_gemm_tc_prefill (pairs)");
+  }
   int BN = tile_n > 0 ? tile_n : ayk_gemm_tc_prefill_tile(M, N, sms);
   AYK_REQUIRE(BN >= 32 && BN <= 256 && BN % 32 == 0, "ayk_gemm_tc_prefill: tile width %d is not a multiple of 32 in [32, 256]", BN);
   {
@@ -429,6 +752,8 @@ AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const 
   args.C = C; args.bias = bias; args.residual = residual; args.error = g_error_dev;
   args.M = M; args.N = N; args.K = K; args.act = act; args.out_bf16 = out_dtype == AYK_DTYPE_BF16;
   args.BN = BN;
+  args.vec_ok = (N % 8 == 0) && (bias == nullptr || (uintptr_t)bias % 16 == 0);
+  args.mode = epilogue_mode(act, residual != nullptr, args.out_bf16);
   args.box_m = box_m;
   args.m_tiles = (M + BM - 1) / BM;
   args.n_tiles = (N + BN - 1) / BN;

@@ -294,9 +294,11 @@ PREFILL_ROWS = 16        # more rows than this: the kernel with 128-row tiles an
 def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
                     activation: str = "none", residual: torch.Tensor | None = None,
                     out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
-                    tile_n: int = 0) -> torch.Tensor:
+                    tile_n: int = 0, pair: bool | None = None) -> torch.Tensor:
     """act(a[M,K] @ w[N,K]^T + bias) (+ residual) for many rows: persistent tcgen05
-    kernel, epilogue of a tile under the main loop of the next."""
+    kernel, epilogue of a tile under the main loop of the next.  ``pair``: two SMs
+    on a 256-row tile (tcgen05 cta_group::2) or one SM on a 128-row tile (the default;
+    AYAKA_B200_GEMM_PAIR=1 makes pairs the default from 129 rows on)."""
     lib = _ready()
     M, K = a.shape
     N = w.shape[0]
@@ -314,7 +316,7 @@ def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None 
     _launch(lib.ayk_gemm_tc_prefill(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
                                     ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]),
                                     ctypes.c_int(_tag(out_dtype)), ctypes.c_int(tile_n), ctypes.c_int(SM_COUNT),
-                                    _stream()))
+                                    ctypes.c_int(-1 if pair is None else int(pair)), _stream()))
     return out
 
 

@@ -368,7 +368,8 @@ PREFILL_GEMM_CASES = [
 
 @pytest.mark.parametrize("M,N,K,tile_n", PREFILL_GEMM_CASES)
 @pytest.mark.parametrize("act,out_dtype", [("none", "float32"), ("gelu_tanh", "bfloat16")])
-def test_gemm_tcgen05_many_rows(M, N, K, tile_n, act, out_dtype):
+@pytest.mark.parametrize("pair", [False, True], ids=["one_sm", "two_sms"])
+def test_gemm_tcgen05_many_rows(M, N, K, tile_n, act, out_dtype, pair):
     from ayaka_py_b200 import ops
     rs = np.random.RandomState(12)
     a, w = rs.randn(M, K).astype(np.float32), (rs.randn(N, K) / np.sqrt(K)).astype(np.float32)
@@ -379,13 +380,13 @@ def test_gemm_tcgen05_many_rows(M, N, K, tile_n, act, out_dtype):
         y = plain_gpt2.activation("gelu_new", y)
     want = y + res
     R = dev(res)
-    out = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=DTYPES[out_dtype], tile_n=tile_n)
+    out = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=DTYPES[out_dtype], tile_n=tile_n, pair=pair)
     torch.cuda.synchronize()
     assert ops.tc_error() == 0
     err = np.abs(out.float().cpu().numpy() - want).max()
     assert err < (1e-3 if out_dtype == "float32" else 5e-2), err
     if out_dtype == "float32":
-        again = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=torch.float32, out=R, tile_n=tile_n)   # in place
+        again = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=torch.float32, out=R, tile_n=tile_n, pair=pair)   # in place
         assert torch.equal(again, out) and ops.tc_error() == 0
         few = ops.gemm_tc(A[:64].contiguous(), W, dev(bias), act, dev(res[:64]), out_dtype=torch.float32, splits=1)
         assert float((few - out[:64]).abs().max()) < 1e-4                     # the few-row kernel agrees

@@ -155,6 +155,7 @@ struct EpilogueArgs {
   int M, N, K;
   int act, out_bf16;
   int kb_per_split;
+  int kb_base, kb_rem;        // cluster form: split z takes kb_base K blocks, one more if z < kb_rem
   long long* trace;          // cycle marks of CTA (0,0,0) when built with -DAYK_TRACE, else unused
 };
 
@@ -208,7 +209,27 @@ __device__ __forceinline__ void store_chunk_pre(const EpilogueArgs& a, int tok0,
   }
 }
 
-template <int BT>
+// Split-K inside a thread-block cluster (up to 16 rows, 2, 4 or 8 splits): the CTAs that share an
+// output tile are one cluster along z.  Each owns 128 / splits of the tile's out features: every
+// epilogue thread sends its 16 partial sums straight into the owner's shared memory
+// (st.shared::cluster), one cluster barrier later the owner adds the `splits` partials in split
+// order and finishes its rows.  No scratch in global memory, no fence, no counter, no second pass
+// through L2; measured against the scratch form inside the decode graph this takes the product
+// from about 10 to 7.5 us.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int BT, bool CLUSTER = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const EpilogueArgs args) {
@@ -228,13 +249,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 1);
   volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
   volatile int* flag_ptr = (volatile int*)(smem_raw + (tmem_slot + 4 - raw));
+  // cluster form: [split][row of this CTA's share][16 tokens] partial sums, 8 KB
+  const uint32_t red = (tmem_slot + 8u + 15u) & ~15u;
+  const float* red_ptr = (const float*)(smem_raw + (red - raw));
 
   if (threadIdx.x == 0) mark(args, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BLOCK_N, t0 = blockIdx.y * BT;
   const int total_kb = (args.K + BLOCK_K - 1) / BLOCK_K;
-  const int kb_begin = blockIdx.z * args.kb_per_split;
-  const int num_kb = min(total_kb, kb_begin + args.kb_per_split) - kb_begin;   // >= 1 by the host's choice
+  const int kb_begin = CLUSTER ? (int)blockIdx.z * args.kb_base + min((int)blockIdx.z, args.kb_rem)
+                               : (int)blockIdx.z * args.kb_per_split;
+  const int num_kb = CLUSTER ? args.kb_base + ((int)blockIdx.z < args.kb_rem ? 1 : 0)
+                             : min(total_kb, kb_begin + args.kb_per_split) - kb_begin;   // >= 1 by the host's choice
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -255,6 +281,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot_ptr;
   if (threadIdx.x == 0) mark(args, 1);
   pdl_trigger();     // the next kernel may be scheduled; it waits for this one before it touches its data
+
+  // cluster form: what the epilogue threads carry across the cluster barrier
+  [[maybe_unused]] bool share_ok = false;
+  [[maybe_unused]] float share_bias[8], share_res[8];
 
   if (warp == 0) {
     if (lane == 0) {
@@ -327,6 +357,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int quarter = warp & 3;
     const int n = n0 + quarter * 32 + lane;
     pdl_wait();        // residual, partials and C belong to kernels before this one until here
+    if constexpr (CLUSTER) {
+      // This thread's part of the CTA's share: token e % 16 of rows e / 16 + 8 i (see below).
+      const int splits = gridDim.z, rows_per = BLOCK_N / splits, e = threadIdx.x - 64;
+      const int tok = t0 + (e & 15);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = (e >> 4) + 8 * i;
+        const int nn = n0 + (int)blockIdx.z * rows_per + row;
+        const bool mine = row < rows_per && nn < args.N;
+        share_bias[i] = (mine && args.bias) ? args.bias[nn] : 0.f;
+        share_res[i] = (mine && args.residual && tok < args.M) ? args.residual[(size_t)tok * args.N + nn] : 0.f;
+      }
+      share_ok = mbar_wait(tmem_full_bar, 0u, args.error, 4);
+      tc_fence_after();
+      if (share_ok) {
+        uint32_t r[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // row `local` of the tile belongs to CTA local / rows_per of the cluster; its 16 sums go to
+        // [this split][local % rows_per][0..15] of that CTA's buffer
+        const int local = quarter * 32 + lane;
+        const uint32_t dst = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + local % rows_per) * 16) * 4),
+                                        (uint32_t)(local / rows_per));
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          st_cluster_v4(dst + 16u * q, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+      }
+    } else {
     // Bias and the residual of the first 16 tokens are fetched while the main loop runs.
     const float bias_pre = (args.bias && n < args.N) ? args.bias[n] : 0.f;
     float res_pre[16];
@@ -420,8 +479,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
       }
     }
+    }   // !CLUSTER
   }
 
+  if constexpr (CLUSTER) {
+    // Every thread of every CTA of the cluster: the partial sums have landed in their owners.
+    cluster_sync_all();
+    if (warp >= 2 && share_ok) {
+      const int splits = gridDim.z, rows_per = BLOCK_N / splits, e = threadIdx.x - 64;
+      const int tok = t0 + (e & 15);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = (e >> 4) + 8 * i;
+        const int nn = n0 + (int)blockIdx.z * rows_per + row;
+        if (row < rows_per && nn < args.N && tok < args.M) {
+          float v = 0.f;
+          for (int z = 0; z < splits; ++z) v += red_ptr[((z * rows_per + row) * 16) + (e & 15)];     // split order
+          const float y = apply_activation(v + share_bias[i], args.act) + share_res[i];
+          const size_t idx = (size_t)tok * args.N + nn;
+          if (args.out_bf16) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(y);
+          else ((float*)args.C)[idx] = y;
+        }
+      }
+    }
+  }
   if (threadIdx.x == 64) mark(args, 7);
   tc_fence_before();
   __syncthreads();
@@ -497,6 +578,33 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& arg
   return ayk_check_launch("ayk_gemm_tc");
 }
 
+// Up to 16 rows, the CTAs of an output tile as one cluster along z.
+int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& args, int splits, cudaStream_t stream) {
+  constexpr int BT = 16;
+  constexpr int STAGES = stages_for(BT);
+  constexpr size_t SMEM = 1024 + (size_t)STAGES * (A_BYTES + BT * BLOCK_K * 2) + 8 * (2 * STAGES + 2) + 16 + BLOCK_N * 16 * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+    if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: shared memory %zu: %s", SMEM, cudaGetErrorString(err));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((args.N + BLOCK_N - 1) / BLOCK_N, 1, splits);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ayk_pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BT, true>, mw, mx, args);
+  return ayk_check_launch("ayk_gemm_tc (cluster)");
+}
+
 }  // namespace
 
 // 0 when the kernel takes this shape; otherwise a text in ayk_last_error().
@@ -520,10 +628,12 @@ AYK_EXPORT long long ayk_gemm_tc_scratch_floats(int M, int N, int splits) {
 // X [M, K] and W [N, K] bfloat16 (contiguous, 16-byte aligned); C [M, N] float32
 // or bfloat16; bias, residual float32 or null (residual may alias a float32 C).
 // splits > 1 needs `partials` (ayk_gemm_tc_scratch_floats) and `counters` (one
-// zeroed unsigned per output tile; the kernel leaves them zero).
+// zeroed unsigned per output tile; the kernel leaves them zero), unless cluster != 0: then the
+// splits of a tile are one thread-block cluster and exchange their sums through shared memory
+// (up to 16 rows; 2, 4 or 8 splits; at least one K block each), and no scratch is touched.
 AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* bias, const float* residual,
                            int M, int N, int K, int act, int out_dtype, int splits, float* partials,
-                           unsigned int* counters, int weight_is_static, cudaStream_t stream) {
+                           unsigned int* counters, int weight_is_static, int cluster, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (ayk_gemm_tc_supported(M, N, K) != 0) return -1;
   AYK_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "ayk_gemm_tc: operands must be 16-byte aligned");
@@ -531,9 +641,14 @@ AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* b
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   if (splits < 1) splits = 1;
   if (splits > total_kb) splits = total_kb;
+  if (cluster) {
+    AYK_REQUIRE(M <= 16 && (splits == 2 || splits == 4 || splits == 8) && total_kb >= splits,
+                "ayk_gemm_tc: the cluster form takes up to 16 rows and 2, 4 or 8 splits of at least one K block (rows %d, splits %d, K blocks %d)",
+                M, splits, total_kb);
+  }
   int kb_per_split = (total_kb + splits - 1) / splits;
-  splits = (total_kb + kb_per_split - 1) / kb_per_split;       // no empty split
-  AYK_REQUIRE(splits == 1 || (partials && counters), "ayk_gemm_tc: split-K needs scratch");
+  if (!cluster) splits = (total_kb + kb_per_split - 1) / kb_per_split;       // no empty split
+  AYK_REQUIRE(splits == 1 || cluster || (partials && counters), "ayk_gemm_tc: split-K needs scratch");
   AYK_REQUIRE(splits <= 65535, "ayk_gemm_tc: too many splits");
   {
     std::lock_guard<std::mutex> lock(g_mutex);
@@ -556,7 +671,9 @@ AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* b
     return -1;
   }
   if (encode(&mx, X, M, K, BT) != 0) return -1;
-  EpilogueArgs args{C, bias, residual, partials, counters, g_error_dev, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split, g_trace};
+  EpilogueArgs args{C, bias, residual, partials, counters, g_error_dev, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split,
+                    total_kb / splits, total_kb % splits, g_trace};
+  if (cluster) return launch_cluster(mw, mx, args, splits, stream);
   switch (BT) {
     case 16: return launch<16>(mw, mx, args, splits, stream);
     case 32: return launch<32>(mw, mx, args, splits, stream);
@@ -658,7 +775,7 @@ AYK_EXPORT int ayk_gemm_tc_no_alloc(void* C, const void* X, const void* W, const
   CUtensorMap mw, mx;
   if (no_alloc_encode(&mw, W, N, K, BLOCK_N) != 0) return -1;
   if (no_alloc_encode(&mx, X, M, K, BT) != 0) return -1;
-  EpilogueArgs args{C, bias, residual, d.partials, d.counters, d.error, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split, g_trace};
+  EpilogueArgs args{C, bias, residual, d.partials, d.counters, d.error, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split, 0, 0, g_trace};
   switch (BT) {
     case 16: return launch<16>(mw, mx, args, splits, stream);
     case 32: return launch<32>(mw, mx, args, splits, stream);

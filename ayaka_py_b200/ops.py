@@ -230,12 +230,15 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None,
 # ------------------------------------------------------------- dispatchers --
 
 _tc_scratch: dict = {}
+_tc_retired: list = []          # a captured CUDA graph may still write to an outgrown buffer
 SM_COUNT = 148
 
 
 def _tc_workspace(device, floats: int):
     ws = _tc_scratch.get(device)
     if ws is None or ws[0].numel() < floats:
+        if ws is not None:
+            _tc_retired.append(ws[0])
         partials = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
         counters = ws[1] if ws is not None else torch.zeros(8192, dtype=torch.int32, device=device)
         ws = (partials, counters)
@@ -245,20 +248,28 @@ def _tc_workspace(device, floats: int):
 
 def tc_splits(M: int, N: int, K: int) -> int:
     """Split-K factor of the tensor-core product: skinny products (few output
-    tiles) are cut along K so that about one CTA per SM streams the weight."""
+    tiles) are cut along K so that about one CTA per SM streams the weight.
+    Up to 16 rows the factor is 1, 2, 4 or 8: those splits form a cluster."""
     bt = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
     tiles = -(-N // 128) * -(-M // bt)
     blocks = -(-K // 64)
-    if tiles >= SM_COUNT // 2 or blocks < 4 or M > 16:
+    if tiles >= SM_COUNT or blocks < 4 or M > 16:
         return 1          # more than 16 rows: the partial sums cost more than the split saves (measured)
-    return max(1, min(SM_COUNT // tiles, blocks // 2, 8))
+    for p in (8, 4, 2):
+        if tiles * p <= SM_COUNT * 14 // 10 and blocks >= 2 * p:
+            return p
+    return 1
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
             activation: str = "none", residual: torch.Tensor | None = None,
             out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
-            splits: int | None = None, static_weight: bool = True) -> torch.Tensor:
-    """act(a[M,K] @ w[N,K]^T + bias) (+ residual), bfloat16 operands, on tcgen05."""
+            splits: int | None = None, static_weight: bool = True, cluster: bool | None = None) -> torch.Tensor:
+    """act(a[M,K] @ w[N,K]^T + bias) (+ residual), bfloat16 operands, on tcgen05.
+    ``splits``: CTAs along K per output tile (default: chosen by shape).  ``cluster``:
+    the splits exchange their sums through shared memory of a thread-block cluster
+    instead of scratch in global memory (default where it applies: up to 16 rows,
+    2, 4 or 8 splits)."""
     lib = _ready()
     M, K = a.shape
     N = w.shape[0]
@@ -275,8 +286,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         raise KernelError("residual must have the output's shape")
     if splits is None:
         splits = tc_splits(M, N, K)
+    can_cluster = M <= 16 and splits in (2, 4, 8) and -(-K // 64) >= splits
+    if cluster is None:
+        cluster = can_cluster
+    elif cluster and not can_cluster:
+        raise KernelError(f"gemm_tc: the cluster form takes up to 16 rows and 2, 4 or 8 splits (rows {M}, splits {splits})")
     partials = counters = None
-    if splits > 1:
+    if splits > 1 and not cluster:
         tiles = -(-N // 128) * -(-M // 16)
         partials, counters = _tc_workspace(a.device, splits * M * N)
         if tiles > counters.numel():
@@ -284,7 +300,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     _launch(lib.ayk_gemm_tc(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
                            ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]),
                            ctypes.c_int(_tag(out_dtype)), ctypes.c_int(splits), _ptr(partials), _ptr(counters),
-                           ctypes.c_int(1 if static_weight else 0), _stream()))
+                           ctypes.c_int(1 if static_weight else 0), ctypes.c_int(1 if cluster else 0), _stream()))
     return out
 
 

@@ -229,6 +229,7 @@ TC_CASES = [
     (1, 128, 64, 1), (5, 50, 72, 1), (16, 257, 200, 1), (17, 384, 1000, 1), (64, 96, 320, 1),
     (100, 1003, 328, 1), (300, 200, 1600, 1), (8, 1600, 1600, None), (64, 1600, 6400, None),
     (3, 130, 512, 4), (40, 300, 1000, 7), (8, 64, 64, 3),
+    (16, 300, 1600, 8), (1, 1600, 6400, 2), (5, 257, 520, 8), (9, 50257 // 16, 128, 2),      # splits as one cluster
 ]
 
 

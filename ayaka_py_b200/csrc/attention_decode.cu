@@ -212,7 +212,6 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
                   const int* __restrict__ table, int table_stride, const int* __restrict__ req_pos0,
                   int H, int Hkv, int page_shift, float scale_log2, int window, int parts, int chunks, int rows) {
   pdl_trigger();
-  pdl_wait();
   static_assert(WARPS * 32 == PART, "each warp owns 32 keys of the partition");
   constexpr int KS = DH / 16;                    // k steps of the first product
   constexpr int PPR = DH / 8;                    // 16-byte pieces per row
@@ -227,12 +226,21 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   const int group = H / Hkv;
   const int head0 = kvh * group + chunk * 8;               // the query head of A row 0
   const int rows_here = min(rows, group - chunk * 8);
+  // Positions and block table are the step's inputs: they are read while the kernels before this one
+  // (the product that makes q, k, v and the append to the cache) may still be running.
   const int pos = req_pos0[r];
   const int page_size = 1 << page_shift;
+  const int wk0 = part * PART + warp * 32;       // this warp's first key
+  // pages of this warp's keys: lane l holds the page of keys [wk0 + l * page_size, ...)
+  const int first_logical = wk0 >> page_shift;
+  int my_page = 0;
+  if (lane < ((32 + page_size - 1) >> page_shift) && first_logical + lane < table_stride)
+    my_page = table[(size_t)r * table_stride + first_logical + lane];
   int k_lo = part * PART;
   const int k_hi = min(pos + 1, k_lo + PART);
   if (window > 0) k_lo = max(k_lo, pos - window + 1);
   const bool empty = k_lo >= k_hi;               // the same for the whole CTA
+  pdl_wait();
   if (empty && (int)threadIdx.x < rows_here) {
     float* dst = scratch + ((size_t)(r * H + head0 + threadIdx.x) * parts + part) * (DH + 2);
     dst[DH] = -INFINITY; dst[DH + 1] = 0.f;
@@ -242,7 +250,6 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   const uint32_t vs_base = ks_base + PART * ROW_BYTES;
   float* comb = reinterpret_cast<float*>(smem_dyn + 2 * PART * ROW_BYTES);      // [WARPS][rows][DH + 2]
 
-  const int wk0 = part * PART + warp * 32;       // this warp's first key
   const int w_lo = max(k_lo, wk0), w_hi = min(k_hi, wk0 + 32);
   const bool warp_has_keys = !empty && w_lo < w_hi;
   float m_w = -INFINITY, l_w = 0.f;
@@ -251,11 +258,6 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   for (int j = 0; j < NT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
 
   if (warp_has_keys) {
-    // pages of this warp's keys: lane l holds the page of keys [wk0 + l * page_size, ...)
-    const int first_logical = wk0 >> page_shift;
-    int my_page = 0;
-    if (lane < ((32 + page_size - 1) >> page_shift) && first_logical + lane < table_stride)
-      my_page = table[(size_t)r * table_stride + first_logical + lane];
     const size_t row_elems = (size_t)Hkv * DH;
     const size_t head_off = (size_t)kvh * DH;
     // copies: lane covers piece (lane % PPR) of rows (lane / PPR) + i * (32 / PPR)   [PPR <= 32]

@@ -182,6 +182,57 @@ layernorm_warp_kernel(O* __restrict__ out, const float* __restrict__ x, const fl
   }
 }
 
+// Few rows (a decode step): one block of 128 threads per row, the row in registers.  The kernel
+// sits on the critical path between two products, so what does not depend on the kernel before
+// it (weight and bias of the norm, the row index) is fetched before the programmatic-launch wait,
+// and the row is read with every load in flight at once.
+template <typename O>
+__global__ void __launch_bounds__(128)
+layernorm_row_kernel(O* __restrict__ out, const float* __restrict__ x, const float* __restrict__ gamma,
+                     const float* __restrict__ beta, const int* __restrict__ rows, int d, float eps) {
+  __shared__ float red[32];
+  pdl_trigger();
+  constexpr int HELD = 4;                        // float4 per thread: widths up to 2048
+  const int r = blockIdx.x, nv = d >> 2;
+  const float4* g4 = reinterpret_cast<const float4*>(gamma);
+  const float4* b4 = reinterpret_cast<const float4*>(beta);
+  float4 g[HELD], b[HELD], v[HELD];
+#pragma unroll
+  for (int i = 0; i < HELD; ++i) {
+    const int idx = threadIdx.x + 128 * i;
+    g[i] = idx < nv ? __ldg(g4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+    b[i] = (idx < nv && beta) ? __ldg(b4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const int src_row = rows ? rows[r] : r;
+  pdl_wait();
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)src_row * d);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < HELD; ++i) {
+    const int idx = threadIdx.x + 128 * i;
+    v[i] = idx < nv ? src[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  const float mean = block_sum(s, red) / (float)d;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < HELD; ++i) {
+    if (threadIdx.x + 128 * i < nv) {
+      const float a = v[i].x - mean, bb = v[i].y - mean, c = v[i].z - mean, e = v[i].w - mean;
+      q += (a * a + bb * bb) + (c * c + e * e);
+    }
+  }
+  const float rstd = rsqrtf(block_sum(q, red) / (float)d + eps);
+  O* dst = out + (size_t)r * d;
+#pragma unroll
+  for (int i = 0; i < HELD; ++i) {
+    const int idx = threadIdx.x + 128 * i;
+    if (idx < nv)
+      store4(dst + 4 * idx, (v[i].x - mean) * rstd * g[i].x + b[i].x, (v[i].y - mean) * rstd * g[i].y + b[i].y,
+             (v[i].z - mean) * rstd * g[i].z + b[i].z, (v[i].w - mean) * rstd * g[i].w + b[i].w);
+  }
+}
+
 // out[r, :] = LayerNorm(x[rows ? rows[r] : r, :]); x float32, statistics and
 // affine in 32-bit, result stored as out_dtype.
 AYK_EXPORT int ayk_layernorm(void* out, const float* x, const float* gamma, const float* beta,
@@ -204,6 +255,13 @@ AYK_EXPORT int ayk_layernorm(void* out, const float* x, const float* gamma, cons
     }
     return ayk_check_launch("ayk_layernorm");
   }
+  if (aligned && d <= 2048 && (out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16)) {
+    if (out_dtype == AYK_DTYPE_F32)
+      ayk_launch(layernorm_row_kernel<float>, dim3(n_rows), dim3(128), 0, stream, (float*)out, x, gamma, beta, rows, d, eps);
+    else
+      ayk_launch(layernorm_row_kernel<__nv_bfloat16>, dim3(n_rows), dim3(128), 0, stream, (__nv_bfloat16*)out, x, gamma, beta, rows, d, eps);
+    return ayk_check_launch("ayk_layernorm");
+  }
   int threads = d >= 1024 ? 256 : 128;
   size_t smem = (size_t)d * sizeof(float);
   if (out_dtype == AYK_DTYPE_F32)
@@ -223,10 +281,11 @@ __global__ void kv_append_kernel(T* __restrict__ kcache, T* __restrict__ vcache,
                                  const int* __restrict__ table, int table_stride, int page_size,
                                  int width) {
   pdl_trigger();
-  pdl_wait();
+  // positions and block table are the step's inputs, not the work of the kernel before this one
   int t = blockIdx.x;
   int p = pos[t];
   int page = table[(size_t)row_req[t] * table_stride + p / page_size];
+  pdl_wait();
   if (page <= 0) return;   // the padding page holds nothing; a live row never maps to it
   size_t dst = ((size_t)page * page_size + (p % page_size)) * width;
   const T* ks = k + (size_t)t * row_stride;

@@ -356,17 +356,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // Epilogue: warp w may read TMEM lanes 32 * (w % 4) ... + 31.
     const int quarter = warp & 3;
     const int n = n0 + quarter * 32 + lane;
-    pdl_wait();        // residual, partials and C belong to kernels before this one until here
     if constexpr (CLUSTER) {
       // This thread's part of the CTA's share: token e % 16 of rows e / 16 + 8 i (see below).
       const int splits = gridDim.z, rows_per = BLOCK_N / splits, e = threadIdx.x - 64;
       const int tok = t0 + (e & 15);
 #pragma unroll
+      for (int i = 0; i < 8; ++i) {               // the bias is a weight: no need to wait for it
+        const int row = (e >> 4) + 8 * i;
+        const int nn = n0 + (int)blockIdx.z * rows_per + row;
+        share_bias[i] = (row < rows_per && nn < args.N && args.bias) ? __ldg(args.bias + nn) : 0.f;
+      }
+      pdl_wait();      // residual and C belong to kernels before this one until here
+#pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int row = (e >> 4) + 8 * i;
         const int nn = n0 + (int)blockIdx.z * rows_per + row;
         const bool mine = row < rows_per && nn < args.N;
-        share_bias[i] = (mine && args.bias) ? args.bias[nn] : 0.f;
         share_res[i] = (mine && args.residual && tok < args.M) ? args.residual[(size_t)tok * args.N + nn] : 0.f;
       }
       share_ok = mbar_wait(tmem_full_bar, 0u, args.error, 4);
@@ -386,6 +391,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
       }
     } else {
+    pdl_wait();        // residual, partials and C belong to kernels before this one until here
     // Bias and the residual of the first 16 tokens are fetched while the main loop runs.
     const float bias_pre = (args.bias && n < args.N) ? args.bias[n] : 0.f;
     float res_pre[16];

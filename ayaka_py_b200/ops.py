@@ -256,7 +256,7 @@ def tc_splits(M: int, N: int, K: int) -> int:
     if tiles >= SM_COUNT or blocks < 4 or M > 16:
         return 1          # more than 16 rows: the partial sums cost more than the split saves (measured)
     for p in (8, 4, 2):
-        if tiles * p <= SM_COUNT * 14 // 10 and blocks >= 2 * p:
+        if tiles * p <= SM_COUNT * 14 // 10 and blocks >= p:
             return p
     return 1
 

@@ -369,9 +369,13 @@ def _decode_buffer(device, floats: int) -> torch.Tensor:
 
 def attention_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, table: torch.Tensor,
                      req_pos0: torch.Tensor, num_heads: int, scale: float, window: int | None,
-                     max_context: int, out: torch.Tensor | None = None) -> torch.Tensor:
+                     max_context: int, out: torch.Tensor | None = None,
+                     append: tuple | None = None) -> torch.Tensor:
     """One query row per request over its pages, split along the context and
-    merged.  ``max_context``: the longest context the engine allows (fixes the grid)."""
+    merged.  ``max_context``: the longest context the engine allows (fixes the grid).
+    ``append`` = (k, v, row_req): this step's key and value rows, not yet in the
+    cache; they are stored at each request's position on the way (inside the
+    attention kernel where it can, else by the append kernel first)."""
     lib = _ready()
     pages, P, Hkv, Dh = kcache.shape
     R = q.shape[0]
@@ -383,11 +387,21 @@ def attention_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor
     scratch = _decode_buffer(q.device, R * num_heads * parts * (Dh + 2))
     if out is None:
         out = torch.empty((R, num_heads * Dh), dtype=q.dtype, device=q.device)
+    k_new = v_new = row_req = None
+    new_stride = 0
+    if append is not None:
+        k_new, v_new, row_req = append
+        if (k_new.shape != (R, Hkv * Dh) or v_new.shape != k_new.shape or k_new.stride(1) != 1 or v_new.stride(1) != 1
+                or k_new.stride(0) != v_new.stride(0) or k_new.dtype != kcache.dtype or v_new.dtype != kcache.dtype):
+            raise KernelError("attention_decode: new keys and values must be [R, kv_heads*head_dim] slices of one matrix")
+        new_stride = k_new.stride(0)
     _launch(lib.ayk_attention_decode(_ptr(out), _ptr(q), ctypes.c_int(q.stride(0)), _ptr(kcache), _ptr(vcache),
                                      _ptr(_i32(table, "table")), ctypes.c_int(table.stride(0)),
                                      _ptr(_i32(req_pos0, "req_pos0")), ctypes.c_int(R), ctypes.c_int(num_heads),
                                      ctypes.c_int(Hkv), ctypes.c_int(Dh), ctypes.c_int(P), ctypes.c_float(scale),
                                      ctypes.c_int(window or 0), ctypes.c_int(parts), _ptr(scratch),
+                                     _ptr(k_new), _ptr(v_new), ctypes.c_int(new_stride),
+                                     _ptr(_i32(row_req, "row_req") if row_req is not None else None),
                                      ctypes.c_int(_tag(q.dtype)), _stream()))
     global launches
     launches += 1            # the call launches two kernels (partitions, merge)
@@ -434,14 +448,18 @@ def tc_error() -> int:
 
 
 def attention(q, kcache, vcache, table, ctx, num_heads: int, scale: float,
-              window: int | None = None) -> torch.Tensor:
+              window: int | None = None, append: tuple | None = None) -> torch.Tensor:
     """Attention of the step's rows (``ctx`` gives the rows of each request): the
     split-context decode kernels when every request brings one row; the
     tensor-core kernel for prompt portions in bfloat16 with head size 64; else
-    the general kernel."""
+    the general kernel.  ``append`` = (k, v): the rows' keys and values, which
+    go into the cache first (in a decode step, inside the attention kernel)."""
     if ctx.max_q_len == 1:
         return attention_decode(q, kcache, vcache, table, ctx.req_pos0, num_heads, scale, window,
-                                ctx.cache.max_len)
+                                ctx.cache.max_len,
+                                append=(append[0], append[1], ctx.row_req) if append is not None else None)
+    if append is not None:
+        kv_append(kcache, vcache, append[0], append[1], ctx.row_req, ctx.positions, table)
     if attention_tc_takes(q, kcache):
         return attention_tc(q, kcache, vcache, table, ctx.req_q_start, ctx.req_pos0, ctx.num_rows,
                             num_heads, scale, window)

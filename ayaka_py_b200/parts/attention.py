@@ -60,9 +60,8 @@ class Attention(Mixer):
             rotate(q, k, self.num_heads, self.kv_heads, self.head_dim, ctx)
         kcache, vcache = ctx.cache.kv_layer(cache.group, cache.layer)
         table = ctx.tables[cache.group]
-        if cache.writes:
-            ops.kv_append(kcache, vcache, k, v, ctx.row_req, ctx.positions, table)
-        o = ops.attention(q, kcache, vcache, table, ctx, self.num_heads, self.scale, self.window)
+        o = ops.attention(q, kcache, vcache, table, ctx, self.num_heads, self.scale, self.window,
+                          append=(k, v) if cache.writes else None)
         return ops.linear(o, self.out_weight, self.out_bias, residual=residual,
                           out_dtype=torch.float32, out=residual)
 

@@ -295,17 +295,24 @@ DECODE_CASES = [
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("case", DECODE_CASES)
-def test_decode_attention_split_and_merge(dtype, case):
+@pytest.mark.parametrize("max_context", [1024, 2048], ids=["8_parts", "16_parts"])
+def test_decode_attention_split_and_merge(dtype, case, max_context):
     from ayaka_py_b200 import ops
     ctxs, H, Hkv, Dh, P, window = case
     rs = np.random.RandomState(8)
     x, plain = paged_case(rs, [1] * len(ctxs), ctxs, H, Hkv, Dh, P, dtype)
     scale = 1.3 / np.sqrt(Dh)
+    kc2, vc2 = x["kc"].clone(), x["vc"].clone()
     ops.kv_append(x["kc"], x["vc"], x["k"], x["v"], x["row_req"], x["pos"], x["table"])
-    out = ops.attention_decode(x["q"], x["kc"], x["vc"], x["table"], x["pos0"], H, scale, window, 1024)
+    out = ops.attention_decode(x["q"], x["kc"], x["vc"], x["table"], x["pos0"], H, scale, window, max_context)
     assert np.abs(out.float().cpu().numpy() - plain(scale, window)).max() < tol(dtype)
     general = ops.attention_simt(x["q"], x["kc"], x["vc"], x["table"], x["q_start"], x["pos0"], len(ctxs), H, scale, window)
     assert np.abs(out.float().cpu().numpy() - general.float().cpu().numpy()).max() < tol(dtype)
+    # the same with the step's keys and values filed by the attention call itself
+    fused = ops.attention_decode(x["q"], kc2, vc2, x["table"], x["pos0"], H, scale, window, max_context,
+                                 append=(x["k"], x["v"], x["row_req"]))
+    assert torch.equal(fused, out)
+    assert torch.equal(kc2, x["kc"]) and torch.equal(vc2, x["vc"])
 
 
 @pytest.mark.parametrize("kpos", [0, 127, 128, 383, 384])

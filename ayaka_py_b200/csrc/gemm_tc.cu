@@ -43,11 +43,12 @@ constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2;
 constexpr int THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
-// Up to 32 rows: 4 stages of 18-20 KB leave room for three CTAs per SM, so that the next
-// kernel's CTAs (launched early, see pdl_wait) can start streaming their weights beside
-// the CTAs of the kernel before them.  64 rows are not split along K (the partial sums
-// would cost more than they save), so few CTAs stream a lot each: a deep ring of 8 stages.
-constexpr int stages_for(int bt) { return bt >= 256 ? 4 : (bt >= 128 ? 6 : (bt >= 64 ? 8 : 4)); }
+// Up to 32 rows: 5 stages of 18-20 KB, about 100 KB per CTA, leave room for two CTAs per SM, so that
+// the next kernel's CTAs (launched early, see pdl_wait) stream their weights beside the CTAs of the
+// kernel before them.  Measured in a decode step at 8 requests: 3, 4, 5 stages give 3350, 3480, 3530
+// tokens/s; 6 or 7 stages (one CTA per SM, no overlap with the kernel before) 2970.  64 rows are not
+// split along K, so few CTAs stream a lot each: a deep ring of 8 stages.
+constexpr int stages_for(int bt) { return bt >= 256 ? 4 : (bt >= 128 ? 6 : (bt >= 64 ? 8 : 5)); }
 constexpr int tmem_cols_for(int bt) { return bt < 32 ? 32 : bt; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -50,6 +50,8 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;
 // split along K, so few CTAs stream a lot each: a deep ring of 8 stages.
 constexpr int stages_for(int bt) { return bt >= 256 ? 4 : (bt >= 128 ? 6 : (bt >= 64 ? 8 : 5)); }
 constexpr int tmem_cols_for(int bt) { return bt < 32 ? 32 : bt; }
+// The cluster form adds 128 * BT floats for the exchange of partial sums and still wants two CTAs per SM.
+constexpr int cluster_stages_for(int bt) { return bt >= 64 ? 3 : (bt >= 32 ? 4 : 5); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -210,9 +212,9 @@ __device__ __forceinline__ void store_chunk_pre(const EpilogueArgs& a, int tok0,
   }
 }
 
-// Split-K inside a thread-block cluster (up to 16 rows, 2, 4 or 8 splits): the CTAs that share an
+// Split-K inside a thread-block cluster (up to 64 rows, 2, 4 or 8 splits): the CTAs that share an
 // output tile are one cluster along z.  Each owns 128 / splits of the tile's out features: every
-// epilogue thread sends its 16 partial sums straight into the owner's shared memory
+// epilogue thread sends its partial sums straight into the owner's shared memory
 // (st.shared::cluster), one cluster barrier later the owner adds the `splits` partials in split
 // order and finishes its rows.  No scratch in global memory, no fence, no counter, no second pass
 // through L2; measured against the scratch form inside the decode graph this takes the product
@@ -234,7 +236,7 @@ template <int BT, bool CLUSTER = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const EpilogueArgs args) {
-  constexpr int STAGES = stages_for(BT);
+  constexpr int STAGES = CLUSTER ? cluster_stages_for(BT) : stages_for(BT);
   constexpr int B_BYTES = BT * BLOCK_K * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TCOLS = tmem_cols_for(BT);
@@ -250,7 +252,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 1);
   volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
   volatile int* flag_ptr = (volatile int*)(smem_raw + (tmem_slot + 4 - raw));
-  // cluster form: [split][row of this CTA's share][16 tokens] partial sums, 8 KB
+  // cluster form: [split][row of this CTA's share][BT tokens] partial sums, 128 * BT floats
   const uint32_t red = (tmem_slot + 8u + 15u) & ~15u;
   const float* red_ptr = (const float*)(smem_raw + (red - raw));
 
@@ -285,7 +287,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   // cluster form: what the epilogue threads carry across the cluster barrier
   [[maybe_unused]] bool share_ok = false;
-  [[maybe_unused]] float share_bias[8], share_res[8];
+  constexpr int SHARE = BT / 2;                 // outputs per epilogue thread in the cluster form, at most (2 splits)
+  [[maybe_unused]] float share_bias = 0.f, share_res[SHARE];
 
   if (warp == 0) {
     if (lane == 0) {
@@ -358,38 +361,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int quarter = warp & 3;
     const int n = n0 + quarter * 32 + lane;
     if constexpr (CLUSTER) {
-      // This thread's part of the CTA's share: token e % 16 of rows e / 16 + 8 i (see below).
+      // This CTA finishes rows_per of the tile's out features.  Thread e of the epilogue takes feature
+      // e % rows_per and the tokens e / rows_per + (128 / rows_per) * i: neighbouring threads write
+      // neighbouring features of one token.
       const int splits = gridDim.z, rows_per = BLOCK_N / splits, e = threadIdx.x - 64;
-      const int tok = t0 + (e & 15);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {               // the bias is a weight: no need to wait for it
-        const int row = (e >> 4) + 8 * i;
-        const int nn = n0 + (int)blockIdx.z * rows_per + row;
-        share_bias[i] = (row < rows_per && nn < args.N && args.bias) ? __ldg(args.bias + nn) : 0.f;
-      }
+      const int my_row = e % rows_per, tok_first = e / rows_per, tok_step = BLOCK_N / rows_per;
+      const int nn = n0 + (int)blockIdx.z * rows_per + my_row;
+      share_bias = (nn < args.N && args.bias) ? __ldg(args.bias + nn) : 0.f;     // a weight: no need to wait for it
       pdl_wait();      // residual and C belong to kernels before this one until here
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int row = (e >> 4) + 8 * i;
-        const int nn = n0 + (int)blockIdx.z * rows_per + row;
-        const bool mine = row < rows_per && nn < args.N;
-        share_res[i] = (mine && args.residual && tok < args.M) ? args.residual[(size_t)tok * args.N + nn] : 0.f;
+      for (int i = 0; i < SHARE; ++i) {
+        const int tok = t0 + tok_first + tok_step * i;
+        share_res[i] = (tok_first + tok_step * i < BT && nn < args.N && args.residual && tok < args.M)
+                           ? args.residual[(size_t)tok * args.N + nn] : 0.f;
       }
       share_ok = mbar_wait(tmem_full_bar, 0u, args.error, 4);
       tc_fence_after();
       if (share_ok) {
-        uint32_t r[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        // row `local` of the tile belongs to CTA local / rows_per of the cluster; its 16 sums go to
-        // [this split][local % rows_per][0..15] of that CTA's buffer
-        const int local = quarter * 32 + lane;
-        const uint32_t dst = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + local % rows_per) * 16) * 4),
+        // Feature `local` of the tile belongs to CTA local / rows_per of the cluster; its BT sums go to
+        // [this split][local % rows_per][0 .. BT) of that CTA's buffer, the 16-byte pieces of a row
+        // rotated by the row number so that the readers (one feature per lane) spread over the banks.
+        const int local = quarter * 32 + lane, rrow = local % rows_per;
+        const uint32_t dst = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + rrow) * BT) * 4),
                                         (uint32_t)(local / rows_per));
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          st_cluster_v4(dst + 16u * q, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        for (int c = 0; c < BT; c += 16) {
+          uint32_t r[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int piece = ((c >> 2) + q) ^ (rrow & (BT / 4 - 1));
+            st_cluster_v4(dst + 16u * piece, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          }
+        }
       }
     } else {
     pdl_wait();        // residual, partials and C belong to kernels before this one until here
@@ -494,15 +499,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     cluster_sync_all();
     if (warp >= 2 && share_ok) {
       const int splits = gridDim.z, rows_per = BLOCK_N / splits, e = threadIdx.x - 64;
-      const int tok = t0 + (e & 15);
+      const int my_row = e % rows_per, tok_first = e / rows_per, tok_step = BLOCK_N / rows_per;
+      const int nn = n0 + (int)blockIdx.z * rows_per + my_row;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int row = (e >> 4) + 8 * i;
-        const int nn = n0 + (int)blockIdx.z * rows_per + row;
-        if (row < rows_per && nn < args.N && tok < args.M) {
+      for (int i = 0; i < SHARE; ++i) {
+        const int tl = tok_first + tok_step * i, tok = t0 + tl;
+        if (tl < BT && nn < args.N && tok < args.M) {
+          const int at = ((tl >> 2) ^ (my_row & (BT / 4 - 1))) * 4 + (tl & 3);
           float v = 0.f;
-          for (int z = 0; z < splits; ++z) v += red_ptr[((z * rows_per + row) * 16) + (e & 15)];     // split order
-          const float y = apply_activation(v + share_bias[i], args.act) + share_res[i];
+          for (int z = 0; z < splits; ++z) v += red_ptr[(z * rows_per + my_row) * BT + at];     // split order
+          const float y = apply_activation(v + share_bias, args.act) + share_res[i];
           const size_t idx = (size_t)tok * args.N + nn;
           if (args.out_bf16) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(y);
           else ((float*)args.C)[idx] = y;
@@ -585,11 +591,11 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& arg
   return ayk_check_launch("ayk_gemm_tc");
 }
 
-// Up to 16 rows, the CTAs of an output tile as one cluster along z.
+// Up to 64 rows, the CTAs of an output tile as one cluster along z.
+template <int BT>
 int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& args, int splits, cudaStream_t stream) {
-  constexpr int BT = 16;
-  constexpr int STAGES = stages_for(BT);
-  constexpr size_t SMEM = 1024 + (size_t)STAGES * (A_BYTES + BT * BLOCK_K * 2) + 8 * (2 * STAGES + 2) + 16 + BLOCK_N * 16 * sizeof(float);
+  constexpr int STAGES = cluster_stages_for(BT);
+  constexpr size_t SMEM = 1024 + (size_t)STAGES * (A_BYTES + BT * BLOCK_K * 2) + 8 * (2 * STAGES + 2) + 16 + BLOCK_N * BT * sizeof(float);
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
@@ -637,7 +643,7 @@ AYK_EXPORT long long ayk_gemm_tc_scratch_floats(int M, int N, int splits) {
 // splits > 1 needs `partials` (ayk_gemm_tc_scratch_floats) and `counters` (one
 // zeroed unsigned per output tile; the kernel leaves them zero), unless cluster != 0: then the
 // splits of a tile are one thread-block cluster and exchange their sums through shared memory
-// (up to 16 rows; 2, 4 or 8 splits; at least one K block each), and no scratch is touched.
+// (up to 64 rows; 2, 4 or 8 splits; at least one K block each), and no scratch is touched.
 AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* bias, const float* residual,
                            int M, int N, int K, int act, int out_dtype, int splits, float* partials,
                            unsigned int* counters, int weight_is_static, int cluster, cudaStream_t stream) {
@@ -649,8 +655,8 @@ AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* b
   if (splits < 1) splits = 1;
   if (splits > total_kb) splits = total_kb;
   if (cluster) {
-    AYK_REQUIRE(M <= 16 && (splits == 2 || splits == 4 || splits == 8) && total_kb >= splits,
-                "ayk_gemm_tc: the cluster form takes up to 16 rows and 2, 4 or 8 splits of at least one K block (rows %d, splits %d, K blocks %d)",
+    AYK_REQUIRE(M <= 64 && (splits == 2 || splits == 4 || splits == 8) && total_kb >= splits,
+                "ayk_gemm_tc: the cluster form takes up to 64 rows and 2, 4 or 8 splits of at least one K block (rows %d, splits %d, K blocks %d)",
                 M, splits, total_kb);
   }
   int kb_per_split = (total_kb + splits - 1) / splits;
@@ -680,7 +686,8 @@ AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* b
   if (encode(&mx, X, M, K, BT) != 0) return -1;
   EpilogueArgs args{C, bias, residual, partials, counters, g_error_dev, M, N, K, act, out_dtype == AYK_DTYPE_BF16, kb_per_split,
                     total_kb / splits, total_kb % splits, g_trace};
-  if (cluster) return launch_cluster(mw, mx, args, splits, stream);
+  if (cluster) return BT == 16 ? launch_cluster<16>(mw, mx, args, splits, stream)
+                      : (BT == 32 ? launch_cluster<32>(mw, mx, args, splits, stream) : launch_cluster<64>(mw, mx, args, splits, stream));
   switch (BT) {
     case 16: return launch<16>(mw, mx, args, splits, stream);
     case 32: return launch<32>(mw, mx, args, splits, stream);

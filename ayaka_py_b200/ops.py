@@ -246,15 +246,18 @@ def _tc_workspace(device, floats: int):
     return ws
 
 
+CLUSTER_ROWS = 64        # up to this many rows the splits of a tile exchange their sums inside a cluster
+
+
 def tc_splits(M: int, N: int, K: int) -> int:
     """Split-K factor of the tensor-core product: skinny products (few output
     tiles) are cut along K so that about one CTA per SM streams the weight.
-    Up to 16 rows the factor is 1, 2, 4 or 8: those splits form a cluster."""
+    Up to 64 rows the factor is 1, 2, 4 or 8: those splits form a cluster."""
     bt = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
     tiles = -(-N // 128) * -(-M // bt)
     blocks = -(-K // 64)
-    if tiles >= SM_COUNT or blocks < 4 or M > 16:
-        return 1          # more than 16 rows: the partial sums cost more than the split saves (measured)
+    if tiles >= SM_COUNT or blocks < 4 or M > CLUSTER_ROWS:
+        return 1          # more rows: partial sums through global scratch cost more than the split saves (measured)
     for p in (8, 4, 2):
         if tiles * p <= SM_COUNT * 14 // 10 and blocks >= p:
             return p
@@ -268,7 +271,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     """act(a[M,K] @ w[N,K]^T + bias) (+ residual), bfloat16 operands, on tcgen05.
     ``splits``: CTAs along K per output tile (default: chosen by shape).  ``cluster``:
     the splits exchange their sums through shared memory of a thread-block cluster
-    instead of scratch in global memory (default where it applies: up to 16 rows,
+    instead of scratch in global memory (default where it applies: up to 64 rows,
     2, 4 or 8 splits)."""
     lib = _ready()
     M, K = a.shape
@@ -286,11 +289,11 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         raise KernelError("residual must have the output's shape")
     if splits is None:
         splits = tc_splits(M, N, K)
-    can_cluster = M <= 16 and splits in (2, 4, 8) and -(-K // 64) >= splits
+    can_cluster = M <= CLUSTER_ROWS and splits in (2, 4, 8) and -(-K // 64) >= splits
     if cluster is None:
         cluster = can_cluster
     elif cluster and not can_cluster:
-        raise KernelError(f"gemm_tc: the cluster form takes up to 16 rows and 2, 4 or 8 splits (rows {M}, splits {splits})")
+        raise KernelError(f"gemm_tc: the cluster form takes up to {CLUSTER_ROWS} rows and 2, 4 or 8 splits (rows {M}, splits {splits})")
     partials = counters = None
     if splits > 1 and not cluster:
         tiles = -(-N // 128) * -(-M // 16)
@@ -343,10 +346,14 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     pipes (true 32-bit); bfloat16 operands on the tensor cores (tcgen05) when
     K is a multiple of 8, else on the FP32 pipes with 32-bit accumulation."""
     if a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[0] > 0:
-        # More than a few rows: tiles of 128 rows by a width that fills the SMs, no split along K.
-        # (Up to 128 rows with an out width that is no multiple of 8 stay with the other kernel,
-        # whose stores run along the features.)
-        if a.shape[0] > PREFILL_ROWS and (w.shape[0] % 8 == 0 or a.shape[0] > 128):
+        M, N, K = a.shape[0], w.shape[0], a.shape[1]
+        # Up to 64 rows with few output tiles: weights as the MMA's M side, K split over a cluster.
+        # More rows: tiles of 128 rows by a width that fills the SMs, no split along K.  (Up to 128
+        # rows with an out width that is no multiple of 8 stay with the first kernel, whose stores
+        # run along the features.)
+        if M <= PREFILL_ROWS or (M <= CLUSTER_ROWS and tc_splits(M, N, K) > 1):
+            return gemm_tc(a, w, bias, activation, residual, out_dtype, out)
+        if N % 8 == 0 or M > 128:
             return gemm_tc_prefill(a, w, bias, activation, residual, out_dtype, out)
         return gemm_tc(a, w, bias, activation, residual, out_dtype, out)
     return gemm_simt(a, w, bias, activation, residual, out_dtype, out)

@@ -230,6 +230,7 @@ TC_CASES = [
     (100, 1003, 328, 1), (300, 200, 1600, 1), (8, 1600, 1600, None), (64, 1600, 6400, None),
     (3, 130, 512, 4), (40, 300, 1000, 7), (8, 64, 64, 3),
     (16, 300, 1600, 8), (1, 1600, 6400, 2), (5, 257, 520, 8), (9, 50257 // 16, 128, 2),      # splits as one cluster
+    (64, 1600, 6400, 8), (33, 4800, 1600, 4), (17, 200, 328, 2), (32, 130, 256, 4), (50, 6400, 1600, 2),
 ]
 
 

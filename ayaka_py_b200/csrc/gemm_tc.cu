@@ -266,6 +266,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                              : min(total_kb, kb_begin + args.kb_per_split) - kb_begin;   // >= 1 by the host's choice
 
   if (threadIdx.x == 0) {
+    // the descriptors are fetched now, not when the first copy needs them (the rows' copy comes after
+    // the wait for the kernel before this one, on the critical path of a decode step)
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);

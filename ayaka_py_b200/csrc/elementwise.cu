@@ -133,59 +133,12 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float
   *reinterpret_cast<uint2*>(p) = w;
 }
 
-// One warp per row, the row held in registers (width a multiple of 4, at most
-// 128 * MAXV): one pass over memory, no shared memory, no block barrier.  Same
-// arithmetic: mean, then the mean of squared deviations, in 32-bit.
-template <typename O, int MAXV>
-__global__ void __launch_bounds__(256)
-layernorm_warp_kernel(O* __restrict__ out, const float* __restrict__ x, const float* __restrict__ gamma,
-                      const float* __restrict__ beta, const int* __restrict__ rows, int n_rows, int d, float eps) {
-  pdl_trigger();
-  pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = blockIdx.x * 8 + warp;
-  if (r >= n_rows) return;
-  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
-  const int nv = d >> 2;
-  float4 v[MAXV];
-  float s = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int idx = lane + 32 * i;
-    if (idx < nv) {
-      v[i] = src[idx];
-      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-    }
-  }
-  const float mean = warp_sum(s) / (float)d;
-  float q = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    if (lane + 32 * i < nv) {
-      const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, e = v[i].w - mean;
-      q += (a * a + b * b) + (c * c + e * e);
-    }
-  }
-  const float rstd = rsqrtf(warp_sum(q) / (float)d + eps);
-  const float4* g4 = reinterpret_cast<const float4*>(gamma);
-  const float4* b4 = reinterpret_cast<const float4*>(beta);
-  O* dst = out + (size_t)r * d;
-#pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int idx = lane + 32 * i;
-    if (idx < nv) {
-      const float4 g = g4[idx];
-      const float4 b = beta ? b4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
-      store4(dst + 4 * idx, (v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y,
-             (v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
-    }
-  }
-}
-
-// Few rows (a decode step): one block of 128 threads per row, the row in registers.  The kernel
-// sits on the critical path between two products, so what does not depend on the kernel before
-// it (weight and bias of the norm, the row index) is fetched before the programmatic-launch wait,
-// and the row is read with every load in flight at once.
+// One block of 128 threads per row, the row in registers (width a multiple of 4, at most 2048): one
+// pass over memory.  In a decode step the kernel sits on the critical path between two products, so
+// what does not depend on the kernel before it (weight and bias of the norm, the row index) is
+// fetched before the programmatic-launch wait, and the row is read with every load in flight at
+// once.  It also serves prompts: 2,048 rows of 1,600 take 5.2 us (3.8 TB/s); a one-warp-per-row
+// variant took 10.2 us and was removed.
 template <typename O>
 __global__ void __launch_bounds__(128)
 layernorm_row_kernel(O* __restrict__ out, const float* __restrict__ x, const float* __restrict__ gamma,
@@ -242,19 +195,6 @@ AYK_EXPORT int ayk_layernorm(void* out, const float* x, const float* gamma, cons
   AYK_REQUIRE(d >= 1 && (size_t)d * 4 <= 48 * 1024, "ayk_layernorm: width %d is not in [1, 12288]", d);
   const bool aligned = (d % 4 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)gamma % 16 == 0) &&
                        (beta == nullptr || (uintptr_t)beta % 16 == 0) && ((uintptr_t)out % 16 == 0);
-  // Many rows: one warp per row (one pass over memory).  Few rows (decode): one block per
-  // row measured faster inside a step (1,845 against 1,713 tokens/s at 8 requests).
-  if (n_rows >= 512 && aligned && d <= 2048 && (out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16)) {
-    dim3 grid((n_rows + 7) / 8);
-    if (out_dtype == AYK_DTYPE_F32) {
-      if (d <= 512) ayk_launch(layernorm_warp_kernel<float, 4>, grid, dim3(256), 0, stream, (float*)out, x, gamma, beta, rows, n_rows, d, eps);
-      else ayk_launch(layernorm_warp_kernel<float, 16>, grid, dim3(256), 0, stream, (float*)out, x, gamma, beta, rows, n_rows, d, eps);
-    } else {
-      if (d <= 512) ayk_launch(layernorm_warp_kernel<__nv_bfloat16, 4>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out, x, gamma, beta, rows, n_rows, d, eps);
-      else ayk_launch(layernorm_warp_kernel<__nv_bfloat16, 16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out, x, gamma, beta, rows, n_rows, d, eps);
-    }
-    return ayk_check_launch("ayk_layernorm");
-  }
   if (aligned && d <= 2048 && (out_dtype == AYK_DTYPE_F32 || out_dtype == AYK_DTYPE_BF16)) {
     if (out_dtype == AYK_DTYPE_F32)
       ayk_launch(layernorm_row_kernel<float>, dim3(n_rows), dim3(128), 0, stream, (float*)out, x, gamma, beta, rows, d, eps);
@@ -279,7 +219,7 @@ __global__ void kv_append_kernel(T* __restrict__ kcache, T* __restrict__ vcache,
                                  const T* __restrict__ k, const T* __restrict__ v, int row_stride,
                                  const int* __restrict__ row_req, const int* __restrict__ pos,
                                  const int* __restrict__ table, int table_stride, int page_size,
-                                 int width) {
+                                 int width, int vec_ok) {
   pdl_trigger();
   // positions and block table are the step's inputs, not the work of the kernel before this one
   int t = blockIdx.x;
@@ -290,6 +230,19 @@ __global__ void kv_append_kernel(T* __restrict__ kcache, T* __restrict__ vcache,
   size_t dst = ((size_t)page * page_size + (p % page_size)) * width;
   const T* ks = k + (size_t)t * row_stride;
   const T* vs = v + (size_t)t * row_stride;
+  if (vec_ok) {            // rows of whole 16-byte pieces, 16-byte aligned on both sides
+    constexpr int PER = 16 / sizeof(T);
+    const uint4* k4 = reinterpret_cast<const uint4*>(ks);
+    const uint4* v4 = reinterpret_cast<const uint4*>(vs);
+    uint4* kd = reinterpret_cast<uint4*>(kcache + dst);
+    uint4* vd = reinterpret_cast<uint4*>(vcache + dst);
+    const int n = width / PER;
+    for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) {
+      if (i < n) kd[i] = k4[i];
+      else vd[i - n] = v4[i - n];
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     kcache[dst + i] = ks[i];
     vcache[dst + i] = vs[i];
@@ -305,13 +258,16 @@ AYK_EXPORT int ayk_kv_append(void* kcache, void* vcache, const void* k, const vo
                              cudaStream_t stream) {
   if (T == 0) return 0;
   int threads = width >= 512 ? 256 : 128;
+  const size_t elem = dtype == AYK_DTYPE_F32 ? 4 : 2;
+  const int vec_ok = (width * elem) % 16 == 0 && ((size_t)row_stride * elem) % 16 == 0 && (uintptr_t)k % 16 == 0 &&
+                     (uintptr_t)v % 16 == 0 && (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0;
   if (dtype == AYK_DTYPE_F32)
     ayk_launch(kv_append_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)kcache, (float*)vcache,
-               (const float*)k, (const float*)v, row_stride, row_req, pos, table, table_stride, page_size, width);
+               (const float*)k, (const float*)v, row_stride, row_req, pos, table, table_stride, page_size, width, vec_ok);
   else if (dtype == AYK_DTYPE_BF16)
     ayk_launch(kv_append_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)kcache,
                (__nv_bfloat16*)vcache, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride, row_req, pos,
-               table, table_stride, page_size, width);
+               table, table_stride, page_size, width, vec_ok);
   else
     return ayk_fail("ayk_kv_append: unknown dtype %d", dtype);
   return ayk_check_launch("ayk_kv_append");

@@ -403,7 +403,7 @@ def test_gemm_tcgen05_many_rows(M, N, K, tile_n, act, out_dtype, pair):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("width", [64, 1600, 2048])
-def test_layernorm_many_rows_one_warp_per_row(dtype, width):
+def test_layernorm_many_rows(dtype, width):
     from ayaka_py_b200 import ops
     rs = np.random.RandomState(13)
     x = (rs.randn(777, width) * 2 - 0.5).astype(np.float32)

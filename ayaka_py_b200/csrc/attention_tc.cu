@@ -129,18 +129,39 @@ __global__ void __launch_bounds__(THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const AttnArgs args) {
   pdl_trigger();
-  pdl_wait();
-  // Which request and which of its 128-row tiles?
-  int tile = blockIdx.x, req = -1, q0 = 0, q_len = 0;
-  for (int r = 0; r < args.num_req; ++r) {
-    const int len = args.req_q_start[r + 1] - args.req_q_start[r];
-    const int tiles = (len + BQ - 1) / BQ;
-    // Late tiles of a request see the most keys: they are handed out first.
-    if (tile < tiles) { req = r; q0 = (tiles - 1 - tile) * BQ; q_len = len; break; }
-    tile -= tiles;
+  // Row ranges, positions and block tables are the step's inputs: the set-up below (barriers, tensor
+  // memory) runs while the kernel before this one finishes; pdl_wait() comes before the first access
+  // to q, the cache or the output.
+  // Which request and which of its 128-row tiles?  blockIdx.y counts tiles in the order "the last
+  // tile of every request, then the one before it of every request that has one, ...": late tiles see
+  // the most keys, and with the heads in blockIdx.x the whole grid starts its long CTAs first (measured:
+  // 47 -> 30 us for two prompts of 1,024 tokens, where CTAs last from 8 to 31 us).  Every warp finds
+  // its tile for itself, 32 requests at a time, from one load per lane and ballots.
+  int tile = blockIdx.y, req = -1, q0 = 0, q_len = 0;
+  {
+    const int lane_id = threadIdx.x & 31;
+    for (int r0 = 0; r0 < args.num_req && req < 0; r0 += 32) {
+      const int r = r0 + lane_id;
+      const int len = r < args.num_req ? args.req_q_start[r + 1] - args.req_q_start[r] : 0;
+      const int tiles = (len + BQ - 1) / BQ;
+      const int group_tiles = __reduce_add_sync(0xffffffffu, tiles);
+      if (tile >= group_tiles) { tile -= group_tiles; continue; }
+      for (int level = 0; req < 0; ++level) {            // ends: tile < group_tiles
+        const unsigned have = __ballot_sync(0xffffffffu, tiles > level);
+        const int n = __popc(have);
+        if (tile < n) {
+          const int src = __fns(have, 0, tile + 1);      // the lane of the (tile + 1)-th such request
+          req = r0 + src;
+          q_len = __shfl_sync(0xffffffffu, len, src);
+          q0 = (__shfl_sync(0xffffffffu, tiles, src) - 1 - level) * BQ;
+        } else {
+          tile -= n;
+        }
+      }
+    }
   }
   if (req < 0) return;
-  const int h = blockIdx.y, kvh = h / (args.H / args.Hkv);
+  const int h = blockIdx.x, kvh = h / (args.H / args.Hkv);
   const int rows = min(BQ, q_len - q0);
   const int row0 = args.req_q_start[req] + q0;
   const int pos0 = args.req_pos0[req] + q0;
@@ -187,35 +208,42 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t tmem_base = *tmem_slot_ptr;
   const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
+  pdl_wait();
   if (warp == 4) {
+    // Lane 0 keeps the barriers; lane p brings page p of a tile (its own look-up in the block table
+    // and its own two copies), so a tile costs one trip to the table instead of one per page.
     if (lane == 0) {
       mbar_expect_tx(q_full, TILE_BYTES);
       tma_load_2d(q_tile, &map_q, h * DH, row0, q_full);
-      const int pages_per_tile = BKV / args.page_size;
-      const uint32_t page_bytes = (uint32_t)args.page_size * 128u;
-      bool ok = true;
-      int issued = 0;
-      for (int i = 0; i < num_tiles && ok; ++i) {
-        const int b = i & 1;
-        if (i >= 2) {
-          ok = mbar_wait(kv_empty0 + 8 * b, (uint32_t)((i >> 1) & 1) ^ 1u, args.error, 11);
-          if (!ok) break;
-        }
-        mbar_expect_tx(kv_full0 + 8 * b, 2 * TILE_BYTES);
+    }
+    const int pages_per_tile = BKV / args.page_size;
+    const uint32_t page_bytes = (uint32_t)args.page_size * 128u;
+    bool ok = true;
+    int issued = 0;
+    for (int i = 0; i < num_tiles && ok; ++i) {
+      const int b = i & 1;
+      const int key0 = k_begin + i * BKV;
+      int page = 0;
+      if (lane < pages_per_tile) {
+        const int logical = key0 / args.page_size + lane;
+        page = logical < args.table_stride ? my_table[logical] : 0;               // beyond the table: the padding page
+      }
+      if (lane == 0) {
+        if (i >= 2) ok = mbar_wait(kv_empty0 + 8 * b, (uint32_t)((i >> 1) & 1) ^ 1u, args.error, 11);
+        if (ok) mbar_expect_tx(kv_full0 + 8 * b, 2 * TILE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      if (lane < pages_per_tile) {
         const uint32_t k_dst = kv_tile + b * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
-        const int key0 = k_begin + i * BKV;
-        for (int p = 0; p < pages_per_tile; ++p) {
-          const int logical = key0 / args.page_size + p;
-          const int page = logical < args.table_stride ? my_table[logical] : 0;   // beyond the table: the padding page
-          tma_load_3d(k_dst + p * page_bytes, &map_k, 0, kvh, page * args.page_size, kv_full0 + 8 * b);
-          tma_load_3d(v_dst + p * page_bytes, &map_v, 0, kvh, page * args.page_size, kv_full0 + 8 * b);
-        }
-        issued = i + 1;
+        tma_load_3d(k_dst + lane * page_bytes, &map_k, 0, kvh, page * args.page_size, kv_full0 + 8 * b);
+        tma_load_3d(v_dst + lane * page_bytes, &map_v, 0, kvh, page * args.page_size, kv_full0 + 8 * b);
       }
-      if (!ok) {
-        for (int i = max(0, issued - 2); i < issued; ++i)
-          mbar_wait(kv_full0 + 8 * (i & 1), (uint32_t)(i >> 1) & 1u, args.error, 12);
-      }
+      issued = i + 1;
+    }
+    if (!ok && lane == 0) {
+      for (int i = max(0, issued - 2); i < issued; ++i)
+        mbar_wait(kv_full0 + 8 * (i & 1), (uint32_t)(i >> 1) & 1u, args.error, 12);
     }
     __syncwarp();
   } else if (warp == 5) {
@@ -259,7 +287,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     uint8_t* p_row = generic_base + (p_tile - base) + row * 128;
     bool ok = true;
     for (int i = 0; i < num_tiles && ok; ++i) {
-      ok = mbar_wait(s_full, (uint32_t)i & 1u, args.error, 16);
+      // one lane per warp watches a barrier: 128 polling threads take issue slots from the other CTA of the SM
+      if (lane == 0) ok = mbar_wait(s_full, (uint32_t)i & 1u, args.error, 16);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
       const int key0 = k_begin + i * BKV;
@@ -270,16 +300,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const bool unmasked = lo <= 0 && hi >= BKV;  // every key of the tile is visible to this row
       // Scores are kept times log2(e), so that exp(s - m) is one ex2 each
       // (32-bit; the result is rounded to bfloat16 for the second product anyway).
+      // The exponentials are what this kernel is made of (the special-function unit does 16 a clock
+      // per SM): chunks of 32 keys that no row of the warp sees (above the diagonal, below the
+      // window) are not read at all, and a row skips the arithmetic of chunks it does not see.
+      const int warp_hi = __reduce_max_sync(0xffffffffu, hi), warp_lo = __reduce_min_sync(0xffffffffu, live ? lo : BKV);
       // Pass 1 over the row of S in tensor memory: its maximum.
       float m_tile = -INFINITY;
 #pragma unroll
       for (int c = 0; c < BKV; c += 32) {
+        if (c >= warp_hi || c + 32 <= warp_lo) continue;       // the same for the whole warp
         uint32_t r[32];
         tmem_ld32(tmem_s + lane_addr + c, r);
         if (unmasked) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
-        } else {
+        } else if (c < hi && c + 32 > lo) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (c + j >= lo && c + j < hi) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
@@ -292,24 +327,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // Pass 2: exponentials, rounded to bfloat16, into the swizzled rows of P.
 #pragma unroll
       for (int c = 0; c < BKV; c += 32) {
+        const bool warp_sees = !(c >= warp_hi || c + 32 <= warp_lo);
+        const bool row_sees = c < hi && c + 32 > lo;
         uint32_t r[32];
-        tmem_ld32(tmem_s + lane_addr + c, r);
+        if (warp_sees) tmem_ld32(tmem_s + lane_addr + c, r);
 #pragma unroll
         for (int g = 0; g < 32; g += 8) {           // 8 keys = one 16-byte chunk of the row of P
-          uint32_t packed[4];
+          uint32_t packed[4] = {0u, 0u, 0u, 0u};
+          if (warp_sees && row_sees) {
 #pragma unroll
-          for (int j = 0; j < 8; j += 2) {
-            const int k0i = c + g + j;
-            float p0 = fast_exp2(fmaf(__uint_as_float(r[g + j]), scale_log2, -m_new));
-            float p1 = fast_exp2(fmaf(__uint_as_float(r[g + j + 1]), scale_log2, -m_new));
-            if (!unmasked) {
-              if (!(k0i >= lo && k0i < hi)) p0 = 0.f;
-              if (!(k0i + 1 >= lo && k0i + 1 < hi)) p1 = 0.f;
+            for (int j = 0; j < 8; j += 2) {
+              const int k0i = c + g + j;
+              float p0 = fast_exp2(fmaf(__uint_as_float(r[g + j]), scale_log2, -m_new));
+              float p1 = fast_exp2(fmaf(__uint_as_float(r[g + j + 1]), scale_log2, -m_new));
+              if (!unmasked) {
+                if (!(k0i >= lo && k0i < hi)) p0 = 0.f;
+                if (!(k0i + 1 >= lo && k0i + 1 < hi)) p1 = 0.f;
+              }
+              l_tile += p0 + p1;                    // 32-bit sum of the unrounded values
+              __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+              packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
             }
-            __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-            // The sum must match what the MMA will multiply: the rounded values.
-            l_tile += __bfloat162float(pb.x) + __bfloat162float(pb.y);
-            packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
           }
           const int chunk = (c + g) >> 3;           // 0..15: tile = chunk / 8, 16-byte column = chunk % 8
           uint8_t* dst = p_row + (chunk >> 3) * TILE_BYTES + (((chunk & 7) ^ (row & 7)) << 4);
@@ -323,7 +361,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
       tc_fence_before();
       mbar_arrive(p_full);
-      ok = mbar_wait(o_full, (uint32_t)i & 1u, args.error, 17);
+      if (lane == 0) ok = mbar_wait(o_full, (uint32_t)i & 1u, args.error, 17);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -466,7 +505,8 @@ AYK_EXPORT int ayk_attention_tc(void* out, const void* q, int q_stride, int tota
   if (cache_map(&mv, vcache, pages * page_size, Hkv, page_size) != 0) return -1;
   AttnArgs args{(__nv_bfloat16*)out, table, req_q_start, req_pos0, g_error_dev, table_stride, num_req, H, Hkv, page_size,
                 window, scale};
-  dim3 grid(total_rows / BQ + num_req, H);
+  AYK_REQUIRE(total_rows / BQ + num_req <= 65535 && H >= 1, "ayk_attention_tc: too many row tiles (%d rows, %d requests)", total_rows, num_req);
+  dim3 grid(H, total_rows / BQ + num_req);      // heads fastest: see the tile order in the kernel
   ayk_launch(attention_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, args);
   return ayk_check_launch("ayk_attention_tc");
 }

@@ -1,8 +1,15 @@
 """The generation loop: schedule, step, sample, read back, commit.
 
 One step is in flight at a time, as in the reference's default
-(``configs/scheduler.py:131``): the next step is planned after this step's
-tokens are on the host (``runtime/engine.py:180-279``)."""
+(``configs/scheduler.py:131``; ``runtime/engine.py:180-279``).  With
+``EngineConfig.lookahead`` the host's share of the next step overlaps the GPU's
+work on this one: when a step is a pure decode step of every running request
+and nobody can reach a length limit, the next step is planned, uploaded and
+launched (its tokens copied from the sampler's output on the device) before this
+step's tokens have reached the host.  The tokens a request sees are the same
+either way; a request that stops on EOS or a stop id has one more position
+computed than it needed, which is dropped.
+"""
 
 from __future__ import annotations
 
@@ -35,58 +42,114 @@ class Engine:
         if config.decode_graph:
             from .graphs import DecodeGraphs
             self.decode_graphs = DecodeGraphs(self.runner, model, config.max_requests)
+        self.lookahead = bool(getattr(config, "lookahead", True)) and torch.cuda.is_available()
+        self._inflight: _Launched | None = None
+        self._copy_stream = torch.cuda.Stream() if torch.cuda.is_available() else None
+        self._pinned: list[torch.Tensor] = []      # host landing places of sampled tokens, reused
 
     def submit(self, request: Request) -> None:
         self.scheduler.add(request)
 
     def abort(self, request_id: str) -> None:
+        self._drain()
         s = self.scheduler.abort(request_id)
         if s is not None:
             self.finished[request_id] = self.scheduler.result_of(s)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self._inflight is not None or self.scheduler.has_work()
 
     def step(self) -> list[GenerationResult]:
-        """Plans and runs one step.  Returns the requests that finished in it."""
-        plan = self.scheduler.schedule()
-        if plan is None:
-            if self.scheduler.has_work():
-                raise RuntimeError("the scheduler can run nothing although requests wait: the cache is "
-                                   "too small for what was admitted")
-            return []
+        """Runs one step to its end (its tokens on the host) and returns the
+        requests that finished in it.  The step after it may already be running."""
+        if self._inflight is None:
+            plan = self.scheduler.schedule()
+            if plan is None:
+                if self.scheduler.has_work():
+                    raise RuntimeError("the scheduler can run nothing although requests wait: the cache is "
+                                       "too small for what was admitted")
+                return []
+            self._inflight = self._launch(plan)
+        current = self._inflight
+        ahead = None
+        if self.lookahead:
+            plan = self.scheduler.lookahead(current.plan)
+            if plan is not None:
+                ahead = self._launch(plan, tokens_from=current.sampled)
+        self._inflight = ahead
+        return self._finish_step(current)
+
+    def _launch(self, plan: ScheduledStep, tokens_from: torch.Tensor | None = None) -> "_Launched":
+        """Hands a planned step to the GPU: upload, forward, sampling, and the copy
+        of the sampled tokens to the host on a stream of its own.  ``tokens_from``:
+        the sampled tokens of the step before, still on the device, are this step's
+        tokens (one per entry, same order)."""
+        ahead = tokens_from is not None
         try:
-            tokens = self._run(plan)
+            entries = [StepEntry(e.state.slot, e.start,
+                                 [0] * e.count if ahead else e.state.tokens[e.start:e.start + e.count],
+                                 [e.count - 1] if e.sample else []) for e in plan.entries]
+            rows = [e.state for e in plan.entries if e.sample]
+            if self.decode_graphs is not None and plan.decode_only:
+                logits = self.decode_graphs.run(entries, tokens_from=tokens_from)
+            else:
+                logits = self.runner.run(entries, tokens_from=tokens_from)
+            sampled = host = done = None
+            if rows:
+                pending = 1 if ahead else 0         # a token of each row is still on its way
+                sampled = self.sampler.sample(logits, [s.request.sampling for s in rows], [s.seed for s in rows],
+                                              [s.generated + pending for s in rows])
+                host = self._pinned.pop() if self._pinned else None
+                if host is None or host.numel() < len(rows):
+                    host = torch.empty(max(len(rows), self.config.max_requests), dtype=torch.int32, pin_memory=True)
+                ready = torch.cuda.Event()
+                ready.record()
+                with torch.cuda.stream(self._copy_stream):
+                    self._copy_stream.wait_event(ready)
+                    host[:len(rows)].copy_(sampled, non_blocking=True)
+                    done = torch.cuda.Event()
+                    done.record()
         except BaseException:
             self.cache.rollback(plan.reservation)
             raise
+        self.scheduler.advance(plan)
+        return _Launched(plan, rows, sampled, host, done)
+
+    def _finish_step(self, launched: "_Launched") -> list[GenerationResult]:
         sampled = {}
-        rows = [e for e in plan.entries if e.sample]
-        for e, token in zip(rows, tokens):
-            sampled[e.state.request.request_id] = token
-        done = self.scheduler.update(plan, sampled)
+        if launched.rows:
+            launched.done.synchronize()
+            tokens = launched.host[:len(launched.rows)].tolist()
+            self._pinned.append(launched.host)
+            for s, token in zip(launched.rows, tokens):
+                sampled[s.request.request_id] = token
+        elif self._inflight is None:
+            torch.cuda.synchronize()
+        done = self.scheduler.resolve(launched.plan, sampled)
         results = [self.scheduler.result_of(s) for s in done]
         for r in results:
             self.finished[r.request_id] = r
         return results
 
-    def _run(self, plan: ScheduledStep) -> list[int]:
-        entries = [StepEntry(e.state.slot, e.start, e.state.tokens[e.start:e.start + e.count],
-                             [e.count - 1] if e.sample else []) for e in plan.entries]
-        rows = [e.state for e in plan.entries if e.sample]
-        if self.decode_graphs is not None and plan.decode_only:
-            logits = self.decode_graphs.run(entries)
-        else:
-            logits = self.runner.run(entries)
-        if not rows:
-            torch.cuda.synchronize()
-            return []
-        tokens = self.sampler.sample(logits, [s.request.sampling for s in rows], [s.seed for s in rows],
-                                     [s.generated for s in rows])
-        return tokens.cpu().tolist()
+    def _drain(self) -> None:
+        """Brings the loop to a point where no step is in flight."""
+        while self._inflight is not None:
+            current, self._inflight = self._inflight, None
+            self._finish_step(current)
 
     def run_until_idle(self) -> dict[str, GenerationResult]:
         while self.has_work():
             self.step()
         out, self.finished = self.finished, {}
         return out
+
+
+class _Launched:
+    """A step on the GPU: its plan, the requests whose tokens it samples, the
+    sampler's output on the device, its landing place on the host and the event
+    that says it has landed."""
+
+    __slots__ = ("plan", "rows", "sampled", "host", "done")
+
+    def __init__(self, plan, rows, sampled, host, done):
+        self.plan, self.rows, self.sampled, self.host, self.done = plan, rows, sampled, host, done

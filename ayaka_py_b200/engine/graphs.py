@@ -49,9 +49,11 @@ class DecodeGraphs:
         self.graphs[bucket] = entry
         return entry
 
-    def run(self, entries: list[StepEntry]) -> torch.Tensor:
+    def run(self, entries: list[StepEntry], tokens_from: torch.Tensor | None = None) -> torch.Tensor:
         """Logits [len(entries), V] of a step whose entries all bring one token
-        and want its logits."""
+        and want its logits.  ``tokens_from``: int32 on the device, the entries'
+        tokens in order (their host copies are not known yet): they are copied into
+        the step's buffer after its upload."""
         if self.generation != self.runner.generation:     # the step buffer moved: graphs point at the old one
             self.graphs.clear()
             self.generation = self.runner.generation
@@ -59,7 +61,9 @@ class DecodeGraphs:
         bucket = self.bucket_for(n)
         entry = self.graphs.get(bucket) or self._capture(bucket)
         graph, logits, kernels = entry
-        self.runner.prepare(entries, pad_to=bucket)
+        ctx = self.runner.prepare(entries, pad_to=bucket)
+        if tokens_from is not None:
+            ctx.tokens[:n].copy_(tokens_from[:n])
         self.h2d_bytes = self.runner.h2d_bytes
         graph.replay()
         self.launches += kernels

@@ -233,12 +233,25 @@ class Scheduler:
     def update(self, step: ScheduledStep, sampled: dict[str, int]) -> list[RequestState]:
         """The step ran: commit it, append the sampled tokens, finish and free.
         ``sampled``: request id -> token for every entry with ``sample``."""
+        self.advance(step)
+        return self.resolve(step, sampled)
+
+    def advance(self, step: ScheduledStep) -> None:
+        """The step has been handed to the GPU and will complete: its tokens count
+        as cached from now on (the cache manager's lengths move, pages that a window
+        has passed return).  The sampled tokens come later, through ``resolve``."""
         self.cache.commit(step.reservation)
+        for e in step.entries:
+            e.state.computed = e.start + e.count
+
+    def resolve(self, step: ScheduledStep, sampled: dict[str, int]) -> list[RequestState]:
+        """The step's sampled tokens are on the host: append them, finish and free.
+        An entry whose request has finished meanwhile (it was planned ahead, see
+        ``lookahead``) is skipped: its token belongs to nobody."""
         finished = []
         for e in step.entries:
             s = e.state
-            s.computed = e.start + e.count
-            if not e.sample:
+            if not e.sample or s.finish_reason is not None:
                 continue
             token = int(sampled[s.request.request_id])
             s.tokens.append(token)
@@ -248,6 +261,35 @@ class Scheduler:
                 self._finish(s, reason)
                 finished.append(s)
         return finished
+
+    def lookahead(self, step: ScheduledStep) -> ScheduledStep | None:
+        """The step after ``step``, planned before ``step``'s tokens are known, or
+        None when that cannot be done without guessing more than "nobody stops":
+        ``step`` (already advanced) must be a pure decode step of every running
+        request, nobody waits, nobody reaches a length limit with the token that is
+        on its way, and the pages are there.  A request that stops on the token on
+        its way (EOS, a stop id) has then one more token computed than it needed;
+        ``resolve`` drops it.  The reference keeps one step in flight
+        (``configs/scheduler.py:131``); this is the same loop with the host's share
+        of the next step done while the GPU works on this one."""
+        if not step.decode_only or self.waiting or len(step.entries) != len(self.running):
+            return None
+        if len(step.entries) > self.batch_tokens:
+            return None
+        for e, s in zip(step.entries, self.running):
+            if e.state is not s or not e.sample or s.finish_reason is not None or s.remaining != 0:
+                return None
+            stop = s.request.stop
+            if s.generated + 1 >= stop.max_tokens or len(s.tokens) + 1 >= self.max_model_len:
+                return None                        # finishes by length when its token arrives
+        entries = [ScheduledEntry(s, s.computed, 1, True) for s in self.running]
+        try:
+            reservation = self.cache.reserve([(e.state.slot, e.start, 1) for e in entries])
+        except OutOfPages:
+            return None
+        self.stats.steps += 1
+        self.stats.decode_tokens += len(entries)
+        return ScheduledStep(entries, reservation, True)
 
     def _finish_reason(self, s: RequestState, token: int) -> str | None:
         """``request/stream.py:130-163``: stop ids and EOS count only from

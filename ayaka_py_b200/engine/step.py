@@ -188,7 +188,14 @@ class StepRunner:
             host={"q_start": q_start, "pos0": starts, "slots": slots, "kv_len": ends, "counts": counts},
             max_q_len=int(counts.max()), max_kv_len=int(ends.max()))
 
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], tokens_from: torch.Tensor | None = None) -> torch.Tensor:
         """Logits [S, V] float32 on the device.  The caller has reserved the
-        step in the cache manager and commits it afterwards."""
-        return self.model.forward(self.prepare(entries))
+        step in the cache manager and commits it afterwards.  ``tokens_from``
+        (int32 on the device, one token per entry): the tokens of a step of single
+        tokens whose host copies are not known yet."""
+        ctx = self.prepare(entries)
+        if tokens_from is not None:
+            if ctx.num_rows != len(entries):
+                raise ValueError("tokens can come from the device only for entries of one token each")
+            ctx.tokens[:len(entries)].copy_(tokens_from[:len(entries)])
+        return self.model.forward(ctx)

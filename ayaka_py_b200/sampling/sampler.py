@@ -25,10 +25,14 @@ class Sampler:
     def _allocate(self, rows: int) -> None:
         pin = torch.cuda.is_available()
         self.rows = rows
-        self.h_float = torch.zeros((3, rows), dtype=torch.float32, pin_memory=pin)   # temperature, top_p, min_p
-        self.h_long = torch.zeros((3, rows), dtype=torch.int64, pin_memory=pin)      # seed, offset, top_k
-        self.d_float = torch.zeros((3, rows), dtype=torch.float32, device=self.device)
-        self.d_long = torch.zeros((3, rows), dtype=torch.int64, device=self.device)
+        # Two sets, used in turn: the engine may pack the options of the next step while the
+        # upload of this step's options still waits in the stream behind this step's kernels.
+        self._sets = [(torch.zeros((3, rows), dtype=torch.float32, pin_memory=pin),   # temperature, top_p, min_p
+                       torch.zeros((3, rows), dtype=torch.int64, pin_memory=pin),     # seed, offset, top_k
+                       torch.zeros((3, rows), dtype=torch.float32, device=self.device),
+                       torch.zeros((3, rows), dtype=torch.int64, device=self.device)) for _ in range(2)]
+        self._uploaded = [None, None]
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                offsets: Sequence[int]) -> torch.Tensor:
@@ -40,17 +44,24 @@ class Sampler:
             return ops.sample(logits)
         if S > self.rows:
             self._allocate(max(S, 2 * self.rows))
+        self._turn ^= 1
+        h_float, h_long, d_float, d_long = self._sets[self._turn]
+        if self._uploaded[self._turn] is not None:
+            self._uploaded[self._turn].synchronize()       # this set's last upload (two calls ago) has left the host
         for i, p in enumerate(params):
-            self.h_float[0, i] = 0.0 if p.greedy else p.temperature
-            self.h_float[1, i] = p.top_p
-            self.h_float[2, i] = p.min_p
-            self.h_long[0, i] = seeds[i]
-            self.h_long[1, i] = offsets[i]
-            self.h_long[2, i] = p.top_k if p.top_k > 0 else 0
-        self.d_float.copy_(self.h_float, non_blocking=True)
-        self.d_long.copy_(self.h_long, non_blocking=True)
+            h_float[0, i] = 0.0 if p.greedy else p.temperature
+            h_float[1, i] = p.top_p
+            h_float[2, i] = p.min_p
+            h_long[0, i] = seeds[i]
+            h_long[1, i] = offsets[i]
+            h_long[2, i] = p.top_k if p.top_k > 0 else 0
+        d_float.copy_(h_float, non_blocking=True)
+        d_long.copy_(h_long, non_blocking=True)
+        if d_float.is_cuda:
+            self._uploaded[self._turn] = torch.cuda.Event()
+            self._uploaded[self._turn].record()
         filtered = any(p.filtered and not p.greedy for p in params)
-        return ops.sample(logits, self.d_float[0, :S], self.d_long[0, :S], self.d_long[1, :S],
-                          top_k=self.d_long[2, :S] if filtered else None,
-                          top_p=self.d_float[1, :S] if filtered else None,
-                          min_p=self.d_float[2, :S] if filtered else None)
+        return ops.sample(logits, d_float[0, :S], d_long[0, :S], d_long[1, :S],
+                          top_k=d_long[2, :S] if filtered else None,
+                          top_p=d_float[1, :S] if filtered else None,
+                          min_p=d_float[2, :S] if filtered else None)

@@ -165,3 +165,109 @@ def test_seeds():
     a = sched.add(Request("a", [1], SamplingParams(seed=42), StopCriteria(max_tokens=4)))
     b = sched.add(Request("b", [1], stop=StopCriteria(max_tokens=4)))
     assert a.seed == 42 and b.seed == derive_seed(1) and 0 <= b.seed < 2 ** 63
+
+
+def drive_ahead(sched, cache, token, arrivals=None, max_steps=10_000, log=None):
+    """The engine's loop with lookahead and a fake model: a step's tokens become
+    known only after the step behind it has been planned and "launched"."""
+    done, inflight, step_no = [], None, 0
+    arrivals = dict(arrivals or {})
+    for _ in range(max_steps):
+        for r in arrivals.pop(step_no, []):
+            sched.add(r)
+        step_no += 1
+        if inflight is None:
+            if not sched.has_work():
+                if not arrivals:
+                    break
+                continue
+            plan = sched.schedule()
+            assert plan is not None
+            sched.advance(plan)
+            inflight = plan
+        current = inflight
+        inflight = sched.lookahead(current)
+        if inflight is not None:
+            sched.advance(inflight)
+        cache.check_invariants()
+        if log is not None:
+            log.append(("ahead" if inflight is not None else "plain", [(e.state.request.request_id, e.start, e.count) for e in current.entries]))
+        # tokens of `current` arrive now; the fake model only looks at what was known when the step was planned
+        sampled = {e.state.request.request_id: token(e.state, e.start + e.count) for e in current.entries if e.sample}
+        done += sched.resolve(current, sampled)
+    assert not sched.has_work() and inflight is None
+    cache.assert_clean()
+    return done
+
+
+def drive_plain(sched, cache, token, arrivals=None, max_steps=10_000):
+    done, step_no = [], 0
+    arrivals = dict(arrivals or {})
+    for _ in range(max_steps):
+        for r in arrivals.pop(step_no, []):
+            sched.add(r)
+        step_no += 1
+        if not sched.has_work():
+            if not arrivals:
+                break
+            continue
+        plan = sched.schedule()
+        assert plan is not None
+        sampled = {e.state.request.request_id: token(e.state, e.start + e.count) for e in plan.entries if e.sample}
+        done += sched.update(plan, sampled)
+    cache.assert_clean()
+    return done
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_lookahead_gives_the_same_tokens_and_reasons(seed):
+    """Planning a decode step before the tokens of the step before it are known
+    changes nothing that a request sees: same tokens, same finish reasons, EOS in
+    the middle of a run included; the cache ends clean."""
+    rs = np.random.RandomState(seed)
+    lens = rs.randint(1, 30, size=6)
+    limits = rs.randint(2, 14, size=6)
+
+    def token(state, position):                    # a function of the request and the position only
+        h = (state.ordinal * 7919 + position * 104729 + seed) % 23
+        return 99 if h == 0 else 5 + h             # 99 is EOS for some positions
+
+    results = []
+    for ahead in (False, True):
+        sched, cache = make(pages=40, page_size=4, max_requests=4, batch_tokens=24, prefill_chunk=8, max_len=64, eos=99)
+        arrivals = {0: [req(i, int(lens[i]), max_tokens=int(limits[i])) for i in range(3)],
+                    5: [req(3, int(lens[3]), max_tokens=int(limits[3]))],
+                    9: [req(4, int(lens[4]), max_tokens=int(limits[4]), ignore_eos=True), req(5, int(lens[5]), max_tokens=int(limits[5]))]}
+        log = []
+        done = drive_ahead(sched, cache, token, arrivals, log=log) if ahead else drive_plain(sched, cache, token, arrivals)
+        results.append({s.request.request_id: (tuple(s.tokens), s.finish_reason) for s in done})
+        if ahead:
+            assert any(kind == "ahead" for kind, _ in log) or seed < 0
+    assert results[0] == results[1]
+    assert len(results[0]) == 6
+
+
+def test_lookahead_refuses_what_it_cannot_know():
+    sched, cache = make(pages=20, page_size=4, max_requests=4, batch_tokens=8)
+    sched.add(req(0, 3, max_tokens=4))
+    sched.add(req(1, 2, max_tokens=2))
+    plan = sched.schedule()                        # both prompts: not a decode step
+    sched.advance(plan)
+    assert sched.lookahead(plan) is None
+    sched.resolve(plan, {"r0": 7, "r1": 7})
+    plan = sched.schedule()                        # decode step; r1 reaches max_tokens with the token on its way
+    assert plan.decode_only
+    sched.advance(plan)
+    assert sched.lookahead(plan) is None
+    done = sched.resolve(plan, {"r0": 7, "r1": 7})
+    assert [s.request.request_id for s in done] == ["r1"]
+    plan = sched.schedule()
+    sched.advance(plan)
+    ahead = sched.lookahead(plan)                  # r0 alone, two tokens to go
+    assert ahead is not None and [(e.start, e.count) for e in ahead.entries] == [(5, 1)]
+    sched.advance(ahead)
+    sched.add(req(2, 2))                           # somebody waits now: no further lookahead
+    sched.resolve(plan, {"r0": 7})
+    assert sched.lookahead(ahead) is None
+    sched.resolve(ahead, {"r0": 7})
+    assert "r0" not in sched.states

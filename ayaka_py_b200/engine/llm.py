@@ -22,7 +22,7 @@ class LLM:
         """``model``: a folder with config.json and model.safetensors, or a
         ``ModelConfig`` for random weights drawn from ``seed``.  ``options``
         are ``EngineConfig`` fields (dtype, kv_pages, page_size, max_requests,
-        batch_tokens, prefill_chunk, max_model_len, decode_graph)."""
+        batch_tokens, prefill_chunk, max_model_len, decode_graph, lookahead)."""
         self.engine_config = engine_config or EngineConfig(**options)
         if isinstance(model, ModelConfig):
             self.model_config = model

@@ -149,3 +149,47 @@ def test_programmatic_dependent_launch_on_and_off_agree(model_folders):
     finally:
         ops.set_pdl(True)
     assert out[False] == out[True]
+
+
+@pytest.mark.parametrize("graph", [False, True], ids=["eager", "graphs"])
+def test_lookahead_gives_the_same_tokens(model_folders, graph):
+    """The next decode step launched before this step's tokens are on the host
+    (its tokens copied from the sampler's output on the device) against the
+    plain loop: same tokens and finish reasons with greedy and seeded sampling,
+    requests that stop on a stop id in the middle of a run, and a late arrival."""
+    from ayaka_py_b200 import EngineConfig, Request, SamplingParams, StopCriteria
+    from ayaka_py_b200.engine.engine import Engine
+    from ayaka_py_b200.engine.loading import load_model
+    folder, cfg, weights = model_folders["B"]
+    prompts = tiny_models.prompts(cfg, [5, 17, 33, 9], seed=31)
+    params = [SamplingParams(temperature=0.0), SamplingParams(temperature=0.9, seed=11, top_k=40),
+              SamplingParams(temperature=0.0), SamplingParams(temperature=0.8, seed=3)]
+    _, model = load_model(folder, "bfloat16", "cuda")
+
+    def run(lookahead, stops):
+        config = EngineConfig(dtype="bfloat16", page_size=8, kv_pages=64, batch_tokens=64, prefill_chunk=32,
+                              decode_graph=graph, lookahead=lookahead)
+        engine = Engine(model, config, eos_token_id=None)
+        for i in range(3):
+            engine.submit(Request(f"r{i}", prompts[i], params[i], stops[i]))
+        steps, ahead = 0, 0
+        while engine.has_work():
+            if steps == 12:
+                engine.submit(Request("r3", prompts[3], params[3], stops[3]))
+            engine.step()
+            ahead += engine._inflight is not None
+            steps += 1
+        engine.cache.assert_clean()
+        out, engine.finished = engine.finished, {}
+        return {k: (v.token_ids, v.finish_reason) for k, v in out.items()}, ahead
+
+    free = [StopCriteria(max_tokens=n, ignore_eos=True) for n in (40, 25, 31, 18)]
+    base, _ = run(False, free)
+    # stop ids taken from the middle of what two of the requests generate
+    stops = [StopCriteria(max_tokens=40, stop_token_ids=(base["r0"][0][13],)), free[1],
+             StopCriteria(max_tokens=31, stop_token_ids=(base["r2"][0][20],), min_tokens=4), free[3]]
+    want, none_ahead = run(False, stops)
+    got, some_ahead = run(True, stops)
+    assert none_ahead == 0 and some_ahead > 10
+    assert got == want
+    assert want["r0"][1] == "stop" and len(want["r0"][0]) <= 14

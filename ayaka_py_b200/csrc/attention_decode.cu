@@ -268,30 +268,40 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   if (warp_has_keys) {
     const size_t row_elems = (size_t)Hkv * DH;
     const size_t head_off = (size_t)kvh * DH;
-    // copies: lane covers piece (lane % PPR) of rows (lane / PPR) + i * (32 / PPR)   [PPR <= 32]
+    // copies: lane covers piece (lane % PPR) of rows (lane / PPR) + i * (32 / PPR)   [PPR <= 32].
+    // Keys and values lie at the same offsets of their caches: the offsets are worked out once
+    // (32-bit, in elements; the host has checked that a cache has fewer than 2^32).
     constexpr int RPI = 32 / PPR;                // rows per instruction
+    constexpr int COPIES = 32 / RPI;
     const int my_piece = lane % PPR, my_row0 = lane / PPR;
+    const uint32_t lane_off = (uint32_t)head_off + (uint32_t)my_piece * 8u;
+    uint32_t off[COPIES];
+    uint32_t ok_bits = 0u;
+    int fresh_i = -1;                            // the copy that brings the step's own key, if it is this lane's
 #pragma unroll
-    const __nv_bfloat16* fresh = knew;
+    for (int i = 0; i < COPIES; ++i) {
+      const int row = my_row0 + i * RPI;         // within the warp's 32 keys
+      const int key = wk0 + row;
+      const int page = __shfl_sync(0xffffffffu, my_page, (key >> page_shift) - first_logical);
+      const bool ok = key >= w_lo && key < w_hi && page > 0;
+      off[i] = ok ? (((uint32_t)page << page_shift) + (uint32_t)(key & (page_size - 1))) * (uint32_t)row_elems + lane_off : 0u;
+      ok_bits |= (ok ? 1u : 0u) << i;
+      if (knew != nullptr && key == pos && ok) fresh_i = i;
+    }
+#pragma unroll
     for (int mat = 0; mat < 2; ++mat) {
-      const __nv_bfloat16* cache = mat == 0 ? kcache : vcache;
-      const uint32_t base = mat == 0 ? ks_base : vs_base;
+      __nv_bfloat16* cache = mat == 0 ? kcache : vcache;
+      const uint32_t base = (mat == 0 ? ks_base : vs_base) + (uint32_t)(warp * 32 + my_row0) * ROW_BYTES;
 #pragma unroll
-      for (int i = 0; i < 32 / RPI; ++i) {
-        const int row = my_row0 + i * RPI;       // within the warp's 32 keys
-        const int key = wk0 + row;
-        const int page = __shfl_sync(0xffffffffu, my_page, (key >> page_shift) - first_logical);
-        const bool ok = key >= w_lo && key < w_hi && page > 0;
-        const size_t off = ok ? ((((size_t)page) << page_shift) + (key & (page_size - 1))) * row_elems + head_off + my_piece * 8 : 0;
-        const __nv_bfloat16* src = cache + off;
-        if (fresh != nullptr && key == pos) {      // the step's own key: not in the cache yet
-          src = (mat == 0 ? knew : vnew) + (size_t)r * new_stride + head_off + my_piece * 8;
-          if (ok && chunk == 0) {                  // one CTA per key/value head files it
-            __nv_bfloat16* dst = (mat == 0 ? kcache : vcache) + off;
-            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-          }
+      for (int i = 0; i < COPIES; ++i) {
+        const int row = my_row0 + i * RPI;
+        const __nv_bfloat16* src = cache + off[i];
+        if (i == fresh_i) {                      // the step's own key: not in the cache yet
+          src = (mat == 0 ? knew : vnew) + (size_t)r * new_stride + lane_off;
+          if (chunk == 0)                        // one CTA per key/value head files it
+            *reinterpret_cast<uint4*>(cache + off[i]) = *reinterpret_cast<const uint4*>(src);
         }
-        cp_async16_zfill(base + (warp * 32 + row) * ROW_BYTES + swizzled_piece<PPR>(row, my_piece) * 16, src, ok);
+        cp_async16_zfill(base + (uint32_t)(i * RPI) * ROW_BYTES + swizzled_piece<PPR>(row, my_piece) * 16, src, (ok_bits >> i) & 1u);
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
@@ -444,12 +454,13 @@ extern "C" int ayk_kv_append(void* kcache, void* vcache, const void* k, const vo
 // position.  parts = ceil(longest possible context / 128) (fixed per engine);
 // scratch holds R * H * parts * (Dh + 2) floats.  knew, vnew (or null): this step's key and
 // value rows [R, new_stride], not yet in the cache: they are stored at (request r, position
-// req_pos0[r]) on the way (row_req[r] must be r: one row per request, in order).
+// req_pos0[r]) on the way (row_req[r] must be r: one row per request, in order).  cache_pages: pages of
+// a cache tensor (the tensor-core kernel addresses a cache with 32-bit element offsets).
 AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void* kcache, void* vcache,
                                     const int* table, int table_stride, const int* req_pos0, int R, int H, int Hkv,
                                     int Dh, int page_size, float scale, int window, int parts, float* scratch,
                                     const void* knew, const void* vnew, int new_stride, const int* row_req,
-                                    int dtype, cudaStream_t stream) {
+                                    long long cache_pages, int dtype, cudaStream_t stream) {
   if (R == 0) return 0;
   AYK_REQUIRE(Dh >= 16 && Dh % 16 == 0 && Dh <= MAX_DH, "ayk_attention_decode: head size %d is not a multiple of 16 in [16, %d]", Dh, MAX_DH);
   AYK_REQUIRE(Hkv >= 1 && H % Hkv == 0, "ayk_attention_decode: %d heads cannot share %d key/value heads", H, Hkv);
@@ -459,9 +470,10 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void
               "ayk_attention_decode: new keys come with new values and the rows' requests");
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
+  const unsigned long long cache_elems = (unsigned long long)cache_pages * page_size * Hkv * Dh;    // of one cache tensor
   const bool mma_ok = dtype == AYK_DTYPE_BF16 && (Dh == 32 || Dh == 64 || Dh == 128) && (1 << page_shift) == page_size &&
                       page_size >= 4 && q_stride % 2 == 0 && (uintptr_t)q % 4 == 0 && (uintptr_t)kcache % 16 == 0 &&
-                      (uintptr_t)vcache % 16 == 0 &&
+                      (uintptr_t)vcache % 16 == 0 && cache_elems < (1ull << 32) &&
                       (knew == nullptr || (new_stride % 8 == 0 && (uintptr_t)knew % 16 == 0 && (uintptr_t)vnew % 16 == 0));
   if (mma_ok) {
     const int group = H / Hkv, chunks = (group + 7) / 8, rows = group < 8 ? group : 8;

@@ -409,7 +409,7 @@ def attention_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor
                                      ctypes.c_int(window or 0), ctypes.c_int(parts), _ptr(scratch),
                                      _ptr(k_new), _ptr(v_new), ctypes.c_int(new_stride),
                                      _ptr(_i32(row_req, "row_req") if row_req is not None else None),
-                                     ctypes.c_int(_tag(q.dtype)), _stream()))
+                                     ctypes.c_longlong(pages), ctypes.c_int(_tag(q.dtype)), _stream()))
     global launches
     launches += 1            # the call launches two kernels (partitions, merge)
     return out

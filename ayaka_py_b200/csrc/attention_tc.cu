@@ -6,17 +6,20 @@
 // (page_size keys x 64 x bf16, 128-byte swizzle) straight from the cache into a
 // K tile and a V tile; S = Q K^T (128 x 128, float32) is made in tensor memory;
 // four warps hold one row each per thread, read their row of S, apply scale and
-// mask, keep the running maximum and sum in 32-bit (online softmax, natural
-// exp), write P as bfloat16 into shared memory in the MMA's swizzled layout;
+// mask, keep the running maximum and sum in 32-bit (online softmax; scores are
+// kept times log2(e) so that an exponential is one ex2), write P as bfloat16
+// into shared memory in the MMA's swizzled layout;
 // O_tile = P V (128 x 64) is made in tensor memory and added, per thread, to the
 // row's running output in registers.  Formula and masking as in the general
 // kernel (kernel/triton/paged_attention.py:295-355 in the reference, which walks
 // the keys per query token without tensor cores).
 //
 // Warps 0..3: softmax and output (warp w owns TMEM lanes 32w..32w+31); warp 4:
-// TMA producer; warp 5: MMA issue and TMEM allocation.  K/V tiles are double
-// buffered.  Every mbarrier wait is bounded; a wait that runs out records a code
-// in the error word and the CTA winds down.
+// TMA producer (lane p brings page p of a tile); warp 5: MMA issue and TMEM
+// allocation.  K/V tiles are double buffered; two CTAs share an SM.  The grid is
+// (heads, row tiles) with the tiles that see the most keys first.  Every
+// mbarrier wait is bounded; a wait that runs out records a code in the error
+// word and the CTA winds down.
 #include <cuda.h>
 #include <math.h>
 

@@ -16,10 +16,12 @@
 // sum in 32-bit).  K is cut into blocks of 64 elements (128 bytes, the 128-byte
 // swizzle); a ring of stages connects producer and MMA through mbarriers.
 //
-// Split-K: for skinny products (decode) gridDim.z CTAs share one output tile;
-// each writes its 32-bit partial tile to scratch, the last to arrive sums the
-// partials in split order (so the result does not depend on arrival order) and
-// runs the epilogue.
+// Split-K: for skinny products (decode) gridDim.z CTAs share one output tile.
+// Up to 64 rows with 2, 4 or 8 splits they form a thread-block cluster and
+// exchange their 32-bit partial sums through distributed shared memory (see
+// CLUSTER below); otherwise each writes its partial tile to scratch and the last
+// to arrive sums the partials.  Either way the sum runs in split order, so the
+// result does not depend on arrival order.
 //
 // Every wait on an mbarrier is bounded; on a time-out the kernel records an
 // error word, waits (bounded) for its own copies, frees its TMEM and returns.

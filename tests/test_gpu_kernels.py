@@ -336,6 +336,8 @@ TC_ATTENTION_CASES = [
     ([70, 200], [250, 57], 4, 2, 64, None),
     ([33, 260], [100, 0], 2, 2, 128, None),
     ([150, 9], [140, 300], 2, 2, 16, 100),
+    # 40 requests (two groups of 32 in the kernel's search for its tile), tiles of very different length
+    ([3] * 20 + [130, 260] + [5] * 17 + [129], [0] * 20 + [40, 0] + [7] * 17 + [200], 2, 1, 16, None),
 ]
 
 

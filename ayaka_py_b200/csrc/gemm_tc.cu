@@ -217,8 +217,12 @@ __device__ __forceinline__ void store_chunk_pre(const EpilogueArgs& a, int tok0,
 // Split-K inside a thread-block cluster (up to 64 rows, 2, 4 or 8 splits): the CTAs that share an
 // output tile are one cluster along z.  Each owns 128 / splits of the tile's out features: every
 // epilogue thread sends its partial sums straight into the owner's shared memory
-// (st.shared::cluster), one cluster barrier later the owner adds the `splits` partials in split
-// order and finishes its rows.  No scratch in global memory, no fence, no counter, no second pass
+// (st.shared::cluster); an owner that knows they are in adds the `splits` partials in split order
+// and finishes its rows.  It knows either by one cluster barrier, or (DELIVERIES) by counting
+// arrivals at an mbarrier of its own.  In the second form a CTA leaves only after every partner has
+// delivered to it and after it has delivered to every partner, so nobody writes into a CTA that is
+// gone; a cluster barrier at the head of the kernel (arrive in the set-up, wait just before the
+// first delivery) makes sure the partners' mbarriers exist.  No scratch in global memory, no fence, no counter, no second pass
 // through L2; measured against the scratch form inside the decode graph this takes the product
 // from about 10 to 7.5 us.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
@@ -229,9 +233,24 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Bounded wait for arrivals that come from other CTAs of the cluster (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* error, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  atomicExch(error, code);
+  return false;
 }
 
 template <int BT, bool CLUSTER = false>
@@ -239,6 +258,10 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const EpilogueArgs args) {
   constexpr int STAGES = CLUSTER ? cluster_stages_for(BT) : stages_for(BT);
+  // How an owner learns that the partial sums are in: 16 rows, one cluster barrier of all threads
+  // (measured 2 % faster at one request); more rows, deliveries counted by the owner's mbarrier, so
+  // that nobody waits for the slowest CTA of the cluster but the owner it delivers to (+4 % at 64).
+  constexpr bool DELIVERIES = CLUSTER && BT > 16;
   constexpr int B_BYTES = BT * BLOCK_K * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TCOLS = tmem_cols_for(BT);
@@ -255,7 +278,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
   volatile int* flag_ptr = (volatile int*)(smem_raw + (tmem_slot + 4 - raw));
   // cluster form: [split][row of this CTA's share][BT tokens] partial sums, 128 * BT floats
-  const uint32_t red = (tmem_slot + 8u + 15u) & ~15u;
+  const uint32_t share_bar = tmem_slot + 8u;                 // cluster form: deliveries of partial sums
+  const uint32_t red = (tmem_slot + 16u + 15u) & ~15u;
   const float* red_ptr = (const float*)(smem_raw + (red - raw));
 
   if (threadIdx.x == 0) mark(args, 0);
@@ -277,6 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(tmem_full_bar, 1);
+    if (DELIVERIES) mbar_init(share_bar, BLOCK_N / min(BLOCK_N / (int)gridDim.z, 32));   // one arrival per group of lanes
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -286,6 +311,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
+  if (DELIVERIES) cluster_arrive();       // matched by cluster_wait() in every role below
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
   if (threadIdx.x == 0) mark(args, 1);
@@ -335,6 +361,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
     __syncwarp();
+    if (DELIVERIES) cluster_wait();
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true;
@@ -362,6 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mark(args, 5);
     }
     __syncwarp();
+    if (DELIVERIES) cluster_wait();
   } else {
     // Epilogue: warp w may read TMEM lanes 32 * (w % 4) ... + 31.
     const int quarter = warp & 3;
@@ -383,6 +411,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       share_ok = mbar_wait(tmem_full_bar, 0u, args.error, 4);
       tc_fence_after();
+      if (DELIVERIES) cluster_wait();      // every partner has set up its barriers (long ago)
+      const int owner = (quarter * 32 + lane) / rows_per;
       if (share_ok) {
         // Feature `local` of the tile belongs to CTA local / rows_per of the cluster; its BT sums go to
         // [this split][local % rows_per][0 .. BT) of that CTA's buffer, the 16-byte pieces of a row
@@ -401,6 +431,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
           }
         }
+      }
+      // delivered (or given up: the error word says so): one lane arrives for the lanes that share its owner
+      if (DELIVERIES) {
+        __syncwarp();
+        if ((lane & (min(rows_per, 32) - 1)) == 0) mbar_arrive_cluster(map_to_cta(share_bar, (uint32_t)owner));
       }
     } else {
     pdl_wait();        // residual, partials and C belong to kernels before this one until here
@@ -501,23 +536,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 
   if constexpr (CLUSTER) {
-    // Every thread of every CTA of the cluster: the partial sums have landed in their owners.
-    cluster_sync_all();
-    if (warp >= 2 && share_ok) {
-      const int splits = gridDim.z, rows_per = BLOCK_N / splits, e = threadIdx.x - 64;
-      const int my_row = e % rows_per, tok_first = e / rows_per, tok_step = BLOCK_N / rows_per;
-      const int nn = n0 + (int)blockIdx.z * rows_per + my_row;
+    if (!DELIVERIES) {                     // every thread of every CTA of the cluster
+      cluster_arrive();
+      cluster_wait();
+    }
+    if (warp >= 2) {
+      bool got = true;
+      if (DELIVERIES) {                    // one lane per warp watches for the deliveries to this CTA
+        if (lane == 0) got = mbar_wait_cluster(share_bar, 0u, args.error, 6);
+        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+      }
+      if (got && share_ok) {
+        const int splits = gridDim.z, rows_per = BLOCK_N / splits, e = threadIdx.x - 64;
+        const int my_row = e % rows_per, tok_first = e / rows_per, tok_step = BLOCK_N / rows_per;
+        const int nn = n0 + (int)blockIdx.z * rows_per + my_row;
 #pragma unroll
-      for (int i = 0; i < SHARE; ++i) {
-        const int tl = tok_first + tok_step * i, tok = t0 + tl;
-        if (tl < BT && nn < args.N && tok < args.M) {
-          const int at = ((tl >> 2) ^ (my_row & (BT / 4 - 1))) * 4 + (tl & 3);
-          float v = 0.f;
-          for (int z = 0; z < splits; ++z) v += red_ptr[(z * rows_per + my_row) * BT + at];     // split order
-          const float y = apply_activation(v + share_bias, args.act) + share_res[i];
-          const size_t idx = (size_t)tok * args.N + nn;
-          if (args.out_bf16) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(y);
-          else ((float*)args.C)[idx] = y;
+        for (int i = 0; i < SHARE; ++i) {
+          const int tl = tok_first + tok_step * i, tok = t0 + tl;
+          if (tl < BT && nn < args.N && tok < args.M) {
+            const int at = ((tl >> 2) ^ (my_row & (BT / 4 - 1))) * 4 + (tl & 3);
+            float part[8];
+#pragma unroll
+            for (int z = 0; z < 8; ++z) part[z] = z < splits ? red_ptr[(z * rows_per + my_row) * BT + at] : 0.f;
+            float v = 0.f;
+#pragma unroll
+            for (int z = 0; z < 8; ++z) v += part[z];                   // split order
+            const float y = apply_activation(v + share_bias, args.act) + share_res[i];
+            const size_t idx = (size_t)tok * args.N + nn;
+            if (args.out_bf16) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(y);
+            else ((float*)args.C)[idx] = y;
+          }
         }
       }
     }
@@ -601,7 +649,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& arg
 template <int BT>
 int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& args, int splits, cudaStream_t stream) {
   constexpr int STAGES = cluster_stages_for(BT);
-  constexpr size_t SMEM = 1024 + (size_t)STAGES * (A_BYTES + BT * BLOCK_K * 2) + 8 * (2 * STAGES + 2) + 16 + BLOCK_N * BT * sizeof(float);
+  constexpr size_t SMEM = 1024 + (size_t)STAGES * (A_BYTES + BT * BLOCK_K * 2) + 8 * (2 * STAGES + 3) + 16 + BLOCK_N * BT * sizeof(float);
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);

@@ -27,6 +27,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -36,87 +37,6 @@ constexpr int DH = 64;           // head size
 constexpr int THREADS = 192;
 constexpr int TILE_BYTES = 128 * 128;            // 128 rows x 64 bf16
 constexpr int TMEM_COLS = 256;                   // S: columns 0..127, O: columns 128..191
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error, int code) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-    if (mbar_try(bar, parity)) return true;
-  atomicExch(error, code);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
-}
-// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
-// The same bits describe a K-major operand (rows = M or N, 64 elements of K per
-// row) and an MN-major operand (rows = K, 64 elements of N per row); which one
-// is meant is said in the instruction descriptor.
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-// kind::f16: D float32, A and B bfloat16; b_mn: B is MN-major.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 struct AttnArgs {
   __nv_bfloat16* out;            // [T, H * 64]
@@ -314,6 +234,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (c >= warp_hi || c + 32 <= warp_lo) continue;       // the same for the whole warp
         uint32_t r[32];
         tmem_ld32(tmem_s + lane_addr + c, r);
+        tmem_ld_wait();
         if (unmasked) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
@@ -333,7 +254,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const bool warp_sees = !(c >= warp_hi || c + 32 <= warp_lo);
         const bool row_sees = c < hi && c + 32 > lo;
         uint32_t r[32];
-        if (warp_sees) tmem_ld32(tmem_s + lane_addr + c, r);
+        if (warp_sees) { tmem_ld32(tmem_s + lane_addr + c, r); tmem_ld_wait(); }
 #pragma unroll
         for (int g = 0; g < 32; g += 8) {           // 8 keys = one 16-byte chunk of the row of P
           uint32_t packed[4] = {0u, 0u, 0u, 0u};
@@ -372,6 +293,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int c = 0; c < DH; c += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_o + lane_addr + c, r);
+        tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) o_acc[c + j] += __uint_as_float(r[j]);
       }

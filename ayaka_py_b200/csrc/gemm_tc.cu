@@ -35,6 +35,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -43,7 +44,6 @@ constexpr int BLOCK_K = 64;           // bf16 elements per stage and row: 128 by
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2;
 constexpr int THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 // Up to 32 rows: 5 stages of 18-20 KB, about 100 KB per CTA, leave room for two CTAs per SM, so that
 // the next kernel's CTAs (launched early, see pdl_wait) stream their weights beside the CTAs of the
@@ -54,101 +54,6 @@ constexpr int stages_for(int bt) { return bt >= 256 ? 4 : (bt >= 128 ? 6 : (bt >
 constexpr int tmem_cols_for(int bt) { return bt < 32 ? 32 : bt; }
 // The cluster form adds 128 * BT floats for the exchange of partial sums and still wants two CTAs per SM.
 constexpr int cluster_stages_for(int bt) { return bt >= 64 ? 3 : (bt >= 32 ? 4 : 5); }
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false (and records `code`) when the barrier did not
-// complete within WAIT_LIMIT polls.
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error, int code) {
-  // A few non-blocking tests first: a phase that is complete already, or nearly, is seen at once
-  // (the possibly suspending try_wait cost ~290 cycles per K block on the MMA thread).
-#pragma unroll 1
-  for (int i = 0; i < 64; ++i) {
-    if (mbar_test(bar, parity)) return true;
-  }
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    if (mbar_try(bar, parity)) return true;
-  }
-  atomicExch(error, code);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart (stride byte offset), version 1 (sm_100).
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;                  // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset
-  d |= (uint64_t)1 << 46;                  // descriptor version
-  d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
-  return d;
-}
-
-// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 struct EpilogueArgs {
   void* C;
@@ -225,34 +130,6 @@ __device__ __forceinline__ void store_chunk_pre(const EpilogueArgs& a, int tok0,
 // first delivery) makes sure the partners' mbarriers exist.  No scratch in global memory, no fence, no counter, no second pass
 // through L2; measured against the scratch form inside the decode graph this takes the product
 // from about 10 to 7.5 us.
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// Bounded wait for arrivals that come from other CTAs of the cluster (acquire at cluster scope).
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* error, int code) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  atomicExch(error, code);
-  return false;
-}
-
 template <int BT, bool CLUSTER = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -424,6 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int c = 0; c < BT; c += 16) {
           uint32_t r[16];
           tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
+          tmem_ld_wait();
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int piece = ((c >> 2) + q) ^ (rrow & (BT / 4 - 1));
@@ -456,6 +334,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (int c = 0; c < BT; c += 16) {
         uint32_t r[16];
         tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
+        tmem_ld_wait();
         if (n < args.N && t0 + c < args.M) {
           if (splits == 1) {
             float v[16];

@@ -337,3 +337,175 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         got = trace_tools.collect(trace, outs)
         assert trace_tools.first_difference(got, want, 1e-4) is None
         session.cache.assert_clean()
+
+
+# ------------------------------------- toy parts: rotating positions, routing --
+
+@dataclass(frozen=True)
+class ToyMixedConfig:
+    """A second toy architecture: layer 0 is the framework's attention (2 query
+    heads on 1 key/value head, a window) with a rotating position encoding and a
+    routed feed-forward that are defined here; layer 1 is the running-mean mixer
+    of the first toy with the framework's MLP.  Two cache groups come out of it:
+    pages for layer 0, state slots for layer 1."""
+    ARCHITECTURE: ClassVar[str] = "ToyMixedLM"
+    vocab_size: int = 61
+    width: int = 32
+    head_dim: int = 16
+    experts: int = 3
+    window: int = 21
+    positions: int = 96
+
+    @classmethod
+    def from_dict(cls, values):
+        names = ("vocab_size", "width", "head_dim", "experts", "window", "positions")
+        return cls(**{k: values[k] for k in names if k in values})
+
+    def to_dict(self):
+        return {"architectures": [self.ARCHITECTURE], **{k: getattr(self, k) for k in
+                ("vocab_size", "width", "head_dim", "experts", "window", "positions")}}
+
+
+def register_toy_mixed():
+    from ayaka_py_b200.parts import (FeedForward, Init, LayerSpec, ModelSpec, PartSpec, PositionEncoding, RunStep,
+                                     Source, TensorDecl, register_part)
+    from ayaka_py_b200.registry import Architecture, register_architecture
+    register_toy()                               # the running-mean mixer
+
+    class TurningPositions(PositionEncoding):
+        """No table: queries and keys are turned, pair (2i, 2i+1) of every head by
+        the angle position * base^(-i / pairs) (32-bit), in place."""
+
+        def __init__(self, head_dim, base, dtype, device):
+            self.head_dim, self.base = head_dim, float(base)
+
+        def tensors(self):
+            return {}
+
+        def rotate_qk(self, q, k, heads, kv_heads, head_dim, ctx):
+            pairs = head_dim // 2
+            freq = self.base ** (-torch.arange(pairs, device=q.device, dtype=torch.float32) / pairs)
+            angle = ctx.positions.float()[:, None] * freq[None, :]
+            cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+            for x, n in ((q, heads), (k, kv_heads)):
+                v = x.unflatten(1, (n, head_dim)).float()
+                a, b = v[..., 0::2], v[..., 1::2]
+                turned = torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).flatten(-2)
+                x.copy_(turned.flatten(1).to(x.dtype))
+
+    class RoutedFeedForward(FeedForward):
+        """Each row goes to the expert its router likes best (32-bit logits): out =
+        residual + p_e * tanh(h) * gain_e, p = softmax over the experts."""
+
+        def __init__(self, width, experts, dtype, device):
+            self.width, self.experts = width, experts
+            self.router = self.gain = None
+
+        def tensors(self):
+            return {"router": TensorDecl((self.experts, self.width), "vector"),
+                    "gain": TensorDecl((self.experts, self.width), "vector")}
+
+        def forward(self, h, residual, ctx):
+            logits = h.float() @ self.router.t()
+            p = torch.softmax(logits, dim=-1)
+            e = torch.argmax(logits, dim=-1)
+            return residual + p.gather(1, e[:, None]) * torch.tanh(h.float()) * self.gain[e]
+
+    register_part("toy_turning_positions", TurningPositions)
+    register_part("toy_routed_ffn", RoutedFeedForward)
+
+    def spec(cfg: ToyMixedConfig) -> ModelSpec:
+        d, H, Dh = cfg.width, 2, cfg.head_dim
+        norm = lambda name: PartSpec("layernorm", {"width": d, "eps": 1e-5},
+                                     {"weight": Source(name + ".g", init=Init(0.1, 1.0)), "bias": Source(name + ".b", init=Init(0.1))})
+        attention = PartSpec("attention", {"width": d, "num_heads": H, "kv_heads": 1, "head_dim": Dh, "scale": Dh ** -0.5,
+                                           "window": cfg.window, "bias": False},
+                             {"qkv_weight": Source("l0.qkv", init=Init(0.4)), "out_weight": Source("l0.out", init=Init(0.3))})
+        routed = PartSpec("toy_routed_ffn", {"width": d, "experts": cfg.experts},
+                          {"router": Source("l0.router", init=Init(0.5)), "gain": Source("l0.gain", init=Init(0.5))})
+        mean = PartSpec("toy_running_mean", {"width": d}, {"weight": Source("l1.mix", init=Init(0.3))})
+        mlp = PartSpec("mlp", {"width": d, "inner": 40, "activation": "gelu_erf", "bias": True},
+                       {"up_weight": Source("l1.up", init=Init(0.3)), "up_bias": Source("l1.up_b", init=Init(0.1)),
+                        "down_weight": Source("l1.down", init=Init(0.3)), "down_bias": Source("l1.down_b", init=Init(0.1))})
+        layers = (LayerSpec(norm("l0.n1"), attention, norm("l0.n2"), routed),
+                  LayerSpec(norm("l1.n1"), mean, norm("l1.n2"), mlp))
+        return ModelSpec(cfg.vocab_size, d, cfg.positions,
+                         PartSpec("token_embedding", {"vocab": cfg.vocab_size, "width": d}, {"weight": Source("emb", init=Init(1.0))}),
+                         PartSpec("toy_turning_positions", {"head_dim": Dh, "base": 50.0}, {}),
+                         layers, (RunStep(0), RunStep(1)), norm("final"),
+                         PartSpec("lm_head", {"vocab": cfg.vocab_size, "width": d}, {"weight": Source("head", init=Init(0.3))}))
+
+    register_architecture(Architecture("ToyMixedLM", "toy_mixed", ToyMixedConfig, spec))
+
+
+def plain_toy_mixed(cfg, t, tokens):
+    """Whole sequence, float64, no cache."""
+    T, d, H, Dh = len(tokens), cfg.width, 2, cfg.head_dim
+    x = t["emb"][tokens]
+    # layer 0: windowed attention of 2 heads over one key/value head, turned by position
+    h = plain_gpt2.layer_norm(x, t["l0.n1.g"], t["l0.n1.b"], 1e-5)
+    qkv = h @ t["l0.qkv"].T
+    q, k, v = qkv[:, :H * Dh].reshape(T, H, Dh), qkv[:, H * Dh:H * Dh + Dh], qkv[:, H * Dh + Dh:]
+    pairs = Dh // 2
+    angle = np.arange(T)[:, None] * 50.0 ** (-np.arange(pairs) / pairs)[None, :]
+
+    def turn(a):                                  # [T, ..., Dh]
+        out = np.empty_like(a)
+        c, s = np.cos(angle), np.sin(angle)
+        if a.ndim == 3:
+            c, s = c[:, None, :], s[:, None, :]
+        out[..., 0::2] = a[..., 0::2] * c - a[..., 1::2] * s
+        out[..., 1::2] = a[..., 0::2] * s + a[..., 1::2] * c
+        return out
+
+    q, k = turn(q), turn(k)
+    o = np.zeros((T, H, Dh))
+    for i in range(T):
+        lo = max(0, i - cfg.window + 1)
+        for hd in range(H):
+            s = k[lo:i + 1] @ q[i, hd] * Dh ** -0.5
+            p = np.exp(s - s.max())
+            o[i, hd] = (p / p.sum()) @ v[lo:i + 1]
+    x = x + o.reshape(T, H * Dh) @ t["l0.out"].T
+    h = plain_gpt2.layer_norm(x, t["l0.n2.g"], t["l0.n2.b"], 1e-5)
+    logits = h @ t["l0.router"].T
+    p = np.exp(logits - logits.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    e = logits.argmax(-1)
+    x = x + p[np.arange(T), e][:, None] * np.tanh(h) * t["l0.gain"][e]
+    # layer 1: running mean, then the MLP
+    h = plain_gpt2.layer_norm(x, t["l1.n1.g"], t["l1.n1.b"], 1e-5)
+    x = x + (np.cumsum(h, axis=0) / np.arange(1, T + 1)[:, None]) @ t["l1.mix"].T
+    h = plain_gpt2.layer_norm(x, t["l1.n2.g"], t["l1.n2.b"], 1e-5)
+    x = x + plain_gpt2.activation("gelu", h @ t["l1.up"].T + t["l1.up_b"]) @ t["l1.down"].T + t["l1.down_b"]
+    return plain_gpt2.layer_norm(x, t["final.g"], t["final.b"], 1e-5) @ t["head"].T
+
+
+def test_toy_positions_routing_and_mixed_layers_without_touching_the_framework(tmp_path):
+    """Another position encoding (through the attention part's rotate_qk hook), a
+    feed-forward with routing, and layers of different kinds in one model, all
+    registered from this file: built, given random weights, and replayed whole,
+    in portions and mixed with few pages, against the plain formulas."""
+    import trace_tools
+    from ayaka_py_b200.parts.base import KVNeed, StateNeed
+    from ayaka_py_b200.replay import ReplaySession
+    from ayaka_py_b200.weights import write_random_model
+
+    register_toy_mixed()
+    cfg = ToyMixedConfig()
+    folder = write_random_model(tmp_path / "mixed", cfg, seed=9, dtype="float32")
+    tensors = {k: v.astype(np.float64) for k, v in plain_gpt2.read_safetensors(folder / "model.safetensors").items()}
+    rs = np.random.RandomState(3)
+    reqs = {f"m{i}": rs.randint(0, cfg.vocab_size, n).tolist() for i, n in enumerate([50, 9, 64, 27])}
+    want = {rid: plain_toy_mixed(cfg, tensors, toks) for rid, toks in reqs.items()}
+    for trace in (trace_tools.whole(reqs), trace_tools.tail_decoded(reqs, tail=8), trace_tools.portions(reqs),
+                  trace_tools.mixed(reqs, seed=4)):
+        session = ReplaySession(folder, "float32", max_tokens=256, page_size=8)
+        needs = sorted(type(g.need).__name__ for g in session.model.groups)
+        assert needs == ["KVNeed", "StateNeed"]
+        kv = [g.need for g in session.model.groups if isinstance(g.need, KVNeed)][0]
+        assert (kv.kv_heads, kv.head_dim, kv.window) == (1, cfg.head_dim, cfg.window)
+        outs = [None if (o := session.step(rec)) is None or o.shape[0] == 0 else o.cpu().numpy() for rec in trace]
+        got = trace_tools.collect(trace, outs)
+        assert trace_tools.first_difference(got, want, 2e-4) is None
+        session.cache.assert_clean()

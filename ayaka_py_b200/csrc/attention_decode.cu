@@ -227,10 +227,15 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   constexpr int ROW_BYTES = DH * 2;
   const long item = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int part = (int)(item % parts);
-  const int chunk = (int)((item / parts) % chunks);
-  const int kvh = (int)((item / ((long)parts * chunks)) % Hkv);
-  const int r = (int)(item / ((long)parts * chunks * Hkv));
+  // The partition is the slowest index: the CTAs of the first partitions, which every request
+  // has, get their places first; those of partitions beyond a request's context come last and
+  // leave at once (measured inside a decode step at 8 requests: empty CTAs had held a place for
+  // 3.6 us each while they waited to write a marker).
+  const long per_part = (long)gridDim.x / parts;
+  const int part = (int)(item / per_part);
+  const int chunk = (int)((item % per_part) % chunks);
+  const int kvh = (int)(((item % per_part) / chunks) % Hkv);
+  const int r = (int)((item % per_part) / ((long)chunks * Hkv));
   const int group = H / Hkv;
   const int head0 = kvh * group + chunk * 8;               // the query head of A row 0
   const int rows_here = min(rows, group - chunk * 8);
@@ -248,15 +253,12 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   const int k_hi = min(pos + 1, k_lo + PART);
   if (window > 0) k_lo = max(k_lo, pos - window + 1);
   const bool empty = k_lo >= k_hi;               // the same for the whole CTA
+  if (empty) return;                             // the merge knows from the position which partitions exist
   pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_dyn[];
   const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(smem_dyn);
   const uint32_t vs_base = ks_base + PART * ROW_BYTES;
   float* comb = reinterpret_cast<float*>(smem_dyn + 2 * PART * ROW_BYTES);      // [WARPS][rows][DH + 2]
-  if (empty && (int)threadIdx.x < rows_here) {
-    float* dst = scratch + ((size_t)(r * H + head0 + threadIdx.x) * parts + part) * (DH + 2);
-    dst[DH] = -INFINITY; dst[DH + 1] = 0.f;
-  }
 
   const int w_lo = max(k_lo, wk0), w_hi = min(k_hi, wk0 + 32);
   const bool warp_has_keys = !empty && w_lo < w_hi;
@@ -401,11 +403,16 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
 // Combines the partitions of one (request, head) in partition order.  Eight partitions at a time:
 // every load of the eight (maximum, sum, value) first, so that the kernel, which sits between the
 // attention and the next product of a decode step, makes one trip to L2 instead of three.
+// Which partitions hold keys follows from the request's position and the window, as in the
+// kernels that fill them; the others' scratch is never read (nobody wrote it).
 template <typename T>
-__global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict__ scratch, int H, int Dh, int parts) {
+__global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict__ scratch, int H, int Dh, int parts,
+                                    const int* __restrict__ req_pos0, int window) {
   pdl_trigger();
-  pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
+  const int pos = req_pos0[r];                   // the step's own input: read before the wait
+  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  pdl_wait();
   const float* base = scratch + (size_t)(r * H + h) * parts * (Dh + 2);
   T* o = out + ((size_t)r * H + h) * Dh;
   for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
@@ -414,8 +421,9 @@ __global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict
       float ms[8], ls[8], vs[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const bool in = s0 + i < parts;
-        const float* p = base + (size_t)(in ? s0 + i : 0) * (Dh + 2);
+        const int part = s0 + i;
+        const bool in = part < parts && max(part * PART, first_key) < min(pos + 1, (part + 1) * PART);
+        const float* p = base + (size_t)(in ? part : 0) * (Dh + 2);
         ms[i] = in ? p[Dh] : -INFINITY;
         ls[i] = in ? p[Dh + 1] : 0.f;
         vs[i] = in ? p[d] : 0.f;
@@ -498,7 +506,7 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void
     if (Dh == 32) AYK_DECODE_MMA(32); else if (Dh == 64) AYK_DECODE_MMA(64); else AYK_DECODE_MMA(128);
 #undef AYK_DECODE_MMA
     ayk_launch(decode_merge_kernel<__nv_bfloat16>, dim3(R, H), dim3(Dh <= 32 ? 32 : (Dh <= 64 ? 64 : 128)), 0, stream,
-               (__nv_bfloat16*)out, (const float*)scratch, H, Dh, parts);
+               (__nv_bfloat16*)out, (const float*)scratch, H, Dh, parts, req_pos0, window);
     return ayk_check_launch("ayk_attention_decode");
   }
   if (knew != nullptr &&
@@ -511,13 +519,13 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void
     ayk_launch(decode_split_kernel<float>, grid, dim3(WARPS * 32), 0, stream, scratch, (const float*)q, q_stride,
                (const float*)kcache, (const float*)vcache, table, table_stride, req_pos0, H, Hkv, Dh, page_size, scale,
                window, parts);
-    ayk_launch(decode_merge_kernel<float>, mgrid, dim3(mthreads), 0, stream, (float*)out, (const float*)scratch, H, Dh, parts);
+    ayk_launch(decode_merge_kernel<float>, mgrid, dim3(mthreads), 0, stream, (float*)out, (const float*)scratch, H, Dh, parts, req_pos0, window);
   } else {
     ayk_launch(decode_split_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), 0, stream, scratch, (const __nv_bfloat16*)q,
                q_stride, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, table, table_stride, req_pos0, H, Hkv,
                Dh, page_size, scale, window, parts);
     ayk_launch(decode_merge_kernel<__nv_bfloat16>, mgrid, dim3(mthreads), 0, stream, (__nv_bfloat16*)out,
-               (const float*)scratch, H, Dh, parts);
+               (const float*)scratch, H, Dh, parts, req_pos0, window);
   }
   return ayk_check_launch("ayk_attention_decode");
 }

@@ -198,6 +198,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   [[maybe_unused]] bool share_ok = false;
   constexpr int SHARE = BT / 2;                 // outputs per epilogue thread in the cluster form, at most (2 splits)
   [[maybe_unused]] float share_bias = 0.f, share_res[SHARE];
+  [[maybe_unused]] int share_row = 0, share_tok0 = 0, share_nn = 0;    // worked out before the main loop ends: divisions off the critical path
 
   if (warp == 0) {
     if (lane == 0) {
@@ -278,6 +279,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int splits = gridDim.z, rows_per = BLOCK_N / splits, e = threadIdx.x - 64;
       const int my_row = e % rows_per, tok_first = e / rows_per, tok_step = BLOCK_N / rows_per;
       const int nn = n0 + (int)blockIdx.z * rows_per + my_row;
+      share_row = my_row; share_tok0 = tok_first; share_nn = nn;
       share_bias = (nn < args.N && args.bias) ? __ldg(args.bias + nn) : 0.f;     // a weight: no need to wait for it
       pdl_wait();      // residual and C belong to kernels before this one until here
 #pragma unroll
@@ -426,9 +428,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
       }
       if (got && share_ok) {
-        const int splits = gridDim.z, rows_per = BLOCK_N / splits, e = threadIdx.x - 64;
-        const int my_row = e % rows_per, tok_first = e / rows_per, tok_step = BLOCK_N / rows_per;
-        const int nn = n0 + (int)blockIdx.z * rows_per + my_row;
+        const int splits = gridDim.z, rows_per = BLOCK_N / splits, tok_step = splits;      // 128 / rows_per
+        const int my_row = share_row, tok_first = share_tok0, nn = share_nn;
 #pragma unroll
         for (int i = 0; i < SHARE; ++i) {
           const int tl = tok_first + tok_step * i, tok = t0 + tl;

@@ -229,17 +229,15 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   constexpr int PPR = DH / 8;                    // 16-byte pieces per row
   constexpr int NT = DH / 8;                     // output tiles of the second product
   constexpr int ROW_BYTES = DH * 2;
-  const long item = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  // The partition is the slowest index: the CTAs of the first partitions, which every request
+  // Grid (key/value head x group of query heads, request, partition): no division to find one's work,
+  // and the partition is the slowest index, so the CTAs of the first partitions, which every request
   // has, get their places first; those of partitions beyond a request's context come last and
   // leave at once (measured inside a decode step at 8 requests: empty CTAs had held a place for
   // 3.6 us each while they waited to write a marker).
-  const long per_part = (long)gridDim.x / parts;
-  const int part = (int)(item / per_part);
-  const int chunk = (int)((item % per_part) % chunks);
-  const int kvh = (int)(((item % per_part) / chunks) % Hkv);
-  const int r = (int)((item % per_part) / ((long)chunks * Hkv));
+  const int part = blockIdx.z, r = blockIdx.y;
+  const int kvh = chunks == 1 ? (int)blockIdx.x : (int)blockIdx.x / chunks;
+  const int chunk = chunks == 1 ? 0 : (int)blockIdx.x % chunks;
   const int group = H / Hkv;
   const int head0 = kvh * group + chunk * 8;               // the query head of A row 0
   const int rows_here = min(rows, group - chunk * 8);
@@ -476,7 +474,7 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void
   if (R == 0) return 0;
   AYK_REQUIRE(Dh >= 16 && Dh % 16 == 0 && Dh <= MAX_DH, "ayk_attention_decode: head size %d is not a multiple of 16 in [16, %d]", Dh, MAX_DH);
   AYK_REQUIRE(Hkv >= 1 && H % Hkv == 0, "ayk_attention_decode: %d heads cannot share %d key/value heads", H, Hkv);
-  AYK_REQUIRE(parts >= 1 && parts <= 65535 && H <= 65535, "ayk_attention_decode: grid too large (heads %d, parts %d)", H, parts);
+  AYK_REQUIRE(parts >= 1 && parts <= 65535 && H <= 65535 && R <= 65535, "ayk_attention_decode: grid too large (requests %d, heads %d, parts %d)", R, H, parts);
   AYK_REQUIRE(dtype == AYK_DTYPE_F32 || dtype == AYK_DTYPE_BF16, "ayk_attention_decode: unknown dtype %d", dtype);
   AYK_REQUIRE((knew == nullptr) == (vnew == nullptr) && (knew == nullptr || row_req != nullptr),
               "ayk_attention_decode: new keys come with new values and the rows' requests");
@@ -503,7 +501,7 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void
       configured = true;
     }
 #define AYK_DECODE_MMA(D)                                                                                              \
-  ayk_launch(decode_mma_kernel<D>, dim3((unsigned)items), dim3(WARPS * 32), smem, stream, scratch,                      \
+  ayk_launch(decode_mma_kernel<D>, dim3(Hkv * chunks, R, parts), dim3(WARPS * 32), smem, stream, scratch,                      \
              (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, table, table_stride,    \
              req_pos0, H, Hkv, page_shift, scale_log2, window, parts, chunks, rows, (const __nv_bfloat16*)knew,         \
              (const __nv_bfloat16*)vnew, new_stride)

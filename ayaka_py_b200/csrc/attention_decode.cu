@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__ q, int q_stride,
                   __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
                   const int* __restrict__ table, int table_stride, const int* __restrict__ req_pos0,
-                  int H, int Hkv, int page_shift, float scale_log2, int window, int parts, int chunks, int rows,
+                  int H, int Hkv, int group, int page_shift, float scale_log2, int window, int parts, int chunks, int rows,
                   const __nv_bfloat16* __restrict__ knew, const __nv_bfloat16* __restrict__ vnew, int new_stride) {
   pdl_trigger();
   static_assert(WARPS * 32 == PART, "each warp owns 32 keys of the partition");
@@ -238,7 +238,6 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   const int part = blockIdx.z, r = blockIdx.y;
   const int kvh = chunks == 1 ? (int)blockIdx.x : (int)blockIdx.x / chunks;
   const int chunk = chunks == 1 ? 0 : (int)blockIdx.x % chunks;
-  const int group = H / Hkv;
   const int head0 = kvh * group + chunk * 8;               // the query head of A row 0
   const int rows_here = min(rows, group - chunk * 8);
   // Positions and block table are the step's inputs: they are read while the kernels before this one
@@ -503,7 +502,7 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void
 #define AYK_DECODE_MMA(D)                                                                                              \
   ayk_launch(decode_mma_kernel<D>, dim3(Hkv * chunks, R, parts), dim3(WARPS * 32), smem, stream, scratch,                      \
              (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, table, table_stride,    \
-             req_pos0, H, Hkv, page_shift, scale_log2, window, parts, chunks, rows, (const __nv_bfloat16*)knew,         \
+             req_pos0, H, Hkv, group, page_shift, scale_log2, window, parts, chunks, rows, (const __nv_bfloat16*)knew,  \
              (const __nv_bfloat16*)vnew, new_stride)
     if (Dh == 32) AYK_DECODE_MMA(32); else if (Dh == 64) AYK_DECODE_MMA(64); else AYK_DECODE_MMA(128);
 #undef AYK_DECODE_MMA

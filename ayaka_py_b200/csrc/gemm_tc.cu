@@ -288,17 +288,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         share_res[i] = (tok_first + tok_step * i < BT && nn < args.N && args.residual && tok < args.M)
                            ? args.residual[(size_t)tok * args.N + nn] : 0.f;
       }
+      // where this thread's partial sums go (worked out while the main loop runs)
+      const int local = quarter * 32 + lane, rrow = local % rows_per, owner = local / rows_per;
+      const uint32_t dst = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + rrow) * BT) * 4), (uint32_t)owner);
+      const uint32_t owner_bar = DELIVERIES ? map_to_cta(share_bar, (uint32_t)owner) : 0u;
       share_ok = mbar_wait(tmem_full_bar, 0u, args.error, 4);
       tc_fence_after();
       if (DELIVERIES) cluster_wait();      // every partner has set up its barriers (long ago)
-      const int owner = (quarter * 32 + lane) / rows_per;
       if (share_ok) {
         // Feature `local` of the tile belongs to CTA local / rows_per of the cluster; its BT sums go to
         // [this split][local % rows_per][0 .. BT) of that CTA's buffer, the 16-byte pieces of a row
         // rotated by the row number so that the readers (one feature per lane) spread over the banks.
-        const int local = quarter * 32 + lane, rrow = local % rows_per;
-        const uint32_t dst = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + rrow) * BT) * 4),
-                                        (uint32_t)(local / rows_per));
 #pragma unroll
         for (int c = 0; c < BT; c += 16) {
           uint32_t r[16];
@@ -315,7 +315,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // delivered (or given up: the error word says so): one lane arrives for the lanes that share its owner
       if (DELIVERIES) {
         __syncwarp();
-        if ((lane & (min(rows_per, 32) - 1)) == 0) mbar_arrive_cluster(map_to_cta(share_bar, (uint32_t)owner));
+        if ((lane & (min(rows_per, 32) - 1)) == 0) mbar_arrive_cluster(owner_bar);
       }
     } else {
     pdl_wait();        // residual, partials and C belong to kernels before this one until here

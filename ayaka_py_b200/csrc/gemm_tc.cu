@@ -297,23 +297,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int local = quarter * 32 + lane, rrow = local % rows_per, owner = local / rows_per;
       const uint32_t dst = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + rrow) * BT) * 4), (uint32_t)owner);
       const uint32_t owner_bar = DELIVERIES ? map_to_cta(share_bar, (uint32_t)owner) : 0u;
+      // The same for lanes 0 and 16 of this warp, plus this lane's 16 bytes: the staged form below
+      // sends whole rows, 128 / BT of them per instruction, none of which straddles row 16.
+      [[maybe_unused]] uint32_t dst_half[2] = {0u, 0u};
+      if constexpr (BT > 16) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int first = quarter * 32 + 16 * h;
+          dst_half[h] = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + first % rows_per) * BT) * 4),
+                                   (uint32_t)(first / rows_per)) + 16u * (uint32_t)lane;
+        }
+      }
+      if (DELIVERIES) cluster_wait();      // every partner has set up its barriers (long ago; the main loop still runs)
       share_ok = mbar_wait(tmem_full_bar, 0u, args.error, 4);
       tc_fence_after();
-      if (DELIVERIES) cluster_wait();      // every partner has set up its barriers (long ago)
       if (share_ok) {
         // Feature `local` of the tile belongs to CTA local / rows_per of the cluster; its BT sums go to
         // [this split][local % rows_per][0 .. BT) of that CTA's buffer, the 16-byte pieces of a row
         // rotated by the row number so that the readers (one feature per lane) spread over the banks.
-#pragma unroll
-        for (int c = 0; c < BT; c += 16) {
+        if constexpr (BT == 16) {
           uint32_t r[16];
-          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16), r);
           tmem_ld_wait();
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const int piece = ((c >> 2) + q) ^ (rrow & (BT / 4 - 1));
+            const int piece = q ^ (rrow & (BT / 4 - 1));
             st_cluster_v4(dst + 16u * piece, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          }
+        } else {
+          // One lane holds one row: sent as it is, an instruction would touch 32 rows, 16 bytes of each,
+          // and the 64-row product spent 1.8 us sending.  So the warp first lays its 32 rows down in
+          // this CTA's shared memory as they shall lie in the owner's (the main loop's stages are
+          // free: every MMA is done), then copies them 512 contiguous bytes per instruction.
+          const uint32_t stage = tiles + (uint32_t)(quarter * 32 * BT * 4);
+          const uint32_t my_stage = stage + (uint32_t)(lane * BT * 4);
+#pragma unroll
+          for (int c = 0; c < BT; c += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int piece = ((c >> 2) + q) ^ (lane & (BT / 4 - 1));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_stage + 16u * piece), "r"(r[4 * q]),
+                           "r"(r[4 * q + 1]), "r"(r[4 * q + 2]), "r"(r[4 * q + 3]) : "memory");
+            }
+          }
+          __syncwarp();
+          constexpr int ROWS_PER_COPY = 128 / BT;
+#pragma unroll
+          for (int j = 0; j < BT / 4; ++j) {
+            float a, b, c, d;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
+                         : "r"(stage + (uint32_t)(j * 512 + lane * 16)) : "memory");
+            const int row = j * ROWS_PER_COPY;
+            st_cluster_v4(dst_half[row / 16] + (uint32_t)((row % 16) * BT * 4), a, b, c, d);
           }
         }
       }

@@ -255,7 +255,6 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   if (window > 0) k_lo = max(k_lo, pos - window + 1);
   const bool empty = k_lo >= k_hi;               // the same for the whole CTA
   if (empty) return;                             // the merge knows from the position which partitions exist
-  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_dyn[];
   const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(smem_dyn);
   const uint32_t vs_base = ks_base + PART * ROW_BYTES;
@@ -268,46 +267,64 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
 #pragma unroll
   for (int j = 0; j < NT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
 
+  // copies: lane covers piece (lane % PPR) of rows (lane / PPR) + i * (32 / PPR)   [PPR <= 32].
+  // Keys and values lie at the same offsets of their caches: the offsets are worked out once
+  // (32-bit, in elements; the host has checked that a cache has fewer than 2^32).
+  constexpr int RPI = 32 / PPR;                  // rows per instruction
+  constexpr int COPIES = 32 / RPI;
+  const int my_piece = lane % PPR, my_row0 = lane / PPR;
+  const uint32_t lane_off = (uint32_t)(kvh * DH) + (uint32_t)my_piece * 8u;
+  int fresh_i = -1;                              // the copy that brings the key at the query's position, if it is this lane's
+  uint32_t fresh_off = 0u;
   if (warp_has_keys) {
-    const size_t row_elems = (size_t)Hkv * DH;
-    const size_t head_off = (size_t)kvh * DH;
-    // copies: lane covers piece (lane % PPR) of rows (lane / PPR) + i * (32 / PPR)   [PPR <= 32].
-    // Keys and values lie at the same offsets of their caches: the offsets are worked out once
-    // (32-bit, in elements; the host has checked that a cache has fewer than 2^32).
-    constexpr int RPI = 32 / PPR;                // rows per instruction
-    constexpr int COPIES = 32 / RPI;
-    const int my_piece = lane % PPR, my_row0 = lane / PPR;
-    const uint32_t lane_off = (uint32_t)head_off + (uint32_t)my_piece * 8u;
+    // The keys before the query's position were written by earlier steps: their copies start now,
+    // while the kernels before this one (the product that makes q, k and v) may still be running.
+    const uint32_t row_elems = (uint32_t)(Hkv * DH);
     uint32_t off[COPIES];
     uint32_t ok_bits = 0u;
-    int fresh_i = -1;                            // the copy that brings the step's own key, if it is this lane's
 #pragma unroll
     for (int i = 0; i < COPIES; ++i) {
       const int row = my_row0 + i * RPI;         // within the warp's 32 keys
       const int key = wk0 + row;
       const int page = __shfl_sync(0xffffffffu, my_page, (key >> page_shift) - first_logical);
       const bool ok = key >= w_lo && key < w_hi && page > 0;
-      off[i] = ok ? (((uint32_t)page << page_shift) + (uint32_t)(key & (page_size - 1))) * (uint32_t)row_elems + lane_off : 0u;
-      ok_bits |= (ok ? 1u : 0u) << i;
-      if (knew != nullptr && key == pos && ok) fresh_i = i;
+      off[i] = ok ? (((uint32_t)page << page_shift) + (uint32_t)(key & (page_size - 1))) * row_elems + lane_off : 0u;
+      if (key == pos && ok) { fresh_i = i; fresh_off = off[i]; }
+      else ok_bits |= (ok ? 1u : 0u) << i;       // the fresh row's place stays empty until after the wait
     }
 #pragma unroll
     for (int mat = 0; mat < 2; ++mat) {
-      __nv_bfloat16* cache = mat == 0 ? kcache : vcache;
+      const __nv_bfloat16* cache = mat == 0 ? kcache : vcache;
       const uint32_t base = (mat == 0 ? ks_base : vs_base) + (uint32_t)(warp * 32 + my_row0) * ROW_BYTES;
 #pragma unroll
       for (int i = 0; i < COPIES; ++i) {
         const int row = my_row0 + i * RPI;
-        const __nv_bfloat16* src = cache + off[i];
-        if (i == fresh_i) {                      // the step's own key: not in the cache yet
+        if (i != fresh_i)
+          cp_async16_zfill(base + (uint32_t)(i * RPI) * ROW_BYTES + swizzled_piece<PPR>(row, my_piece) * 16, cache + off[i],
+                           (ok_bits >> i) & 1u);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  pdl_wait();
+  if (warp_has_keys) {
+    if (fresh_i >= 0) {
+      // the key and value at the query's position: made by the kernels just before this one
+      const int row = my_row0 + fresh_i * RPI;
+      const uint32_t place = (uint32_t)(warp * 32 + row) * ROW_BYTES + swizzled_piece<PPR>(row, my_piece) * 16;
+#pragma unroll
+      for (int mat = 0; mat < 2; ++mat) {
+        __nv_bfloat16* cache = mat == 0 ? kcache : vcache;
+        const __nv_bfloat16* src = cache + fresh_off;
+        if (knew != nullptr) {                   // not in the cache yet
           src = (mat == 0 ? knew : vnew) + (size_t)r * new_stride + lane_off;
           if (chunk == 0)                        // one CTA per key/value head files it
-            *reinterpret_cast<uint4*>(cache + off[i]) = *reinterpret_cast<const uint4*>(src);
+            *reinterpret_cast<uint4*>(cache + fresh_off) = *reinterpret_cast<const uint4*>(src);
         }
-        cp_async16_zfill(base + (uint32_t)(i * RPI) * ROW_BYTES + swizzled_piece<PPR>(row, my_piece) * 16, src, (ok_bits >> i) & 1u);
+        cp_async16_zfill((mat == 0 ? ks_base : vs_base) + place, src, true);
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     // the query rows as A operands (rows beyond the group stay zero)
     uint32_t qa[KS][2];
     {
@@ -319,7 +336,7 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
         qa[ks][1] = row_ok ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
       }
     }
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
     // scores: 4 tiles of 8 keys
     float sc[4][4];
@@ -357,8 +374,6 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
     }
     l_w += __shfl_xor_sync(0xffffffffu, l_w, 1);
     l_w += __shfl_xor_sync(0xffffffffu, l_w, 2);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncwarp();
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
       const int row = s * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);

@@ -421,6 +421,13 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
 // attention and the next product of a decode step, makes one trip to L2 instead of three.
 // Which partitions hold keys follows from the request's position and the window, as in the
 // kernels that fill them; the others' scratch is never read (nobody wrote it).
+// exp() of the merge: the bfloat16 path takes ex2.approx (2 instructions; the kernel runs its code
+// once, so every instruction counts), the 32-bit path the full-precision function.
+template <typename T> __device__ __forceinline__ float merge_exp(float x) {
+  if constexpr (sizeof(T) == 2) return fast_exp2(x * 1.4426950408889634f);
+  else return expf(x);
+}
+
 template <typename T>
 __global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict__ scratch, int H, int Dh, int parts,
                                     const int* __restrict__ req_pos0, int window) {
@@ -448,12 +455,12 @@ __global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict
 #pragma unroll
       for (int i = 0; i < 8; ++i) m_new = fmaxf(m_new, ms[i]);
       if (m_new > -INFINITY) {
-        const float f = expf(m - m_new);           // exp(-inf) = 0 before the first live partition
+        const float f = merge_exp<T>(m - m_new);   // exp(-inf) = 0 before the first live partition
         acc *= f; l *= f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           if (ms[i] > -INFINITY) {
-            const float w = expf(ms[i] - m_new);
+            const float w = merge_exp<T>(ms[i] - m_new);
             acc = fmaf(vs[i], w, acc);
             l = fmaf(ls[i], w, l);
           }

@@ -17,7 +17,7 @@
 // swizzle); a ring of stages connects producer and MMA through mbarriers.
 //
 // Split-K: for skinny products (decode) gridDim.z CTAs share one output tile.
-// Up to 64 rows with 2, 4 or 8 splits they form a thread-block cluster and
+// Up to 64 rows with 2, 4, 8 or 16 splits they form a thread-block cluster and
 // exchange their 32-bit partial sums through distributed shared memory (see
 // CLUSTER below); otherwise each writes its partial tile to scratch and the last
 // to arrive sums the partials.  Either way the sum runs in split order, so the
@@ -120,7 +120,7 @@ __device__ __forceinline__ void store_chunk_pre(const EpilogueArgs& a, int tok0,
   }
 }
 
-// Split-K inside a thread-block cluster (up to 64 rows, 2, 4 or 8 splits): the CTAs that share an
+// Split-K inside a thread-block cluster (up to 64 rows, 2, 4, 8 or 16 splits): the CTAs that share an
 // output tile are one cluster along z.  Each owns 128 / splits of the tile's out features: every
 // epilogue thread sends its partial sums straight into the owner's shared memory
 // (st.shared::cluster); an owner that knows they are in adds the `splits` partials in split order
@@ -297,15 +297,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int local = quarter * 32 + lane, rrow = local % rows_per, owner = local / rows_per;
       const uint32_t dst = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + rrow) * BT) * 4), (uint32_t)owner);
       const uint32_t owner_bar = DELIVERIES ? map_to_cta(share_bar, (uint32_t)owner) : 0u;
-      // The same for lanes 0 and 16 of this warp, plus this lane's 16 bytes: the staged form below
-      // sends whole rows, 128 / BT of them per instruction, none of which straddles row 16.
-      [[maybe_unused]] uint32_t dst_half[2] = {0u, 0u};
+      // The same for lanes 0, 8, 16 and 24 of this warp, plus this lane's 16 bytes: the staged form
+      // below sends whole rows, 128 / BT of them per instruction, none of which straddles a group of 8
+      // (a share of the tile is at least 8 features).
+      [[maybe_unused]] uint32_t dst_group[4] = {0u, 0u, 0u, 0u};
       if constexpr (BT > 16) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int first = quarter * 32 + 16 * h;
-          dst_half[h] = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + first % rows_per) * BT) * 4),
-                                   (uint32_t)(first / rows_per)) + 16u * (uint32_t)lane;
+        for (int h = 0; h < 4; ++h) {
+          const int first = quarter * 32 + 8 * h;
+          dst_group[h] = map_to_cta(red + (uint32_t)((((int)blockIdx.z * rows_per + first % rows_per) * BT) * 4),
+                                    (uint32_t)(first / rows_per)) + 16u * (uint32_t)lane;
         }
       }
       if (DELIVERIES) cluster_wait();      // every partner has set up its barriers (long ago; the main loop still runs)
@@ -339,7 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tmem_ld_wait();
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const int piece = ((c >> 2) + q) ^ (lane & (BT / 4 - 1));
+              const int piece = ((c >> 2) + q) ^ (rrow & (BT / 4 - 1));     // as the owner's readers expect it
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_stage + 16u * piece), "r"(r[4 * q]),
                            "r"(r[4 * q + 1]), "r"(r[4 * q + 2]), "r"(r[4 * q + 3]) : "memory");
             }
@@ -352,7 +353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
                          : "r"(stage + (uint32_t)(j * 512 + lane * 16)) : "memory");
             const int row = j * ROWS_PER_COPY;
-            st_cluster_v4(dst_half[row / 16] + (uint32_t)((row % 16) * BT * 4), a, b, c, d);
+            st_cluster_v4(dst_group[row / 8] + (uint32_t)((row % 8) * BT * 4), a, b, c, d);
           }
         }
       }
@@ -506,7 +507,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           }
         };
         const int splits = gridDim.z;
-        if (splits == 8) finish(std::integral_constant<int, 8>());
+        if (splits == 16) finish(std::integral_constant<int, 16>());
+        else if (splits == 8) finish(std::integral_constant<int, 8>());
         else if (splits == 4) finish(std::integral_constant<int, 4>());
         else finish(std::integral_constant<int, 2>());
       }
@@ -596,6 +598,9 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueA
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
     if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: shared memory %zu: %s", SMEM, cudaGetErrorString(err));
+    // clusters of 16 are beyond the portable size of 8
+    err = cudaFuncSetAttribute(gemm_tc_kernel<BT, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: clusters of 16: %s", cudaGetErrorString(err));
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -639,7 +644,7 @@ AYK_EXPORT long long ayk_gemm_tc_scratch_floats(int M, int N, int splits) {
 // splits > 1 needs `partials` (ayk_gemm_tc_scratch_floats) and `counters` (one
 // zeroed unsigned per output tile; the kernel leaves them zero), unless cluster != 0: then the
 // splits of a tile are one thread-block cluster and exchange their sums through shared memory
-// (up to 64 rows; 2, 4 or 8 splits; at least one K block each), and no scratch is touched.
+// (up to 64 rows; 2, 4, 8 or 16 splits; at least one K block each), and no scratch is touched.
 AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* bias, const float* residual,
                            int M, int N, int K, int act, int out_dtype, int splits, float* partials,
                            unsigned int* counters, int weight_is_static, int cluster, cudaStream_t stream) {
@@ -651,8 +656,8 @@ AYK_EXPORT int ayk_gemm_tc(void* C, const void* X, const void* W, const float* b
   if (splits < 1) splits = 1;
   if (splits > total_kb) splits = total_kb;
   if (cluster) {
-    AYK_REQUIRE(M <= 64 && (splits == 2 || splits == 4 || splits == 8) && total_kb >= splits,
-                "ayk_gemm_tc: the cluster form takes up to 64 rows and 2, 4 or 8 splits of at least one K block (rows %d, splits %d, K blocks %d)",
+    AYK_REQUIRE(M <= 64 && (splits == 2 || splits == 4 || splits == 8 || splits == 16) && total_kb >= splits,
+                "ayk_gemm_tc: the cluster form takes up to 64 rows and 2, 4, 8 or 16 splits of at least one K block (rows %d, splits %d, K blocks %d)",
                 M, splits, total_kb);
   }
   int kb_per_split = (total_kb + splits - 1) / splits;

@@ -252,12 +252,17 @@ CLUSTER_ROWS = 64        # up to this many rows the splits of a tile exchange th
 def tc_splits(M: int, N: int, K: int) -> int:
     """Split-K factor of the tensor-core product: skinny products (few output
     tiles) are cut along K so that about one CTA per SM streams the weight.
-    Up to 64 rows the factor is 1, 2, 4 or 8: those splits form a cluster."""
+    Up to 64 rows the factor is 1, 2, 4, 8 or 16: those splits form a cluster.  16 (beyond the
+    portable cluster size) only where each split still has four K blocks: a product of 13
+    tiles and K = 6400 streamed at 3.6 TB/s from 104 CTAs, which do not keep enough
+    bytes in flight, and at the copy rate from 200."""
     bt = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
     tiles = -(-N // 128) * -(-M // bt)
     blocks = -(-K // 64)
     if tiles >= SM_COUNT or blocks < 4 or M > CLUSTER_ROWS:
         return 1          # more rows: partial sums through global scratch cost more than the split saves (measured)
+    if tiles * 16 <= SM_COUNT * 3 // 2 and blocks >= 64:
+        return 16
     for p in (8, 4, 2):
         if tiles * p <= SM_COUNT * 14 // 10 and blocks >= p:
             return p
@@ -272,7 +277,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     ``splits``: CTAs along K per output tile (default: chosen by shape).  ``cluster``:
     the splits exchange their sums through shared memory of a thread-block cluster
     instead of scratch in global memory (default where it applies: up to 64 rows,
-    2, 4 or 8 splits)."""
+    2, 4, 8 or 16 splits)."""
     lib = _ready()
     M, K = a.shape
     N = w.shape[0]
@@ -289,11 +294,11 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         raise KernelError("residual must have the output's shape")
     if splits is None:
         splits = tc_splits(M, N, K)
-    can_cluster = M <= CLUSTER_ROWS and splits in (2, 4, 8) and -(-K // 64) >= splits
+    can_cluster = M <= CLUSTER_ROWS and splits in (2, 4, 8, 16) and -(-K // 64) >= splits
     if cluster is None:
         cluster = can_cluster
     elif cluster and not can_cluster:
-        raise KernelError(f"gemm_tc: the cluster form takes up to {CLUSTER_ROWS} rows and 2, 4 or 8 splits (rows {M}, splits {splits})")
+        raise KernelError(f"gemm_tc: the cluster form takes up to {CLUSTER_ROWS} rows and 2, 4, 8 or 16 splits (rows {M}, splits {splits})")
     partials = counters = None
     if splits > 1 and not cluster:
         tiles = -(-N // 128) * -(-M // 16)

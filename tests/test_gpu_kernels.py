@@ -231,6 +231,7 @@ TC_CASES = [
     (3, 130, 512, 4), (40, 300, 1000, 7), (8, 64, 64, 3),
     (16, 300, 1600, 8), (1, 1600, 6400, 2), (5, 257, 520, 8), (9, 50257 // 16, 128, 2),      # splits as one cluster
     (64, 1600, 6400, 8), (33, 4800, 1600, 4), (17, 200, 328, 2), (32, 130, 256, 4), (50, 6400, 1600, 2),
+    (8, 1600, 6400, 16), (1, 300, 1104, 16), (24, 257, 2048, 16), (64, 1000, 4104, 16),         # clusters of 16
 ]
 
 

@@ -132,7 +132,7 @@ __device__ __forceinline__ void store_chunk_pre(const EpilogueArgs& a, int tok0,
 // through L2; measured against the scratch form inside the decode graph this takes the product
 // from about 10 to 7.5 us.
 template <int BT, bool CLUSTER = false>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, (BT <= 16 && !CLUSTER) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const EpilogueArgs args) {
   constexpr int STAGES = CLUSTER ? cluster_stages_for(BT) : stages_for(BT);

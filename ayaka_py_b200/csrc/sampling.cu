@@ -56,17 +56,18 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
 
 __device__ MaxIdx block_argmax(const float* row, int V, MaxIdx* red) {
   MaxIdx best = {-INFINITY, 0x7fffffff};
-  // Eight independent loads in flight per thread; compared in ascending index
-  // order, so that the first maximum stays.
-  for (int base = threadIdx.x; base < V; base += blockDim.x * 8) {
-    float v[8];
+  // Sixteen independent loads in flight per thread (a row of 50,257 is six trips to L2 instead of
+  // twelve); compared in ascending index order, so that the first maximum stays.
+  constexpr int FLY = 16;
+  for (int base = threadIdx.x; base < V; base += blockDim.x * FLY) {
+    float v[FLY];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < FLY; ++u) {
       const int i = base + u * blockDim.x;
       v[u] = i < V ? row[i] : -INFINITY;
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < FLY; ++u) {
       if (v[u] > best.v) { best.v = v[u]; best.i = base + u * blockDim.x; }
     }
   }

@@ -279,6 +279,9 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   if (warp_has_keys) {
     // The keys before the query's position were written by earlier steps: their copies start now,
     // while the kernels before this one (the product that makes q, k and v) may still be running.
+    // (Between two steps lies the upload of the step's inputs or a graph launch, both full
+    // dependencies: no kernel of an earlier step can still be running here.  A caller that chains
+    // steps by programmatic launches alone must not use this kernel.)
     const uint32_t row_elems = (uint32_t)(Hkv * DH);
     uint32_t off[COPIES];
     uint32_t ok_bits = 0u;

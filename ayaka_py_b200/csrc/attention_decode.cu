@@ -222,7 +222,7 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
                   __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
                   const int* __restrict__ table, int table_stride, const int* __restrict__ req_pos0,
                   int H, int Hkv, int group, int page_shift, float scale_log2, int window, int parts, int chunks, int rows,
-                  const __nv_bfloat16* __restrict__ knew, const __nv_bfloat16* __restrict__ vnew, int new_stride) {
+                  const __nv_bfloat16* __restrict__ knew, const __nv_bfloat16* __restrict__ vnew, int new_stride, int settled) {
   pdl_trigger();
   static_assert(WARPS * 32 == PART, "each warp owns 32 keys of the partition");
   constexpr int KS = DH / 16;                    // k steps of the first product
@@ -276,12 +276,13 @@ decode_mma_kernel(float* __restrict__ scratch, const __nv_bfloat16* __restrict__
   const uint32_t lane_off = (uint32_t)(kvh * DH) + (uint32_t)my_piece * 8u;
   int fresh_i = -1;                              // the copy that brings the key at the query's position, if it is this lane's
   uint32_t fresh_off = 0u;
+  // `settled`: the caller vouches that whatever wrote the keys before the query's position is
+  // complete (the engine: between two steps lies the upload of the step's inputs or a graph
+  // launch, both full dependencies).  Their copies then start now, while the kernels before this
+  // one (the product that makes q, k and v) may still be running.  Without that word the
+  // kernel waits first: the call before this one may be the one that wrote them.
+  if (!settled) pdl_wait();
   if (warp_has_keys) {
-    // The keys before the query's position were written by earlier steps: their copies start now,
-    // while the kernels before this one (the product that makes q, k and v) may still be running.
-    // (Between two steps lies the upload of the step's inputs or a graph launch, both full
-    // dependencies: no kernel of an earlier step can still be running here.  A caller that chains
-    // steps by programmatic launches alone must not use this kernel.)
     const uint32_t row_elems = (uint32_t)(Hkv * DH);
     uint32_t off[COPIES];
     uint32_t ok_bits = 0u;
@@ -489,12 +490,15 @@ extern "C" int ayk_kv_append(void* kcache, void* vcache, const void* k, const vo
 // scratch holds R * H * parts * (Dh + 2) floats.  knew, vnew (or null): this step's key and
 // value rows [R, new_stride], not yet in the cache: they are stored at (request r, position
 // req_pos0[r]) on the way (row_req[r] must be r: one row per request, in order).  cache_pages: pages of
-// a cache tensor (the tensor-core kernel addresses a cache with 32-bit element offsets).
+// a cache tensor (the tensor-core kernel addresses a cache with 32-bit element offsets).  settled != 0:
+// every earlier write of the cache rows before the requests' positions is complete (no kernel that
+// wrote them can still be running): the tensor-core kernel then copies them before it waits for the
+// kernels launched before it.
 AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void* kcache, void* vcache,
                                     const int* table, int table_stride, const int* req_pos0, int R, int H, int Hkv,
                                     int Dh, int page_size, float scale, int window, int parts, float* scratch,
                                     const void* knew, const void* vnew, int new_stride, const int* row_req,
-                                    long long cache_pages, int dtype, cudaStream_t stream) {
+                                    long long cache_pages, int settled, int dtype, cudaStream_t stream) {
   if (R == 0) return 0;
   AYK_REQUIRE(Dh >= 16 && Dh % 16 == 0 && Dh <= MAX_DH, "ayk_attention_decode: head size %d is not a multiple of 16 in [16, %d]", Dh, MAX_DH);
   AYK_REQUIRE(Hkv >= 1 && H % Hkv == 0, "ayk_attention_decode: %d heads cannot share %d key/value heads", H, Hkv);
@@ -528,7 +532,7 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void
   ayk_launch(decode_mma_kernel<D>, dim3(Hkv * chunks, R, parts), dim3(WARPS * 32), smem, stream, scratch,                      \
              (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, table, table_stride,    \
              req_pos0, H, Hkv, group, page_shift, scale_log2, window, parts, chunks, rows, (const __nv_bfloat16*)knew,  \
-             (const __nv_bfloat16*)vnew, new_stride)
+             (const __nv_bfloat16*)vnew, new_stride, settled)
     if (Dh == 32) AYK_DECODE_MMA(32); else if (Dh == 64) AYK_DECODE_MMA(64); else AYK_DECODE_MMA(128);
 #undef AYK_DECODE_MMA
     ayk_launch(decode_merge_kernel<__nv_bfloat16>, dim3(R, H), dim3(Dh <= 32 ? 32 : (Dh <= 64 ? 64 : 128)), 0, stream,

@@ -53,6 +53,10 @@ class StepContext:
     host: dict = field(default_factory=dict)   # the same arrays as NumPy, for host-side decisions
     max_q_len: int = 1
     max_kv_len: int = 1
+    # Cache rows that earlier steps wrote are complete when this step's kernels start: the upload
+    # of the step's inputs (or a graph launch) lies between.  Kernels may read them ahead of the
+    # kernels launched just before them.
+    earlier_rows_settled: bool = False
 
 
 class StepRunner:
@@ -186,7 +190,7 @@ class StepRunner:
             req_slot=self._field(d, "req_slot", R), req_kv_len=self._field(d, "req_kv_len", R),
             tables=tables, cache=self.cache, dtype=self.model.dtype,
             host={"q_start": q_start, "pos0": starts, "slots": slots, "kv_len": ends, "counts": counts},
-            max_q_len=int(counts.max()), max_kv_len=int(ends.max()))
+            max_q_len=int(counts.max()), max_kv_len=int(ends.max()), earlier_rows_settled=True)
 
     def run(self, entries: Sequence[StepEntry], tokens_from: torch.Tensor | None = None) -> torch.Tensor:
         """Logits [S, V] float32 on the device.  The caller has reserved the

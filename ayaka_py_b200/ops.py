@@ -382,12 +382,15 @@ def _decode_buffer(device, floats: int) -> torch.Tensor:
 def attention_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, table: torch.Tensor,
                      req_pos0: torch.Tensor, num_heads: int, scale: float, window: int | None,
                      max_context: int, out: torch.Tensor | None = None,
-                     append: tuple | None = None) -> torch.Tensor:
+                     append: tuple | None = None, settled: bool = False) -> torch.Tensor:
     """One query row per request over its pages, split along the context and
     merged.  ``max_context``: the longest context the engine allows (fixes the grid).
     ``append`` = (k, v, row_req): this step's key and value rows, not yet in the
     cache; they are stored at each request's position on the way (inside the
-    attention kernel where it can, else by the append kernel first)."""
+    attention kernel where it can, else by the append kernel first).  ``settled``:
+    the cache rows before the requests' positions were written by work that is
+    complete (an earlier step); the kernel may then read them while the kernels
+    launched just before it still run."""
     lib = _ready()
     pages, P, Hkv, Dh = kcache.shape
     R = q.shape[0]
@@ -414,7 +417,8 @@ def attention_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor
                                      ctypes.c_int(window or 0), ctypes.c_int(parts), _ptr(scratch),
                                      _ptr(k_new), _ptr(v_new), ctypes.c_int(new_stride),
                                      _ptr(_i32(row_req, "row_req") if row_req is not None else None),
-                                     ctypes.c_longlong(pages), ctypes.c_int(_tag(q.dtype)), _stream()))
+                                     ctypes.c_longlong(pages), ctypes.c_int(1 if settled else 0),
+                                     ctypes.c_int(_tag(q.dtype)), _stream()))
     global launches
     launches += 1            # the call launches two kernels (partitions, merge)
     return out
@@ -469,7 +473,8 @@ def attention(q, kcache, vcache, table, ctx, num_heads: int, scale: float,
     if ctx.max_q_len == 1:
         return attention_decode(q, kcache, vcache, table, ctx.req_pos0, num_heads, scale, window,
                                 ctx.cache.max_len,
-                                append=(append[0], append[1], ctx.row_req) if append is not None else None)
+                                append=(append[0], append[1], ctx.row_req) if append is not None else None,
+                                settled=getattr(ctx, "earlier_rows_settled", False))
     if append is not None:
         kv_append(kcache, vcache, append[0], append[1], ctx.row_req, ctx.positions, table)
     if attention_tc_takes(q, kcache):

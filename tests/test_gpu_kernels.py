@@ -315,6 +315,15 @@ def test_decode_attention_split_and_merge(dtype, case, max_context):
                                  append=(x["k"], x["v"], x["row_req"]))
     assert torch.equal(fused, out)
     assert torch.equal(kc2, x["kc"]) and torch.equal(vc2, x["vc"])
+    # the same when the caller vouches that the rows of earlier steps are complete (they are: nothing
+    # that wrote them is still running), so that their copies may start before the kernel's wait
+    torch.cuda.synchronize()
+    kc3, vc3 = x["kc"].clone(), x["vc"].clone()
+    early = ops.attention_decode(x["q"], kc3, vc3, x["table"], x["pos0"], H, scale, window, max_context,
+                                 append=(x["k"], x["v"], x["row_req"]), settled=True)
+    assert torch.equal(early, out)
+    assert torch.equal(ops.attention_decode(x["q"], kc3, vc3, x["table"], x["pos0"], H, scale, window, max_context,
+                                            settled=True), out)
 
 
 @pytest.mark.parametrize("kpos", [0, 127, 128, 383, 384])

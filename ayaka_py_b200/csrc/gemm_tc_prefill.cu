@@ -48,21 +48,40 @@ struct PrefillArgs {
   int box_m;                 // rows of X that one TMA copy brings (128, fewer when M is small)
   int mode;                  // which compiled form of the epilogue (see epilogue_chunk)
   int vec_ok;                // N % 8 == 0 and bias, residual, C 16-byte aligned: whole chunks move in 16-byte pieces
+  // mode 4: the columns from kv_col0 on are keys (kv_width of them) and then values of the rows' tokens; they
+  // are also stored into the paged cache, at the place that (request, position) has in the block table
+  __nv_bfloat16* kcache;
+  __nv_bfloat16* vcache;
+  const int* kv_row_req;     // [M] the row's request within the step
+  const int* kv_pos;         // [M] the row's position
+  const int* kv_table;       // [requests, kv_table_stride] pages
+  int kv_table_stride, kv_page_size, kv_col0, kv_width;
 };
+
+// Where the keys of row `row` go: element offset of the row's place in a cache tensor, or -1 (a row
+// beyond the matrix, or one that maps to the padding page).
+__device__ __forceinline__ long long cache_place(const PrefillArgs& a, int row) {
+  if (a.mode != 4 || row >= a.M) return -1;
+  const int p = a.kv_pos[row];
+  const int page = a.kv_table[(size_t)a.kv_row_req[row] * a.kv_table_stride + p / a.kv_page_size];
+  return page > 0 ? ((long long)page * a.kv_page_size + p % a.kv_page_size) * a.kv_width : -1;
+}
 
 // One row, W consecutive columns (W = 16 or 32) starting at column n.  The epilogue competes
 // with nothing for memory but it does for issue slots and registers, and with 25 K blocks per
 // tile it is as long as the main loop.  So whole chunks inside the matrix take 16-byte loads of
 // bias and residual and no test per element, and the three combinations that a transformer block
 // uses are compiled on their own (MODE): 0 = bfloat16 out, no activation, no residual; 1 = float32
-// out with residual; 2 = bfloat16 out with tanh-GELU; 3 = anything, decided at run time.
+// out with residual; 2 = bfloat16 out with tanh-GELU; 3 = anything, decided at run time; 4 = as 0, and
+// the key and value columns go into the paged cache as well (`place`: where this row's do, or -1).
 template <int W, int MODE>
-__device__ __forceinline__ void epilogue_chunk(const PrefillArgs& a, uint32_t taddr, int row, int n, bool row_ok) {
+__device__ __forceinline__ void epilogue_chunk(const PrefillArgs& a, uint32_t taddr, int row, int n, bool row_ok,
+                                               long long place) {
   constexpr int ACT = MODE == 2 ? AYK_ACT_GELU_TANH : (MODE == 3 ? -1 : AYK_ACT_NONE);
   uint32_t r[W];
   if (W == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
   const size_t idx = (size_t)row * a.N + n;
-  const bool out_bf16 = MODE == 3 ? a.out_bf16 != 0 : MODE != 1;
+  const bool out_bf16 = MODE == 3 ? a.out_bf16 != 0 : MODE != 1;       // modes 0, 2 and 4 store bfloat16
   if (a.vec_ok && n + W <= a.N) {
     const bool with_res = (MODE == 1 || MODE == 3) && a.residual != nullptr && row_ok;
     float4 res[(MODE == 1 || MODE == 3) ? W / 4 : 1];
@@ -100,6 +119,13 @@ __device__ __forceinline__ void epilogue_chunk(const PrefillArgs& a, uint32_t ta
           w[u >> 1] = *reinterpret_cast<uint32_t*>(&p);
         }
         *reinterpret_cast<uint4*>((__nv_bfloat16*)a.C + idx + j) = make_uint4(w[0], w[1], w[2], w[3]);
+        if (MODE == 4) {
+          const int off = n + j - a.kv_col0;         // kv_col0 and kv_width are multiples of 8: a piece is all key or all value
+          if (place >= 0 && off >= 0) {
+            __nv_bfloat16* dst = off < a.kv_width ? a.kcache + place + off : a.vcache + place + (off - a.kv_width);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
       } else {
         float* dst = (float*)a.C + idx + j;
         *reinterpret_cast<float4*>(dst) = make_float4(y[0], y[1], y[2], y[3]);
@@ -118,22 +144,30 @@ __device__ __forceinline__ void epilogue_chunk(const PrefillArgs& a, uint32_t ta
       const float y = apply_activation_tc<ACT>(__uint_as_float(r[j]) + b, a.act) + res;
       if (a.out_bf16) ((__nv_bfloat16*)a.C)[idx + j] = __float2bfloat16_rn(y);
       else ((float*)a.C)[idx + j] = y;
+      if (MODE == 4) {
+        const int off = n + j - a.kv_col0;
+        if (place >= 0 && off >= 0)
+          (off < a.kv_width ? a.kcache + place + off : a.vcache + place + (off - a.kv_width))[0] = __float2bfloat16_rn(y);
+      }
     }
   }
 }
 
 // `cols` columns of one row, from column n on (cols a multiple of 16)
 template <int MODE>
-__device__ __forceinline__ void epilogue_row(const PrefillArgs& a, uint32_t taddr, int row, int n, int cols, bool row_ok) {
+__device__ __forceinline__ void epilogue_row(const PrefillArgs& a, uint32_t taddr, int row, int n, int cols, bool row_ok,
+                                             long long place) {
   int c = 0;
-  for (; c + 32 <= cols; c += 32) epilogue_chunk<32, MODE>(a, taddr + c, row, n + c, row_ok);
-  if (c < cols) epilogue_chunk<16, MODE>(a, taddr + c, row, n + c, row_ok);
+  for (; c + 32 <= cols; c += 32) epilogue_chunk<32, MODE>(a, taddr + c, row, n + c, row_ok, place);
+  if (c < cols) epilogue_chunk<16, MODE>(a, taddr + c, row, n + c, row_ok, place);
 }
-__device__ __forceinline__ void epilogue_row_any(const PrefillArgs& a, uint32_t taddr, int row, int n, int cols, bool row_ok) {
-  if (a.mode == 0) epilogue_row<0>(a, taddr, row, n, cols, row_ok);
-  else if (a.mode == 1) epilogue_row<1>(a, taddr, row, n, cols, row_ok);
-  else if (a.mode == 2) epilogue_row<2>(a, taddr, row, n, cols, row_ok);
-  else epilogue_row<3>(a, taddr, row, n, cols, row_ok);
+__device__ __forceinline__ void epilogue_row_any(const PrefillArgs& a, uint32_t taddr, int row, int n, int cols, bool row_ok,
+                                                 long long place) {
+  if (a.mode == 0) epilogue_row<0>(a, taddr, row, n, cols, row_ok, place);
+  else if (a.mode == 1) epilogue_row<1>(a, taddr, row, n, cols, row_ok, place);
+  else if (a.mode == 2) epilogue_row<2>(a, taddr, row, n, cols, row_ok, place);
+  else if (a.mode == 4) epilogue_row<4>(a, taddr, row, n, cols, row_ok, place);
+  else epilogue_row<3>(a, taddr, row, n, cols, row_ok, place);
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -273,6 +307,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       const int b = t & 1;
       const int tile = blockIdx.x + t * gridDim.x;
       const int m0 = (tile / args.n_tiles) * BM, n0 = (tile % args.n_tiles) * BN;
+      const long long place = cache_place(args, m0 + quarter * 32 + lane);   // three dependent loads: under the main loop
       // One lane per warp watches the barrier; 256 threads polling it slow the producer and MMA warps down.
       if (lane == 0) ok = mbar_wait(tmem_full(b), (uint32_t)(t >> 1) & 1u, args.error, 25);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -281,7 +316,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < args.M;
       const uint32_t taddr = tmem_base + (uint32_t)b * 256u + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
-      epilogue_row_any(args, taddr, row, n0 + half * half_cols, half_cols, row_ok);
+      epilogue_row_any(args, taddr, row, n0 + half * half_cols, half_cols, row_ok, place);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty(b));
@@ -459,6 +494,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       const int b = t & 1;
       const int tile = pair + t * pairs;
       const int m0 = (tile / args.n_tiles) * PAIR_ROWS + (int)rank * BM, n0 = (tile % args.n_tiles) * BN;
+      const long long place = cache_place(args, m0 + quarter * 32 + lane);
       if (lane == 0) ok = mbar_wait(tmem_full(b), (uint32_t)(t >> 1) & 1u, args.error, 35);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
@@ -466,7 +502,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < args.M;
       const uint32_t taddr = tmem_base + (uint32_t)b * 256u + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
-      epilogue_row_any(args, taddr, row, n0 + half * half_cols, half_cols, row_ok);
+      epilogue_row_any(args, taddr, row, n0 + half * half_cols, half_cols, row_ok, place);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(empty_at_leader[b]);
@@ -584,9 +620,52 @@ AYK_EXPORT int ayk_gemm_tc_pair_tile(int M, int N, int sms) {
 // pair: 1 = two SMs per 256-row tile, 0 = one SM per 128-row tile, -1 = one SM unless the environment
 // variable AYAKA_B200_GEMM_PAIR=1 asks for pairs from 129 rows on (measured equal on the XL shapes:
 // both forms are bound by the tensor pipe's rate per instruction, not by operand traffic).
+namespace {
+struct CacheTarget {        // where the key and value columns of the product also go (see PrefillArgs, mode 4)
+  void* kcache; void* vcache;
+  const int* row_req; const int* pos; const int* table;
+  int table_stride, page_size, col0, width;
+};
+// 0 when the epilogue that files keys and values applies to this call; its fields then go into `args`.
+int take_cache_target(PrefillArgs& args, const CacheTarget* kv) {
+  if (kv == nullptr) return 0;
+  AYK_REQUIRE(args.mode == 0 && args.vec_ok && args.N == kv->col0 + 2 * kv->width && kv->col0 % 8 == 0 && kv->width % 8 == 0 &&
+              kv->page_size >= 1 && (uintptr_t)kv->kcache % 16 == 0 && (uintptr_t)kv->vcache % 16 == 0,
+              "ayk_gemm_tc_prefill_kv: needs bfloat16 out without activation or residual, and key and value columns in whole "
+              "16-byte pieces after column %d (N %d, width %d)", kv->col0, args.N, kv->width);
+  args.mode = 4;
+  args.kcache = (__nv_bfloat16*)kv->kcache; args.vcache = (__nv_bfloat16*)kv->vcache;
+  args.kv_row_req = kv->row_req; args.kv_pos = kv->pos; args.kv_table = kv->table;
+  args.kv_table_stride = kv->table_stride; args.kv_page_size = kv->page_size; args.kv_col0 = kv->col0; args.kv_width = kv->width;
+  return 0;
+}
+int prefill_product(void* C, const void* X, const void* W, const float* bias, const float* residual,
+                    int M, int N, int K, int act, int out_dtype, int tile_n, int sms, int pair,
+                    const CacheTarget* kv, cudaStream_t stream);
+}  // namespace
+
 AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const float* bias, const float* residual,
                                    int M, int N, int K, int act, int out_dtype, int tile_n, int sms, int pair,
                                    cudaStream_t stream) {
+  return prefill_product(C, X, W, bias, residual, M, N, K, act, out_dtype, tile_n, sms, pair, nullptr, stream);
+}
+
+// The same product for a fused q | k | v projection of prompt rows: the columns from col0 on, `width` keys and then
+// `width` values per row, are stored into the paged caches [pages, page_size, width] as well, row t at the place
+// that table[row_req[t], pos[t] / page_size] and pos[t] % page_size name (the padding page 0 takes nothing): no
+// separate append kernel has to read them back.  bfloat16 out, no activation, no residual.
+AYK_EXPORT int ayk_gemm_tc_prefill_kv(void* C, const void* X, const void* W, const float* bias, int M, int N, int K,
+                                      int tile_n, int sms, int pair, void* kcache, void* vcache, const int* row_req,
+                                      const int* pos, const int* table, int table_stride, int page_size, int col0,
+                                      int width, cudaStream_t stream) {
+  CacheTarget kv{kcache, vcache, row_req, pos, table, table_stride, page_size, col0, width};
+  return prefill_product(C, X, W, bias, nullptr, M, N, K, AYK_ACT_NONE, AYK_DTYPE_BF16, tile_n, sms, pair, &kv, stream);
+}
+
+namespace {
+int prefill_product(void* C, const void* X, const void* W, const float* bias, const float* residual,
+                    int M, int N, int K, int act, int out_dtype, int tile_n, int sms, int pair,
+                    const CacheTarget* kv, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   AYK_REQUIRE(K >= 8 && K % 8 == 0, "ayk_gemm_tc_prefill: K = %d must be a positive multiple of 8", K);
   AYK_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)C % 16 == 0) &&
@@ -624,6 +703,7 @@ AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const 
     args.BN = BN;
     args.vec_ok = (N % 8 == 0) && (bias == nullptr || (uintptr_t)bias % 16 == 0);
     args.mode = epilogue_mode(act, residual != nullptr, args.out_bf16);
+    if (take_cache_target(args, kv) != 0) return -1;
     args.box_m = BM;
     args.m_tiles = (M + PAIR_ROWS - 1) / PAIR_ROWS;
     args.n_tiles = (N + BN - 1) / BN;
@@ -671,6 +751,7 @@ AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const 
   args.BN = BN;
   args.vec_ok = (N % 8 == 0) && (bias == nullptr || (uintptr_t)bias % 16 == 0);
   args.mode = epilogue_mode(act, residual != nullptr, args.out_bf16);
+  if (take_cache_target(args, kv) != 0) return -1;
   args.box_m = box_m;
   args.m_tiles = (M + BM - 1) / BM;
   args.n_tiles = (N + BN - 1) / BN;
@@ -682,3 +763,4 @@ AYK_EXPORT int ayk_gemm_tc_prefill(void* C, const void* X, const void* W, const 
   ayk_launch(gemm_tc_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mx, mw, args);
   return ayk_check_launch("ayk_gemm_tc_prefill");
 }
+}  // namespace

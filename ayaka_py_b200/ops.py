@@ -315,14 +315,34 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
 PREFILL_ROWS = 16        # more rows than this: the kernel with 128-row tiles and no split along K
 
 
+class KVAppend:
+    """Where the key and value columns of a fused q | k | v projection belong in the paged
+    cache: ``linear`` hands this to the product that can file them itself (the many-row
+    tensor-core kernel, in its epilogue) and sets ``done``; the caller appends them with
+    ``kv_append`` otherwise."""
+
+    def __init__(self, kcache: torch.Tensor, vcache: torch.Tensor, row_req: torch.Tensor, positions: torch.Tensor,
+                 table: torch.Tensor, col0: int, width: int):
+        self.kcache, self.vcache, self.row_req, self.positions, self.table = kcache, vcache, row_req, positions, table
+        self.col0, self.width = col0, width
+        self.done = False
+
+    def fits(self, n_out: int, out_dtype) -> bool:
+        pages, P, Hkv, Dh = self.kcache.shape
+        return (out_dtype == torch.bfloat16 and self.kcache.dtype == torch.bfloat16 and self.width == Hkv * Dh
+                and self.col0 % 8 == 0 and self.width % 8 == 0 and n_out == self.col0 + 2 * self.width
+                and self.kcache.is_contiguous() and self.vcache.is_contiguous())
+
+
 def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
                     activation: str = "none", residual: torch.Tensor | None = None,
                     out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
-                    tile_n: int = 0, pair: bool | None = None) -> torch.Tensor:
+                    tile_n: int = 0, pair: bool | None = None, kv: KVAppend | None = None) -> torch.Tensor:
     """act(a[M,K] @ w[N,K]^T + bias) (+ residual) for many rows: persistent tcgen05
     kernel, epilogue of a tile under the main loop of the next.  ``pair``: two SMs
     on a 256-row tile (tcgen05 cta_group::2) or one SM on a 128-row tile (the default;
-    AYAKA_B200_GEMM_PAIR=1 makes pairs the default from 129 rows on)."""
+    AYAKA_B200_GEMM_PAIR=1 makes pairs the default from 129 rows on).  ``kv``: the product is a
+    q | k | v projection whose key and value columns also go into the paged cache."""
     lib = _ready()
     M, K = a.shape
     N = w.shape[0]
@@ -337,6 +357,18 @@ def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None 
             raise KernelError(f"{name} must be contiguous float32")
     if residual is not None and tuple(residual.shape) != (M, N):
         raise KernelError("residual must have the output's shape")
+    if kv is not None:
+        if activation != "none" or residual is not None or not kv.fits(N, out_dtype):
+            raise KernelError("gemm_tc_prefill: keys and values are filed only by a plain bfloat16 q | k | v projection")
+        P = kv.kcache.shape[1]
+        _launch(lib.ayk_gemm_tc_prefill_kv(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), ctypes.c_int(M), ctypes.c_int(N),
+                                           ctypes.c_int(K), ctypes.c_int(tile_n), ctypes.c_int(SM_COUNT),
+                                           ctypes.c_int(-1 if pair is None else int(pair)), _ptr(kv.kcache), _ptr(kv.vcache),
+                                           _ptr(_i32(kv.row_req, "row_req")), _ptr(_i32(kv.positions, "positions")),
+                                           _ptr(_i32(kv.table, "table")), ctypes.c_int(kv.table.stride(0)), ctypes.c_int(P),
+                                           ctypes.c_int(kv.col0), ctypes.c_int(kv.width), _stream()))
+        kv.done = True
+        return out
     _launch(lib.ayk_gemm_tc_prefill(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
                                     ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]),
                                     ctypes.c_int(_tag(out_dtype)), ctypes.c_int(tile_n), ctypes.c_int(SM_COUNT),
@@ -346,10 +378,12 @@ def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            activation: str = "none", residual: torch.Tensor | None = None,
-           out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+           out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
+           kv: KVAppend | None = None) -> torch.Tensor:
     """act(a @ w^T + bias) (+ residual).  float32 operands run on the FP32
     pipes (true 32-bit); bfloat16 operands on the tensor cores (tcgen05) when
-    K is a multiple of 8, else on the FP32 pipes with 32-bit accumulation."""
+    K is a multiple of 8, else on the FP32 pipes with 32-bit accumulation.
+    ``kv``: see KVAppend; ``kv.done`` tells whether the product filed the rows."""
     if a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[0] > 0:
         M, N, K = a.shape[0], w.shape[0], a.shape[1]
         # Up to 64 rows with few output tiles: weights as the MMA's M side, K split over a cluster.
@@ -359,6 +393,9 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         if M <= PREFILL_ROWS or (M <= CLUSTER_ROWS and tc_splits(M, N, K) > 1):
             return gemm_tc(a, w, bias, activation, residual, out_dtype, out)
         if N % 8 == 0 or M > 128:
+            if (kv is not None and N % 8 == 0 and activation == "none" and residual is None
+                    and kv.fits(N, out_dtype or a.dtype) and (bias is None or bias.data_ptr() % 16 == 0)):
+                return gemm_tc_prefill(a, w, bias, activation, residual, out_dtype, out, kv=kv)
             return gemm_tc_prefill(a, w, bias, activation, residual, out_dtype, out)
         return gemm_tc(a, w, bias, activation, residual, out_dtype, out)
     return gemm_simt(a, w, bias, activation, residual, out_dtype, out)

@@ -51,17 +51,24 @@ class Attention(Mixer):
         return KVNeed(self.kv_heads, self.head_dim, self.window)
 
     def forward(self, h, residual, ctx, cache):
-        qkv = ops.linear(h, self.qkv_weight, self.qkv_bias, out_dtype=self.dtype)
+        kcache, vcache = ctx.cache.kv_layer(cache.group, cache.layer)
+        table = ctx.tables[cache.group]
+        rotate = getattr(self.position, "rotate_qk", None)
+        # Rows of prompts whose keys go into the cache as the projection makes them: the product may
+        # file them itself.  (A decode step's are filed by its attention kernel, rotated keys after
+        # the rotation.)
+        filing = None
+        if cache.writes and rotate is None and ctx.max_q_len > 1:
+            filing = ops.KVAppend(kcache, vcache, ctx.row_req, ctx.positions, table, self.q_width, self.kv_width)
+        qkv = ops.linear(h, self.qkv_weight, self.qkv_bias, out_dtype=self.dtype, kv=filing)
         q = qkv[:, :self.q_width]
         k = qkv[:, self.q_width:self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
-        rotate = getattr(self.position, "rotate_qk", None)
         if rotate is not None:
             rotate(q, k, self.num_heads, self.kv_heads, self.head_dim, ctx)
-        kcache, vcache = ctx.cache.kv_layer(cache.group, cache.layer)
-        table = ctx.tables[cache.group]
+        filed = filing is not None and filing.done
         o = ops.attention(q, kcache, vcache, table, ctx, self.num_heads, self.scale, self.window,
-                          append=(k, v) if cache.writes else None)
+                          append=(k, v) if cache.writes and not filed else None)
         return ops.linear(o, self.out_weight, self.out_bias, residual=residual,
                           out_dtype=torch.float32, out=residual)
 

@@ -387,6 +387,43 @@ PREFILL_GEMM_CASES = [
 ]
 
 
+@pytest.mark.parametrize("pair", [False, True], ids=["one_sm", "two_sms"])
+@pytest.mark.parametrize("lens_q,lens_ctx,H,Hkv,Dh,P,K,tile_n", [
+    ([130, 7, 200], [0, 50, 13], 4, 4, 64, 16, 256, 0),       # q | k | v of 256 columns each
+    ([300], [5], 6, 2, 32, 8, 136, 96),                       # grouped heads: 192 | 64 | 64, tiles that straddle the parts
+    ([129, 140], [0, 0], 3, 1, 24, 16, 64, 64),               # 72 | 24 | 24 = 120 columns: a ragged last chunk
+])
+def test_gemm_prefill_files_keys_and_values(lens_q, lens_ctx, H, Hkv, Dh, P, K, tile_n, pair):
+    """The many-row product as a q | k | v projection that also stores the key and value columns into
+    the paged cache: the same output as without, and the same cache as the append kernel leaves."""
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(21)
+    x, _ = paged_case(rs, lens_q, lens_ctx, H, Hkv, Dh, P, "bfloat16")
+    T, qw, kvw = sum(lens_q), H * Dh, Hkv * Dh
+    N = qw + 2 * kvw
+    a = dev(rs.randn(T, K).astype(np.float32), torch.bfloat16)
+    w = dev((rs.randn(N, K) / np.sqrt(K)).astype(np.float32), torch.bfloat16)
+    bias = dev(rs.randn(N).astype(np.float32))
+    plain_out = ops.gemm_tc_prefill(a, w, bias, out_dtype=torch.bfloat16, tile_n=tile_n, pair=pair)
+    kc1, vc1 = x["kc"].clone(), x["vc"].clone()
+    ops.kv_append(kc1, vc1, plain_out[:, qw:qw + kvw], plain_out[:, qw + kvw:], x["row_req"], x["pos"], x["table"])
+    kc2, vc2 = x["kc"].clone(), x["vc"].clone()
+    filing = ops.KVAppend(kc2, vc2, x["row_req"], x["pos"], x["table"], qw, kvw)
+    out = ops.gemm_tc_prefill(a, w, bias, out_dtype=torch.bfloat16, tile_n=tile_n, pair=pair, kv=filing)
+    torch.cuda.synchronize()
+    assert ops.tc_error() == 0 and filing.done
+    assert torch.equal(out, plain_out)
+    assert torch.equal(kc2, kc1) and torch.equal(vc2, vc1)
+    assert not torch.equal(kc2, x["kc"])
+    # through the dispatcher, which takes this path for many rows
+    kc3, vc3 = x["kc"].clone(), x["vc"].clone()
+    filing = ops.KVAppend(kc3, vc3, x["row_req"], x["pos"], x["table"], qw, kvw)
+    again = ops.linear(a, w, bias, out_dtype=torch.bfloat16, kv=filing)
+    if filing.done:
+        assert torch.equal(kc3, kc1) and torch.equal(vc3, vc1)
+    assert torch.equal(again, plain_out) or np.abs((again.float() - plain_out.float()).cpu().numpy()).max() < 4e-2
+
+
 @pytest.mark.parametrize("M,N,K,tile_n", PREFILL_GEMM_CASES)
 @pytest.mark.parametrize("act,out_dtype", [("none", "float32"), ("gelu_tanh", "bfloat16")])
 @pytest.mark.parametrize("pair", [False, True], ids=["one_sm", "two_sms"])

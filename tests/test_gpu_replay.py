@@ -149,3 +149,26 @@ def test_trace_run_program(model_folders, oracles, tmp_path):
             outputs.append(None)
     got = trace_tools.collect(trace, outputs)
     assert trace_tools.first_difference(got, want, 1e-4) is None
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [0, 1, 4, 7, 9, 11, 16])
+def test_random_configurations(seed, dtype, tmp_path):
+    """Configurations drawn from a seed (head sizes 16 to 128, 1 to 7 heads, widths that are no
+    multiple of 8, pages of 8 to 64 tokens), mixed and in portions, against the plain implementation."""
+    cfg, page, lengths = tiny_models.random_config(seed)
+    weights = tiny_models.numpy_weights(cfg, seed, scale=4.0, bf16_exact=True)
+    folder = tiny_models.write_folder(tmp_path / "m", cfg, weights)
+    reqs = {f"r{i}": t for i, t in enumerate(tiny_models.prompts(cfg, lengths, seed=seed))}
+    want = trace_tools.oracle(cfg, weights, reqs)
+    limit = tolerance(dtype, want)
+    for trace in (trace_tools.mixed(reqs, seed=seed), trace_tools.portions(reqs)):
+        from ayaka_py_b200.replay import ReplaySession
+        session = ReplaySession(folder, dtype, trace_tools.tokens_needed(trace, round_to=max(64, page)), page)
+        outputs = []
+        for record in trace:
+            logits = session.step(record)
+            outputs.append(None if logits is None or logits.shape[0] == 0 else logits.cpu().numpy())
+        session.cache.assert_clean()
+        bad = trace_tools.first_difference(trace_tools.collect(trace, outputs), want, limit)
+        assert bad is None, f"{cfg}: first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"

@@ -149,3 +149,26 @@ def write_folder(folder, cfg: dict, tensors: dict[str, np.ndarray], matrices_bf1
 def prompts(cfg: dict, lengths, seed: int):
     rs = np.random.RandomState(seed)
     return [rs.randint(0, cfg["vocab_size"], size=n).tolist() for n in lengths]
+
+
+def random_config(seed: int) -> tuple[dict, int, list[int]]:
+    """A tiny configuration drawn from a seed: head counts 1..7, head sizes 16..128 in steps of 16,
+    feed-forward widths that are and are not multiples of 8, odd vocabularies, every activation.
+    Returns (config, page size, prompt lengths).  Scores stay scaled (unscaled scores of random
+    weights reach the hundreds, where bfloat16 rounding of q and k alone moves a probability by
+    tens of per cent)."""
+    rs = np.random.RandomState(1000 + seed)
+    heads = int(rs.choice([1, 2, 3, 4, 5, 7]))
+    head_dim = int(rs.choice([16, 32, 48, 64, 64, 80, 128]))
+    inner = int(rs.choice([8 * rs.randint(8, 50), 4 * rs.randint(20, 90), rs.randint(70, 300)]))
+    cfg = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_layer": int(rs.randint(1, 4)),
+           "n_embd": heads * head_dim, "n_head": heads, "n_inner": inner, "vocab_size": int(rs.randint(40, 1300)),
+           "n_positions": int(rs.choice([200, 300, 520, 700])),
+           "layer_norm_epsilon": float(rs.choice([1e-5, 1e-6, 3e-4])),
+           "activation_function": str(rs.choice(["gelu_new", "gelu", "quick_gelu", "gelu_pytorch_tanh"])),
+           "scale_attn_weights": True, "scale_attn_by_inverse_layer_idx": bool(rs.rand() < 0.5),
+           "tie_word_embeddings": True}
+    page = int(rs.choice([8, 16, 32, 64]))
+    limit = cfg["n_positions"]
+    lengths = [int(x) for x in rs.randint(1, limit, size=rs.randint(2, 5))] + [int(rs.choice([128, 129, 256, limit]))]
+    return cfg, page, [min(n, limit) for n in lengths]

@@ -136,6 +136,23 @@ class Scheduler:
 
     # ------------------------------------------------------------- planning --
     def schedule(self) -> ScheduledStep | None:
+        """The next step, or None when nothing can run (no work, or a single request that the
+        cache cannot hold).  A pass that ends with nothing to run although several requests
+        hold pages gives the newest holder's pages back and plans again: two half-recomputed
+        prompts that fill the cache between them must not wait for each other for ever."""
+        while True:
+            before = self.stats.preemptions
+            plan = self._plan()
+            if plan is not None:
+                return plan
+            if self.stats.preemptions == before:          # the pass itself freed nothing
+                victim = self._pick_victim([])
+                if victim is None:
+                    self.stats.blocked_steps += 1
+                    return None
+                self._preempt(victim)
+
+    def _plan(self) -> ScheduledStep | None:
         budget = self.batch_tokens
         entries: list[ScheduledEntry] = []
 
@@ -202,7 +219,6 @@ class Scheduler:
         if shrunk:
             self.stats.shrunk_steps += 1
         if not entries:
-            self.stats.blocked_steps += 1
             return None
         self.stats.steps += 1
         decode_only = all(e.is_decode for e in entries)

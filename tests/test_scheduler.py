@@ -271,3 +271,49 @@ def test_lookahead_refuses_what_it_cannot_know():
     assert sched.lookahead(ahead) is None
     sched.resolve(ahead, {"r0": 7})
     assert "r0" not in sched.states
+
+
+@pytest.mark.parametrize("block", range(6))
+def test_random_pressure_never_blocks(block):
+    """Random prompts, budgets, arrivals and pools just large enough for the longest request alone
+    (so that requests are preempted and recompute): every request finishes, no step comes back
+    empty while work waits.  (Two half-recomputed prompts that held all pages between them, and a
+    pass that preempted a request and then had nothing left to run, used to end the loop.)"""
+    for seed in range(block * 60, block * 60 + 60):
+        rs = np.random.RandomState(seed)
+        page = int(rs.choice([4, 8, 16]))
+        n_req = int(rs.randint(2, 9))
+        plens = [int(rs.randint(1, 120)) for _ in range(n_req)]
+        news = [int(rs.randint(1, 40)) for _ in range(n_req)]
+        longest = max(p + n for p, n in zip(plens, news))
+        pages = -(-longest // page) + 1 + int(rs.randint(0, 6))
+        sched, cache = make(pages=pages, page_size=page, max_requests=int(rs.randint(2, 6)),
+                            batch_tokens=int(rs.choice([8, 16, 48, 200])), prefill_chunk=int(rs.choice([4, 8, 32, 128])),
+                            max_len=256)
+        arrive = sorted(int(rs.randint(0, 30)) for _ in range(n_req))
+        nxt, step, done = 0, 0, []
+        while sched.has_work() or nxt < n_req:
+            while nxt < n_req and arrive[nxt] <= step:
+                sched.add(req(nxt, plens[nxt], max_tokens=news[nxt], ignore_eos=True))
+                nxt += 1
+            if sched.has_work():
+                plan = sched.schedule()
+                assert plan is not None, f"seed {seed}: blocked at step {step}"
+                cache.check_invariants()
+                done += sched.update(plan, {e.state.request.request_id: 7 for e in plan.entries if e.sample})
+            step += 1
+            assert step < 20000
+        cache.assert_clean()
+        assert sorted(s.request.request_id for s in done) == sorted(f"r{i}" for i in range(n_req))
+        assert all(s.generated == news[int(s.request.request_id[1:])] for s in done)
+
+
+def test_two_recomputing_prompts_that_fill_the_pool():
+    """Both running requests are in the middle of recomputing, hold every page between them and need
+    one more each: the newer one gives its pages back, the older one goes on."""
+    sched, cache = make(pages=14, page_size=16, max_requests=5, batch_tokens=200, prefill_chunk=128, max_len=256)   # 13 usable
+    sched.add(req(0, 115, max_tokens=32, ignore_eos=True))
+    sched.add(req(1, 99, max_tokens=36, ignore_eos=True))
+    done = drive(sched, cache)
+    assert sorted(s.request.request_id for s in done) == ["r0", "r1"]
+    assert sched.stats.preemptions > 0

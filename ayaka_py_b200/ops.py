@@ -193,6 +193,8 @@ def attention_simt(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
     T = q.shape[0]
     if q.shape[1] != num_heads * Dh or q.stride(1) != 1 or q.dtype != kcache.dtype:
         raise KernelError("attention: q must be a [T, heads*head_dim] slice of the cache's dtype")
+    if total_rows != T:
+        raise KernelError(f"attention: {total_rows} rows named, q has {T} (rows beyond the count would stay unwritten)")
     if out is None:
         out = torch.empty((T, num_heads * Dh), dtype=q.dtype, device=q.device)
     R = req_pos0.numel()
@@ -478,6 +480,8 @@ def attention_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ta
     T = q.shape[0]
     if q.shape[1] != num_heads * Dh or q.stride(1) != 1 or q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
         raise KernelError("attention_tc: q must be a bfloat16 [T, heads*head_dim] slice, the cache bfloat16")
+    if total_rows != T:
+        raise KernelError(f"attention_tc: {total_rows} rows named, q has {T} (rows beyond the count would stay unwritten)")
     if not kcache.is_contiguous() or not vcache.is_contiguous():
         raise KernelError("attention_tc: the cache must be contiguous")
     if out is None:

@@ -89,6 +89,14 @@ __device__ MaxIdx block_argmax(const float* row, int V, MaxIdx* red) {
 
 constexpr double FIXED_ONE = 1099511627776.0;   // 2^40: exp(z - zmax) <= 1 as fixed point
 
+// exp(z - zmax) of one logit, z = logit / T rounded to 32-bit before the subtraction, as zmax is: the
+// row's maximum then has the weight 1 exactly and no weight is above it.  (Left to the compiler, the
+// product and the subtraction fuse, the maximum's own weight comes out as 1 - 4e-6 or 1 + 4e-6, and a
+// filter that keeps "the maximum only" - min_p = 1, top_k = 1 - kept nothing or the wrong token.)
+__device__ __forceinline__ float row_weight(float logit, float inv_t, float zmax) {
+  return expf(__fsub_rn(__fmul_rn(logit, inv_t), zmax));
+}
+
 __device__ __forceinline__ unsigned long long to_fixed(float e) {
   return (unsigned long long)((double)e * FIXED_ONE);
 }
@@ -102,7 +110,7 @@ __device__ uint32_t select_kth(const float* row, int V, float inv_t, float zmax,
     for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
     __syncthreads();
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      uint32_t bits = __float_as_uint(expf(row[i] * inv_t - zmax));
+      uint32_t bits = __float_as_uint(row_weight(row[i], inv_t, zmax));
       if ((bits & mask) == prefix) atomicAdd(&hist[(bits >> shift) & 255u], 1ull);
     }
     __syncthreads();
@@ -132,7 +140,7 @@ __device__ uint32_t select_nucleus(const float* row, int V, float inv_t, float z
   __syncthreads();
   unsigned long long mine = 0ull;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float e = expf(row[i] * inv_t - zmax);
+    float e = row_weight(row[i], inv_t, zmax);
     if (__float_as_uint(e) >= floor_bits) mine += to_fixed(e);
   }
   atomicAdd(&shared_u64[0], mine);
@@ -145,7 +153,7 @@ __device__ uint32_t select_nucleus(const float* row, int V, float inv_t, float z
     for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
     __syncthreads();
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      float e = expf(row[i] * inv_t - zmax);
+      float e = row_weight(row[i], inv_t, zmax);
       uint32_t bits = __float_as_uint(e);
       if (bits >= floor_bits && (bits & mask) == prefix) atomicAdd(&hist[(bits >> shift) & 255u], to_fixed(e));
     }
@@ -191,7 +199,11 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
     return;
   }
   const float inv_t = 1.0f / fmaxf(temp, 1e-6f);
-  const float zmax = top.v * inv_t;
+  const float zmax = __fmul_rn(top.v, inv_t);
+  if (!(top.v > -INFINITY)) {                    // a row without a finite logit: as greedy
+    if (threadIdx.x == 0) out[r] = top.i;
+    return;
+  }
   __shared__ unsigned long long hist[256];
   __shared__ unsigned long long shared_u64[2];
   __shared__ uint32_t shared_u32[2];
@@ -206,7 +218,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
   const int lo = min(V, (int)threadIdx.x * seg), hi = min(V, lo + seg);
   float s = 0.f;
   for (int i = lo; i < hi; ++i) {
-    float e = expf(row[i] * inv_t - zmax);
+    float e = row_weight(row[i], inv_t, zmax);
     if (__float_as_uint(e) >= keep_bits) s += e;
   }
   partial[threadIdx.x] = (double)s;
@@ -238,7 +250,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
     double run = chosen_base;
     int token = -1, last_positive = lo;
     for (int i = lo; i < hi; ++i) {
-      float p = expf(row[i] * inv_t - zmax);
+      float p = row_weight(row[i], inv_t, zmax);
       if (__float_as_uint(p) < keep_bits) p = 0.f;
       if (p > 0.f) last_positive = i;
       run += (double)p;

@@ -201,6 +201,31 @@ def test_temperature_draws_fall_in_the_twins_interval_and_are_batch_independent(
     assert alone[0] == out[9]
 
 
+def test_filters_that_keep_the_maximum_only():
+    """min_p = 1 and top_k = 1 leave the most likely token alone, whatever the temperature: the
+    maximum's own weight exp(z - zmax) has to come out as 1 exactly (with logit / T and the
+    subtraction fused it came out as 1 +- 4e-6, and nothing or the wrong token was kept).  A row
+    without a finite logit gives token 0, as greedy does."""
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(12)
+    for V in (11, 1971, 50257):
+        S = 48
+        logits = (rs.randn(S, V) * 6).astype(np.float32)
+        logits[7] = -np.inf
+        temp = rs.choice([0.3, 0.8, 1.7], size=S).astype(np.float32)
+        seed = rs.randint(0, 2 ** 62, S).astype(np.int64)
+        offset = rs.randint(0, 5000, S).astype(np.int64)
+        want = np.argmax(logits, axis=1)
+        want[7] = 0
+        ones = np.ones(S, dtype=np.float32)
+        only_max = ops.sample(dev(logits), dev(temp), dev(seed), dev(offset), None, None, dev(ones)).cpu().numpy()
+        assert only_max.tolist() == want.tolist()
+        top_one = ops.sample(dev(logits), dev(temp), dev(seed), dev(offset), dev(np.ones(S, dtype=np.int64)), None, None).cpu().numpy()
+        assert top_one.tolist() == want.tolist()
+        tiny_nucleus = ops.sample(dev(logits), dev(temp), dev(seed), dev(offset), None, dev(np.full(S, 1e-6, dtype=np.float32)), None)
+        assert tiny_nucleus.cpu().numpy().tolist() == want.tolist()
+
+
 def test_temperature_distribution():
     from ayaka_py_b200 import ops
     logits = np.tile(np.array([[0.0, 1.0, 2.0, -1.0, 0.5]], dtype=np.float32), (20000, 1))

@@ -100,12 +100,20 @@ def main(argv=None) -> int:
     out_dir.mkdir(parents=True, exist_ok=True)
     print("[trace_run] ready", file=sys.stderr, flush=True)
 
-    for line in sys.stdin:
+    for number, line in enumerate(sys.stdin, 1):
         line = line.strip()
         if not line:
             continue
-        record = json.loads(line)
-        logits = session.step(record)
+        # A step that cannot run (not JSON, an unknown token, more tokens than the pool holds, a fifth
+        # live request, ...) ends the program with one line that says which and why, and status 1.
+        record = None
+        try:
+            record = json.loads(line)
+            logits = session.step(record)
+        except Exception as problem:
+            step = record.get("step", "?") if isinstance(record, dict) else "?"
+            print(f"trace_run: input line {number} (step {step}): {type(problem).__name__}: {problem}", file=sys.stderr, flush=True)
+            return 1
         if logits is not None and logits.shape[0]:
             logits.to(torch.float32).cpu().numpy().astype("<f4").tofile(out_dir / f"{record['step']}.f32")
         else:

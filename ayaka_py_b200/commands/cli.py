@@ -130,10 +130,18 @@ def main(argv=None) -> int:
         from ..replay import main as replay_main
         return replay_main(argv[1:])
     args = build_parser().parse_args(argv)
-    if args.command == "generate":
-        return _generate(args)
-    if args.command == "random-weights":
-        return _random_weights(args)
+    # What the user can put right (a folder, a configuration, weights, a request, a size that a kernel
+    # refuses) comes back as one line and status 1; anything else keeps its traceback.
+    from ..cache.manager import NoFreeSlot, OutOfPages
+    from ..ops import KernelError
+    try:
+        if args.command == "generate":
+            return _generate(args)
+        if args.command == "random-weights":
+            return _random_weights(args)
+    except (ValueError, KernelError, OutOfPages, NoFreeSlot, FileNotFoundError) as problem:
+        print(f"ayaka_py_b200 {args.command}: {type(problem).__name__}: {problem}", file=sys.stderr)
+        return 1
     return 2
 
 

@@ -172,3 +172,31 @@ def test_random_configurations(seed, dtype, tmp_path):
         session.cache.assert_clean()
         bad = trace_tools.first_difference(trace_tools.collect(trace, outputs), want, limit)
         assert bad is None, f"{cfg}: first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_xl_layer_sizes(dtype, tmp_path):
+    """Two layers of the XL shape (width 1600, 25 heads, inner 6400, 50,257 tokens) with the engine's
+    own random-weights writer: four requests, mixed and with decoded tails, against the plain
+    implementation that reads the same folder.  The kernels run at the sizes the benchmark runs."""
+    import plain_gpt2
+    from ayaka_py_b200 import GPT2Config
+    from ayaka_py_b200.replay import ReplaySession
+    from ayaka_py_b200.weights import write_random_model
+
+    folder = tmp_path / "xl2"
+    write_random_model(str(folder), GPT2Config(vocab_size=50257, n_positions=1024, n_embd=1600, n_layer=2, n_head=25,
+                                               n_inner=6400), seed=7)
+    cfg, weights = plain_gpt2.read_model_folder(folder)
+    rs = np.random.RandomState(3)
+    reqs = {f"x{i}": [int(t) for t in rs.randint(0, 50257, size=n)] for i, n in enumerate([300, 70, 9, 640])}
+    want = trace_tools.oracle(cfg, weights, reqs)
+    for trace in (trace_tools.mixed(reqs, seed=1), trace_tools.tail_decoded(reqs, 32)):
+        session = ReplaySession(str(folder), dtype, trace_tools.tokens_needed(trace), 16)
+        outputs = []
+        for record in trace:
+            logits = session.step(record)
+            outputs.append(None if logits is None or logits.shape[0] == 0 else logits.cpu().numpy())
+        session.cache.assert_clean()
+        bad = trace_tools.first_difference(trace_tools.collect(trace, outputs), want, tolerance(dtype, want))
+        assert bad is None, f"first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"

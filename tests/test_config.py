@@ -72,3 +72,28 @@ def test_engine_config():
     for bad in ({"page_size": 12}, {"kv_pages": 1}, {"dtype": "fp8"}, {"batch_tokens": 0}):
         with pytest.raises(ConfigError):
             EngineConfig(**bad)
+
+
+def test_command_line_says_what_is_wrong_in_one_line(tmp_path, capsys):
+    """A folder without config.json, an architecture nobody registered, a configuration that
+    contradicts itself: status 1 or 2 and one line on standard error, no traceback."""
+    import json
+
+    from ayaka_py_b200.commands.cli import main
+
+    assert main(["generate", str(tmp_path / "nowhere"), "--prompt-ids", "5"]) != 0
+    said = capsys.readouterr()
+    assert "config.json" in said.err + said.out
+    other = tmp_path / "other"
+    other.mkdir()
+    (other / "config.json").write_text(json.dumps({"architectures": ["SomethingElseLM"], "model_type": "else"}))
+    assert main(["generate", str(other), "--prompt-ids", "5"]) == 1
+    err = capsys.readouterr().err
+    assert "unknown architecture 'SomethingElseLM'" in err and "GPT2LMHeadModel" in err and "Traceback" not in err
+    odd = tmp_path / "odd"
+    odd.mkdir()
+    (odd / "config.json").write_text(json.dumps({"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+                                                 "n_embd": 65, "n_head": 4}))
+    assert main(["generate", str(odd), "--prompt-ids", "5"]) == 1
+    err = capsys.readouterr().err
+    assert "n_embd (65) must be divisible by n_head (4)" in err and len(err.strip().splitlines()) == 1

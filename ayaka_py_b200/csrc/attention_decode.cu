@@ -519,7 +519,8 @@ AYK_EXPORT int ayk_attention_decode(void* out, const void* q, int q_stride, void
     AYK_REQUIRE(items <= 0x7fffffffL, "ayk_attention_decode: too many partitions (%ld)", items);
     const float scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = 2 * (size_t)PART * Dh * 2 + (size_t)WARPS * rows * (Dh + 2) * sizeof(float);
-    static bool configured = false;
+    static AykPerDevice configured_on;
+    bool& configured = configured_on.here();
     if (!configured) {
       const int most = 2 * PART * 128 * 2 + WARPS * 8 * (128 + 2) * 4;
       if (cudaFuncSetAttribute(decode_mma_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||

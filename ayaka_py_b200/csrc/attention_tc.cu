@@ -51,7 +51,6 @@ struct AttnArgs {
 __global__ void __launch_bounds__(THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const AttnArgs args) {
-  pdl_trigger();
   // Row ranges, positions and block tables are the step's inputs: the set-up below (barriers, tensor
   // memory) runs while the kernel before this one finishes; pdl_wait() comes before the first access
   // to q, the cache or the output.
@@ -83,7 +82,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   }
-  if (req < 0) return;
+  if (req < 0) { pdl_trigger(); return; }
   const int h = blockIdx.x, kvh = h / (args.H / args.Hkv);
   const int rows = min(BQ, q_len - q0);
   const int row0 = args.req_q_start[req] + q0;
@@ -98,6 +97,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t raw = smem_u32(smem_raw);
   if (raw & 1023u) {                 // the swizzled tiles need 1024-byte alignment; no slack is reserved for it
     if (threadIdx.x == 0) atomicExch(args.error, 18);
+    pdl_trigger();
     return;
   }
   const uint32_t base = raw;
@@ -130,6 +130,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
   const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  // Only now may the next kernel be scheduled: a dependent CTA that landed on this SM before the
+  // allocation above could take tensor-memory columns that this CTA then waits for without bound,
+  // while the dependent waits for this kernel.  (Kernels that can share an SM must ask for 512
+  // columns or fewer between them.)
+  pdl_trigger();
 
   pdl_wait();
   if (warp == 4) {
@@ -400,14 +405,17 @@ AYK_EXPORT int ayk_attention_tc_supported(int Dh, int page_size, int q_stride) {
 
 AYK_EXPORT int ayk_attention_tc_error() { return g_error_host ? *g_error_host : 0; }
 
-// out [T, H*64] bf16; q: rows of q_stride elements (head h at column h*64) of a
-// matrix with q_cols columns in total; caches [pages, page_size, Hkv, 64] bf16.
-AYK_EXPORT int ayk_attention_tc(void* out, const void* q, int q_stride, int total_rows, const void* kcache,
+// out [T, H*64] bf16; q: q_rows rows of q_stride elements (head h at column h*64);
+// caches [pages, page_size, Hkv, 64] bf16.  The requests named by req_q_start / req_pos0 /
+// table cover total_rows of q's rows (their row numbers are absolute); a step whose first rows
+// are handled by another kernel passes the tail of the request arrays and the rows they cover.
+AYK_EXPORT int ayk_attention_tc(void* out, const void* q, int q_stride, int q_rows, int total_rows, const void* kcache,
                                 const void* vcache, int pages, const int* table, int table_stride,
                                 const int* req_q_start, const int* req_pos0, int num_req, int H, int Hkv, int Dh,
                                 int page_size, float scale, int window, cudaStream_t stream) {
   if (num_req == 0 || total_rows == 0) return 0;
   if (ayk_attention_tc_supported(Dh, page_size, q_stride) != 0) return -1;
+  AYK_REQUIRE(q_rows >= total_rows, "ayk_attention_tc: %d rows named, q has %d", total_rows, q_rows);
   AYK_REQUIRE(Hkv >= 1 && H % Hkv == 0 && H <= 65535, "ayk_attention_tc: %d heads cannot share %d key/value heads", H, Hkv);
   AYK_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0 && (uintptr_t)out % 16 == 0,
               "ayk_attention_tc: operands must be 16-byte aligned");
@@ -417,7 +425,7 @@ AYK_EXPORT int ayk_attention_tc(void* out, const void* q, int q_stride, int tota
   }
   CUtensorMap mq, mk, mv;
   {
-    cuuint64_t dims[2] = {(cuuint64_t)H * DH, (cuuint64_t)total_rows};
+    cuuint64_t dims[2] = {(cuuint64_t)H * DH, (cuuint64_t)q_rows};
     cuuint64_t strides[1] = {(cuuint64_t)q_stride * 2};
     cuuint32_t box[2] = {(cuuint32_t)DH, (cuuint32_t)BQ};
     cuuint32_t elem[2] = {1, 1};

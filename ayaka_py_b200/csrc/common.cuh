@@ -82,6 +82,19 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 int ayk_pdl_enabled();
+int ayk_sm_count();          // streaming multiprocessors of the current device
+
+// "Has this kernel's launch attribute been set on the current device?"  Attributes of a kernel
+// (dynamic shared memory, cluster size) belong to the device's copy of the kernel, so a flag per
+// process would leave a second device unconfigured.  Returns a reference to the current device's flag.
+struct AykPerDevice {
+  bool done[64] = {};
+  bool& here() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = 0;
+    return done[device];
+  }
+};
 
 template <typename... KArgs, typename... Args>
 cudaError_t ayk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

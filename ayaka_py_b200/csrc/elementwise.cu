@@ -35,6 +35,20 @@ int ayk_pdl_enabled() { return g_pdl; }
 // Launch kernels with programmatic stream serialization (1) or plainly (0).
 AYK_EXPORT void ayk_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
+// Streaming multiprocessors of the current device (read once per device; 148 on a B200).
+static int g_sm_count[64] = {0};
+int ayk_sm_count() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+  if (g_sm_count[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n < 1) return 148;
+    g_sm_count[device] = n;
+  }
+  return g_sm_count[device];
+}
+AYK_EXPORT int ayk_device_sm_count() { return ayk_sm_count(); }
+
 AYK_EXPORT int ayk_init(int device) {
   cudaError_t err = cudaSetDevice(device);
   if (err != cudaSuccess) return ayk_fail("cudaSetDevice(%d): %s", device, cudaGetErrorString(err));
@@ -42,6 +56,7 @@ AYK_EXPORT int ayk_init(int device) {
   err = cudaGetDeviceProperties(&prop, device);
   if (err != cudaSuccess) return ayk_fail("cudaGetDeviceProperties: %s", cudaGetErrorString(err));
   if (prop.major != 10) return ayk_fail("this library is built for sm_100a, device %d is sm_%d%d", device, prop.major, prop.minor);
+  if (device >= 0 && device < 64) g_sm_count[device] = prop.multiProcessorCount;
   return 0;
 }
 

@@ -578,11 +578,15 @@ template <int BT>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& args, int splits, cudaStream_t stream) {
   constexpr int STAGES = stages_for(BT);
   constexpr size_t SMEM = 1024 + (size_t)STAGES * (A_BYTES + BT * BLOCK_K * 2) + 8 * (2 * STAGES + 2);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: shared memory %zu: %s", SMEM, cudaGetErrorString(err));
-    configured = true;
+  static AykPerDevice configured;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    bool& done = configured.here();
+    if (!done) {
+      cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+      if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: shared memory %zu: %s", SMEM, cudaGetErrorString(err));
+      done = true;
+    }
   }
   dim3 grid((args.N + BLOCK_N - 1) / BLOCK_N, (args.M + BT - 1) / BT, splits);
   ayk_launch(gemm_tc_kernel<BT>, grid, dim3(THREADS), SMEM, stream, mw, mx, args);
@@ -594,14 +598,18 @@ template <int BT>
 int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const EpilogueArgs& args, int splits, cudaStream_t stream) {
   constexpr int STAGES = cluster_stages_for(BT);
   constexpr size_t SMEM = 1024 + (size_t)STAGES * (A_BYTES + BT * BLOCK_K * 2) + 8 * (2 * STAGES + 3) + 16 + BLOCK_N * BT * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: shared memory %zu: %s", SMEM, cudaGetErrorString(err));
-    // clusters of 16 are beyond the portable size of 8
-    err = cudaFuncSetAttribute(gemm_tc_kernel<BT, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: clusters of 16: %s", cudaGetErrorString(err));
-    configured = true;
+  static AykPerDevice configured;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    bool& done = configured.here();
+    if (!done) {
+      cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+      if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: shared memory %zu: %s", SMEM, cudaGetErrorString(err));
+      // clusters of 16 are beyond the portable size of 8
+      err = cudaFuncSetAttribute(gemm_tc_kernel<BT, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (err != cudaSuccess) return ayk_fail("ayk_gemm_tc: clusters of 16: %s", cudaGetErrorString(err));
+      done = true;
+    }
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((args.N + BLOCK_N - 1) / BLOCK_N, 1, splits);
@@ -721,6 +729,9 @@ EncodeTiledFn g_na_encode = nullptr;
 // Once per device, with that device current: the names of the __device__ arrays
 // are host-side stand-ins, so their device addresses are asked for here.
 int no_alloc_setup(int device) {
+  // Under the library's mutex: two threads that make their first call on a device together
+  // would otherwise both write the table.
+  std::lock_guard<std::mutex> lock(g_mutex);
   NoAllocDevice& d = g_na_devices[device];
   if (d.ready) return 0;
   if (g_na_encode == nullptr) {
@@ -764,7 +775,15 @@ AYK_EXPORT int ayk_gemm_tc_no_alloc(void* C, const void* X, const void* W, const
   const int BT = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
   const int tiles = ((N + BLOCK_N - 1) / BLOCK_N) * ((M + BT - 1) / BT);
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
-  if (splits <= 0) splits = tiles >= 74 ? 1 : 148 / tiles;
+  if (splits <= 0) {
+    // The library chooses: about one CTA per multiprocessor, but never more partial sums than the
+    // built-in scratch holds, and no split at all where the tile counters would not suffice.
+    const int sms = ayk_sm_count();
+    splits = tiles >= sms / 2 ? 1 : sms / tiles;
+    const long long room = (long long)AYK_NO_ALLOC_MAX_PARTIALS / ((long long)M * N);
+    if (splits > room) splits = room < 1 ? 1 : (int)room;
+    if (tiles > AYK_NO_ALLOC_MAX_TILES) splits = 1;
+  }
   if (splits > total_kb) splits = total_kb;
   const int kb_per_split = (total_kb + splits - 1) / splits;
   splits = (total_kb + kb_per_split - 1) / kb_per_split;

@@ -25,8 +25,13 @@
 //     Every GPU whose context loads the library holds these arrays (about
 //     4 MiB) until the process exits.
 //   * The first call on a device looks up the arrays' device addresses (and the
-//     driver's tensor-map encoder).  Make that first call outside any stream
-//     capture.
+//     driver's tensor-map encoder) and sets the kernel's shared-memory
+//     attribute on that device; it does so under the library's mutex, so first
+//     calls from several threads, or on several devices, are safe.  Make that
+//     first call outside any stream capture.
+//   * With splits <= 0 the library chooses a split count that fits the built-in
+//     scratch (down to no split at all); only a count that the caller asks for
+//     can be refused as too large.
 //   * All calls share the one scratch region, which keeps whatever the last
 //     call left in it; the entry point clears the counters itself before each
 //     launch.  Two calls that overlap on the GPU (different streams, or one

@@ -260,7 +260,26 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V,
   }
 }
 
+// Tokens that a row must not produce yet (stop ids and EOS before the request's min_tokens,
+// request/stream.py:130-136 in the reference): their logits become -inf before sampling.
+__global__ void ban_tokens_kernel(float* logits, const int* rows, const int* tokens, int count, int S, int V) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const int r = rows[i], t = tokens[i];
+  if (r >= 0 && r < S && t >= 0 && t < V) logits[(size_t)r * V + t] = -INFINITY;
+}
+
 }  // namespace
+
+// logits[rows[i], tokens[i]] = -inf for i < count (pairs outside [S, V] are ignored).
+AYK_EXPORT int ayk_ban_tokens(float* logits, const int* rows, const int* tokens, int count, int S, int V,
+                              cudaStream_t stream) {
+  if (count == 0) return 0;
+  ayk_launch(ban_tokens_kernel, dim3((count + 127) / 128), dim3(128), 0, stream, logits, rows, tokens, count, S, V);
+  return ayk_check_launch("ayk_ban_tokens");
+}
 
 // out[S] int32.  temperature null or 0 for a row: greedy.  seed/offset int64 [S].
 // top_k (int64, <= 0 off), top_p and min_p (float32) are null or [S].

@@ -13,6 +13,8 @@ computed than it needed, which is dropped.
 
 from __future__ import annotations
 
+import time
+
 import torch
 
 from ..cache.manager import CacheManager
@@ -46,6 +48,8 @@ class Engine:
         self._inflight: _Launched | None = None
         self._copy_stream = torch.cuda.Stream() if torch.cuda.is_available() else None
         self._pinned: list[torch.Tensor] = []      # host landing places of sampled tokens, reused
+        self.host_seconds = 0.0                    # time inside step() that was not spent waiting for the GPU
+        self.steps_run = 0
 
     def submit(self, request: Request) -> None:
         self.scheduler.add(request)
@@ -62,6 +66,8 @@ class Engine:
     def step(self) -> list[GenerationResult]:
         """Runs one step to its end (its tokens on the host) and returns the
         requests that finished in it.  The step after it may already be running."""
+        began = time.perf_counter()
+        self._waited = 0.0
         if self._inflight is None:
             plan = self.scheduler.schedule()
             if plan is None:
@@ -77,7 +83,10 @@ class Engine:
             if plan is not None:
                 ahead = self._launch(plan, tokens_from=current.sampled)
         self._inflight = ahead
-        return self._finish_step(current)
+        results = self._finish_step(current)
+        self.host_seconds += time.perf_counter() - began - self._waited
+        self.steps_run += 1
+        return results
 
     def _launch(self, plan: ScheduledStep, tokens_from: torch.Tensor | None = None) -> "_Launched":
         """Hands a planned step to the GPU: upload, forward, sampling, and the copy
@@ -97,8 +106,9 @@ class Engine:
             sampled = host = done = None
             if rows:
                 pending = 1 if ahead else 0         # a token of each row is still on its way
+                banned = [(i, t) for i, s in enumerate(rows) for t in self.scheduler.banned_tokens(s, pending)]
                 sampled = self.sampler.sample(logits, [s.request.sampling for s in rows], [s.seed for s in rows],
-                                              [s.generated + pending for s in rows])
+                                              [s.generated + pending for s in rows], banned=banned)
                 host = self._pinned.pop() if self._pinned else None
                 if host is None or host.numel() < len(rows):
                     host = torch.empty(max(len(rows), self.config.max_requests), dtype=torch.int32, pin_memory=True)
@@ -118,13 +128,17 @@ class Engine:
     def _finish_step(self, launched: "_Launched") -> list[GenerationResult]:
         sampled = {}
         if launched.rows:
+            t0 = time.perf_counter()
             launched.done.synchronize()
+            self._waited = getattr(self, "_waited", 0.0) + time.perf_counter() - t0
             tokens = launched.host[:len(launched.rows)].tolist()
             self._pinned.append(launched.host)
             for s, token in zip(launched.rows, tokens):
                 sampled[s.request.request_id] = token
         elif self._inflight is None:
+            t0 = time.perf_counter()
             torch.cuda.synchronize()
+            self._waited = getattr(self, "_waited", 0.0) + time.perf_counter() - t0
         done = self.scheduler.resolve(launched.plan, sampled)
         results = [self.scheduler.result_of(s) for s in done]
         for r in results:

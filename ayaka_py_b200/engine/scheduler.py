@@ -307,11 +307,25 @@ class Scheduler:
         self.stats.decode_tokens += len(entries)
         return ScheduledStep(entries, reservation, True)
 
-    def _finish_reason(self, s: RequestState, token: int) -> str | None:
-        """``request/stream.py:130-163``: stop ids and EOS count only from
-        ``min_tokens`` on; the length limit always."""
+    def banned_tokens(self, s: RequestState, pending: int = 0) -> tuple[int, ...]:
+        """Token ids that ``s`` must not sample next: its stop ids, and EOS unless it
+        ignores it, while it has generated fewer than ``min_tokens``
+        (``request/stream.py:130-136``).  ``pending``: tokens of ``s`` that are sampled
+        but not yet on the host."""
         stop = s.request.stop
-        if s.generated >= stop.min_tokens:
+        if s.generated + pending >= stop.min_tokens:
+            return ()
+        ids = tuple(stop.stop_token_ids)
+        if not stop.ignore_eos and self.eos_token_id is not None:
+            ids += (self.eos_token_id,)
+        return ids
+
+    def _finish_reason(self, s: RequestState, token: int) -> str | None:
+        """``request/stream.py:138-163``: a stop id or EOS ends the request once more than
+        ``min_tokens`` tokens exist, this one included (earlier ones are banned before
+        sampling and cannot appear); the length limit always."""
+        stop = s.request.stop
+        if s.generated > stop.min_tokens:
             if token in stop.stop_token_ids:
                 return "stop"
             if not stop.ignore_eos and self.eos_token_id is not None and token == self.eos_token_id:

@@ -7,6 +7,12 @@ single decoded tokens, cut anywhere (the reference's slices,
 only these tokens, from the cache that earlier steps left, and returns float32
 logits at the wanted places only, in the order of the entries and of ``want``.
 
+Inside the packed batch the entries that bring a single token come first, whatever
+order the caller gave them in (the reference packs decodes first too,
+``sched/continuous.py:325-328``): a mixed step can then run its decode rows and its
+prompt rows through different attention kernels, each on one contiguous range of
+rows.  ``want_rows`` keeps the caller's order.
+
 All step metadata is packed into one pinned int32 buffer and copied to the
 device with one transfer; kernels read block tables and row maps from there
 (the reference uploads one tensor per field, ``runner/buffers.py:369-462``, and
@@ -53,6 +59,8 @@ class StepContext:
     host: dict = field(default_factory=dict)   # the same arrays as NumPy, for host-side decisions
     max_q_len: int = 1
     max_kv_len: int = 1
+    # The first ``num_single`` requests of the step (= its first rows) bring one token each.
+    num_single: int = 0
     # Cache rows that earlier steps wrote are complete when this step's kernels start: the upload
     # of the step's inputs (or a graph launch) lies between.  Kernels may read them ahead of the
     # kernels launched just before them.
@@ -110,6 +118,10 @@ class StepRunner:
         R = max(n, pad_to or 0)
         if R > max(self.max_requests, pad_to or 0):
             raise ValueError(f"{R} requests in one step, the engine was built for {self.max_requests}")
+        # single-token entries first (stable): packed place -> index in ``entries``
+        order = sorted(range(n), key=lambda i: len(entries[i].tokens) != 1)
+        given = entries
+        entries = [given[i] for i in order]
         counts = np.ones(R, dtype=np.int64)
         counts[:n] = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=n)
         if (counts < 1).any():
@@ -144,7 +156,7 @@ class StepRunner:
         tok = self._field(h, "tokens", T)
         pos = self._field(h, "positions", T)
         row_req = self._field(h, "row_req", T)
-        wanted = []
+        wanted_of = [None] * n          # by place in the caller's list: the logits keep the caller's order
         for r, e in enumerate(entries):
             a, b = int(q_start[r]), int(q_start[r + 1])
             tok[a:b] = np.asarray(e.tokens, dtype=np.int64)
@@ -153,7 +165,8 @@ class StepRunner:
             for w in e.want:
                 if not 0 <= w < b - a:
                     raise ValueError(f"want {w} is outside the entry's {b - a} tokens")
-                wanted.append(a + int(w))
+            wanted_of[order[r]] = [a + int(w) for w in e.want]
+        wanted = [row for rows in wanted_of for row in rows]
         for r in range(n, R):                      # padding lanes
             a = int(q_start[r])
             tok[a], pos[a], row_req[a] = 0, 0, r
@@ -189,8 +202,10 @@ class StepRunner:
             req_q_start=self._field(d, "req_q_start", R + 1), req_pos0=self._field(d, "req_pos0", R),
             req_slot=self._field(d, "req_slot", R), req_kv_len=self._field(d, "req_kv_len", R),
             tables=tables, cache=self.cache, dtype=self.model.dtype,
-            host={"q_start": q_start, "pos0": starts, "slots": slots, "kv_len": ends, "counts": counts},
-            max_q_len=int(counts.max()), max_kv_len=int(ends.max()), earlier_rows_settled=True)
+            host={"q_start": q_start, "pos0": starts, "slots": slots, "kv_len": ends, "counts": counts,
+                  "order": np.asarray(order + list(range(n, R)), dtype=np.int64)},   # packed place -> caller's index
+            max_q_len=int(counts.max()), max_kv_len=int(ends.max()), earlier_rows_settled=True,
+            num_single=int((counts == 1).sum()))
 
     def run(self, entries: Sequence[StepEntry], tokens_from: torch.Tensor | None = None) -> torch.Tensor:
         """Logits [S, V] float32 on the device.  The caller has reserved the
@@ -199,7 +214,7 @@ class StepRunner:
         tokens whose host copies are not known yet."""
         ctx = self.prepare(entries)
         if tokens_from is not None:
-            if ctx.num_rows != len(entries):
+            if ctx.num_rows != len(entries):      # then the packed order is the caller's order
                 raise ValueError("tokens can come from the device only for entries of one token each")
             ctx.tokens[:len(entries)].copy_(tokens_from[:len(entries)])
         return self.model.forward(ctx)

@@ -229,11 +229,31 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None,
     return out
 
 
+def ban_tokens(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor) -> None:
+    """logits[rows[i], tokens[i]] = -inf, in place (int32 index tensors on the device)."""
+    lib = _ready()
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or logits.dim() != 2:
+        raise KernelError("ban_tokens: logits must be contiguous float32 [S, V]")
+    if rows.numel() != tokens.numel():
+        raise KernelError("ban_tokens: one row index per token id")
+    S, V = logits.shape
+    _launch(lib.ayk_ban_tokens(_ptr(logits), _ptr(_i32(rows, "rows")), _ptr(_i32(tokens, "tokens")),
+                               ctypes.c_int(rows.numel()), ctypes.c_int(S), ctypes.c_int(V), _stream()))
+
+
 # ------------------------------------------------------------- dispatchers --
 
 _tc_scratch: dict = {}
 _tc_retired: list = []          # a captured CUDA graph may still write to an outgrown buffer
-SM_COUNT = 148
+_sm_count = 0
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device, asked of the driver once (148 on a B200)."""
+    global _sm_count
+    if _sm_count == 0:
+        _sm_count = int(_ready().ayk_device_sm_count())
+    return _sm_count
 
 
 def _tc_workspace(device, floats: int):
@@ -261,12 +281,13 @@ def tc_splits(M: int, N: int, K: int) -> int:
     bt = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
     tiles = -(-N // 128) * -(-M // bt)
     blocks = -(-K // 64)
-    if tiles >= SM_COUNT or blocks < 4 or M > CLUSTER_ROWS:
+    sms = sm_count()
+    if tiles >= sms or blocks < 4 or M > CLUSTER_ROWS:
         return 1          # more rows: partial sums through global scratch cost more than the split saves (measured)
-    if tiles * 16 <= SM_COUNT * 3 // 2 and blocks >= 64:
+    if tiles * 16 <= sms * 3 // 2 and blocks >= 64:
         return 16
     for p in (8, 4, 2):
-        if tiles * p <= SM_COUNT * 14 // 10 and blocks >= p:
+        if tiles * p <= sms * 14 // 10 and blocks >= p:
             return p
     return 1
 
@@ -364,7 +385,7 @@ def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None 
             raise KernelError("gemm_tc_prefill: keys and values are filed only by a plain bfloat16 q | k | v projection")
         P = kv.kcache.shape[1]
         _launch(lib.ayk_gemm_tc_prefill_kv(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), ctypes.c_int(M), ctypes.c_int(N),
-                                           ctypes.c_int(K), ctypes.c_int(tile_n), ctypes.c_int(SM_COUNT),
+                                           ctypes.c_int(K), ctypes.c_int(tile_n), ctypes.c_int(sm_count()),
                                            ctypes.c_int(-1 if pair is None else int(pair)), _ptr(kv.kcache), _ptr(kv.vcache),
                                            _ptr(_i32(kv.row_req, "row_req")), _ptr(_i32(kv.positions, "positions")),
                                            _ptr(_i32(kv.table, "table")), ctypes.c_int(kv.table.stride(0)), ctypes.c_int(P),
@@ -373,7 +394,7 @@ def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None 
         return out
     _launch(lib.ayk_gemm_tc_prefill(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M),
                                     ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]),
-                                    ctypes.c_int(_tag(out_dtype)), ctypes.c_int(tile_n), ctypes.c_int(SM_COUNT),
+                                    ctypes.c_int(_tag(out_dtype)), ctypes.c_int(tile_n), ctypes.c_int(sm_count()),
                                     ctypes.c_int(-1 if pair is None else int(pair)), _stream()))
     return out
 
@@ -473,27 +494,34 @@ def attention_tc_takes(q: torch.Tensor, kcache: torch.Tensor) -> bool:
 
 def attention_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, table: torch.Tensor,
                  req_q_start: torch.Tensor, req_pos0: torch.Tensor, total_rows: int, num_heads: int,
-                 scale: float, window: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Causal attention of prompt portions over the paged cache on tcgen05 (bfloat16, head size 64)."""
+                 scale: float, window: int | None = None, out: torch.Tensor | None = None,
+                 first_row: int = 0) -> torch.Tensor:
+    """Causal attention of prompt portions over the paged cache on tcgen05 (bfloat16, head size 64).
+    ``first_row``: the requests named here cover rows first_row .. T of ``q`` and ``out`` (their
+    ``req_q_start`` holds absolute row numbers); earlier rows are left to another kernel."""
     lib = _ready()
     pages, P, Hkv, Dh = kcache.shape
     T = q.shape[0]
     if q.shape[1] != num_heads * Dh or q.stride(1) != 1 or q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
         raise KernelError("attention_tc: q must be a bfloat16 [T, heads*head_dim] slice, the cache bfloat16")
-    if total_rows != T:
-        raise KernelError(f"attention_tc: {total_rows} rows named, q has {T} (rows beyond the count would stay unwritten)")
+    if total_rows + first_row != T:
+        raise KernelError(f"attention_tc: rows {first_row} .. {first_row + total_rows} named, q has {T} "
+                          f"(rows beyond the count would stay unwritten)")
     if not kcache.is_contiguous() or not vcache.is_contiguous():
         raise KernelError("attention_tc: the cache must be contiguous")
     if out is None:
         out = torch.empty((T, num_heads * Dh), dtype=q.dtype, device=q.device)
     R = req_pos0.numel()
-    _launch(lib.ayk_attention_tc(_ptr(out), _ptr(q), ctypes.c_int(q.stride(0)), ctypes.c_int(total_rows),
+    _launch(lib.ayk_attention_tc(_ptr(out), _ptr(q), ctypes.c_int(q.stride(0)), ctypes.c_int(T), ctypes.c_int(total_rows),
                                  _ptr(kcache), _ptr(vcache), ctypes.c_int(pages), _ptr(_i32(table, "table")),
                                  ctypes.c_int(table.stride(0)), _ptr(_i32(req_q_start, "req_q_start")),
                                  _ptr(_i32(req_pos0, "req_pos0")), ctypes.c_int(R), ctypes.c_int(num_heads),
                                  ctypes.c_int(Hkv), ctypes.c_int(Dh), ctypes.c_int(P), ctypes.c_float(scale),
                                  ctypes.c_int(window or 0), _stream()))
     return out
+
+
+MIXED_DECODE_MIN = 1     # single-token requests in a mixed step from which they take the decode kernels
 
 
 def tc_error() -> int:
@@ -519,6 +547,17 @@ def attention(q, kcache, vcache, table, ctx, num_heads: int, scale: float,
     if append is not None:
         kv_append(kcache, vcache, append[0], append[1], ctx.row_req, ctx.positions, table)
     if attention_tc_takes(q, kcache):
+        # A mixed step: its single-token requests are its first rows (the step runner packs them
+        # first).  They go through the split-context decode kernels, one row per request, and the
+        # prompt portions through the tiled kernel: two launches on disjoint row ranges over one
+        # block table.  (As rows of the tiled kernel each would be a 128-row tile with one live row.)
+        D = getattr(ctx, "num_single", 0)
+        if D >= MIXED_DECODE_MIN and D < ctx.num_requests:
+            out = torch.empty((ctx.num_rows, q.shape[1]), dtype=q.dtype, device=q.device)
+            attention_decode(q[:D], kcache, vcache, table[:D], ctx.req_pos0[:D], num_heads, scale, window,
+                             ctx.cache.max_len, out=out[:D], settled=getattr(ctx, "earlier_rows_settled", False))
+            return attention_tc(q, kcache, vcache, table[D:], ctx.req_q_start[D:], ctx.req_pos0[D:],
+                                ctx.num_rows - D, num_heads, scale, window, out=out, first_row=D)
         return attention_tc(q, kcache, vcache, table, ctx.req_q_start, ctx.req_pos0, ctx.num_rows,
                             num_heads, scale, window)
     return attention_simt(q, kcache, vcache, table, ctx.req_q_start, ctx.req_pos0, ctx.num_rows,

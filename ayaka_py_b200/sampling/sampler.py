@@ -35,11 +35,17 @@ class Sampler:
         self._turn = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               offsets: Sequence[int]) -> torch.Tensor:
-        """logits [S, V] float32 (device) -> tokens [S] int32 (device)."""
+               offsets: Sequence[int], banned: Sequence[tuple[int, int]] = ()) -> torch.Tensor:
+        """logits [S, V] float32 (device) -> tokens [S] int32 (device).
+        ``banned``: (row, token id) pairs that must not be produced in this step (stop ids
+        before a request's ``min_tokens``, ``request/stream.py:130-136``): their logits are
+        set to -inf first, for greedy rows and draws alike."""
         S = logits.shape[0]
         if not (len(params) == len(seeds) == len(offsets) == S):
             raise ValueError("one set of options per logits row")
+        if banned:
+            pairs = torch.tensor(list(banned), dtype=torch.int32).t().contiguous().to(logits.device)
+            ops.ban_tokens(logits, pairs[0], pairs[1])
         if all(p.greedy for p in params):
             return ops.sample(logits)
         if S > self.rows:

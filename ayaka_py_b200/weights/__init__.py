@@ -2,7 +2,8 @@
 
 from .loader import DictStore, FolderStore, WeightMismatchError, load_weights
 from .random_init import random_tensors, write_random_model
-from .safetensors import CheckpointCorruptError, SafetensorsFile, write_safetensors
+from .safetensors import (CheckpointCorruptError, SafetensorsFile, UnsupportedWeightFormatError,
+                          write_safetensors)
 
-__all__ = ["CheckpointCorruptError", "SafetensorsFile", "write_safetensors", "WeightMismatchError",
+__all__ = ["CheckpointCorruptError", "UnsupportedWeightFormatError", "SafetensorsFile", "write_safetensors", "WeightMismatchError",
            "FolderStore", "DictStore", "load_weights", "random_tensors", "write_random_model"]

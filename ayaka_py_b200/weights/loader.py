@@ -10,9 +10,14 @@ Conv1D weights) and dtype, and binds it.  Two parts that name the same source
 share one tensor on the device (a tied head).
 
 Dtypes: ``matrix`` tensors are kept in the compute dtype (bfloat16 or
-float32; narrowing float32 -> bfloat16 is allowed, as in
-``model_loader/validate.py:83-95``); ``vector`` tensors stay float32; ``int``
-tables become int32.
+float32), ``vector`` tensors in float32, ``int`` tables in int32.  A stored
+dtype may feed a target dtype when they are equal, when float32 is narrowed to
+bfloat16 (the deliberate downcast, ``model_loader/validate.py:83-95``), or when
+bfloat16 / float16 is widened to float32 (exact; this is what lets the 32-bit
+engine read a bfloat16 checkpoint, which the reference would refuse).  Anything
+else (float16 read as bfloat16, float64 into anything) is listed as a wrong dtype:
+it would produce no shape complaint and wrong values.  A shard that holds
+tensors which its index does not list is reported too: they are unexpected.
 """
 
 from __future__ import annotations
@@ -23,10 +28,20 @@ from typing import Protocol
 
 import torch
 
-from .safetensors import CheckpointCorruptError, SafetensorsFile
+from .safetensors import CheckpointCorruptError, SafetensorsFile, UnsupportedWeightFormatError  # noqa: F401
 
-_FLOATS = (torch.float64, torch.float32, torch.float16, torch.bfloat16)
 _INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8)
+
+
+def dtype_feeds(stored: torch.dtype, target: torch.dtype) -> bool:
+    """Whether a stored floating dtype may be converted into ``target``."""
+    if stored == target:
+        return True
+    if target == torch.bfloat16:
+        return stored == torch.float32                       # narrowing, on purpose
+    if target == torch.float32:
+        return stored in (torch.bfloat16, torch.float16)     # widening, exact
+    return False
 
 
 class WeightMismatchError(ValueError):
@@ -77,6 +92,14 @@ class FolderStore:
                 if name not in opened[shard].entries:
                     raise CheckpointCorruptError(f"{index}: {name!r} is not in shard {shard}")
                 self.where[name] = opened[shard]
+            # Tensors that a shard holds but the index does not list are offered all the same, so
+            # that the check against the model reports them as unexpected instead of passing over them.
+            for shard, f in opened.items():
+                for name in f.entries:
+                    if name not in self.where:
+                        self.where[name] = f
+                    elif self.where[name] is not f:
+                        raise CheckpointCorruptError(f"{index}: {name!r} is stored in more than one shard")
         else:
             single = folder / "model.safetensors"
             if not single.is_file():
@@ -160,11 +183,13 @@ def load_weights(model, store: TensorStore, normalize_name=None, config=None) ->
             wrong.append(f"{src.name}: a transposed source must be a matrix")
         elif tuple(shape) != expect:
             wrong.append(f"{src.name}: shape {tuple(shape)}, the model expects {expect}")
+        target = _target_dtype(row.decl.kind, model.dtype)
         if row.decl.kind == "int":
             if dtype not in _INTS:
                 wrong.append(f"{src.name}: dtype {dtype}, the model expects an integer table")
-        elif dtype not in _FLOATS:
-            wrong.append(f"{src.name}: dtype {dtype}, the model expects floating point")
+        elif not dtype_feeds(dtype, target):
+            wrong.append(f"{src.name}: dtype {dtype} cannot feed {target} (allowed: the same dtype, "
+                         f"float32 -> bfloat16, bfloat16 or float16 -> float32)")
     unexpected = sorted(name for name in offered if name not in used)
     if missing or unexpected or wrong:
         raise WeightMismatchError(sorted(missing), unexpected, wrong)

@@ -37,6 +37,17 @@ class CheckpointCorruptError(ValueError):
     """The file is not a well-formed safetensors file."""
 
 
+class UnsupportedWeightFormatError(ValueError):
+    """The file is well formed but stores tensors in a format this engine has
+    no path for: sub-byte and 8-bit float dtypes (packed or quantized weights).
+    A refusal rather than a silent reinterpretation (``exceptions.py:53-60``,
+    ``model_loader/st.py:98-131`` in the reference)."""
+
+
+# dtype tokens of the safetensors format that are known but not readable here
+_UNSUPPORTED_TOKENS = {"I4", "U4", "F4", "F6_E2M3", "F6_E3M2", "F8_E4M3", "F8_E5M2", "F8_E8M0"}
+
+
 @dataclass(frozen=True)
 class TensorEntry:
     name: str
@@ -91,7 +102,11 @@ class SafetensorsFile:
             if not isinstance(info, dict) or not {"dtype", "shape", "data_offsets"} <= set(info):
                 raise CheckpointCorruptError(f"{self.path}: entry {name!r} lacks dtype, shape or data_offsets")
             token = info["dtype"]
-            if token not in _ITEMSIZE:
+            if isinstance(token, str) and token in _UNSUPPORTED_TOKENS:
+                raise UnsupportedWeightFormatError(
+                    f"{self.path}: entry {name!r} is stored as {token}: packed and quantized weight formats "
+                    f"are not supported (readable: {sorted(_ITEMSIZE)})")
+            if not isinstance(token, str) or token not in _ITEMSIZE:
                 raise CheckpointCorruptError(f"{self.path}: entry {name!r} has unsupported dtype {token!r}")
             shape = info["shape"]
             if not isinstance(shape, list) or any(isinstance(s, bool) or not isinstance(s, int) or s < 0 for s in shape):

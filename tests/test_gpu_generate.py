@@ -193,3 +193,63 @@ def test_lookahead_gives_the_same_tokens(model_folders, graph):
     assert none_ahead == 0 and some_ahead > 10
     assert got == want
     assert want["r0"][1] == "stop" and len(want["r0"][0]) <= 14
+
+
+@pytest.mark.parametrize("graph", [False, True], ids=["eager", "graphs"])
+def test_stop_ids_are_banned_until_min_tokens(model_folders, graph):
+    """``request/stream.py:130-163``: before ``min_tokens`` the stop ids are masked out of the
+    logits (the request produces the best token that is not banned), afterwards the first stop
+    id ends it.  Greedy, so every token can be checked against the plain model's logits."""
+    from ayaka_py_b200 import LLM, SamplingParams, StopCriteria
+    folder, cfg, weights = model_folders["A"]
+    prompt = tiny_models.prompts(cfg, [14], seed=41)[0]
+    free = plain_gpt2.greedy_generate(cfg, weights, prompt, 12)
+    banned = (free[0], free[2], free[5])
+    llm = LLM(folder, dtype="float32", page_size=16, kv_pages=32, decode_graph=graph)
+    out = llm.generate([prompt, prompt], SamplingParams(temperature=0.0),
+                       [StopCriteria(max_tokens=12, min_tokens=7, stop_token_ids=banned),
+                        StopCriteria(max_tokens=12, min_tokens=0, stop_token_ids=(free[2],))])
+    got = out[0].token_ids
+    assert not set(got[:7]) & set(banned) and got[0] != free[0]
+    logits = plain_gpt2.forward(cfg, weights, prompt + got)
+    for j, token in enumerate(got):
+        row = logits[len(prompt) - 1 + j].copy()
+        if j < 7:
+            row[list(banned)] = -np.inf
+        assert token == int(row.argmax()), (j, token)
+    assert out[0].finish_reason in ("stop", "length") and (out[0].finish_reason == "length" or got[-1] in banned)
+    first = free.index(free[2])                           # no min_tokens: stops at the id's first appearance
+    assert out[1].token_ids == free[:first + 1] and out[1].finish_reason == "stop"
+    llm.engine.cache.assert_clean()
+
+
+def test_abort_with_a_step_in_flight(model_folders):
+    """``Engine.abort`` while a looked-ahead decode step runs: the step is brought to its end first,
+    the request leaves with what it has, the others go on, and every page comes back."""
+    from ayaka_py_b200 import EngineConfig, Request, SamplingParams, StopCriteria
+    from ayaka_py_b200.engine.engine import Engine
+    from ayaka_py_b200.engine.loading import load_model
+    folder, cfg, weights = model_folders["A"]
+    prompts = tiny_models.prompts(cfg, [9, 21, 5], seed=43)
+    _, model = load_model(folder, "float32", "cuda")
+    engine = Engine(model, EngineConfig(dtype="float32", page_size=16, kv_pages=32, max_requests=2, lookahead=True),
+                    eos_token_id=None)
+    def submit(i):
+        engine.submit(Request(f"r{i}", prompts[i], SamplingParams(temperature=0.0), StopCriteria(max_tokens=20, ignore_eos=True)))
+
+    submit(0)
+    submit(1)
+    for _ in range(6):
+        engine.step()
+    assert engine._inflight is not None                 # a step is on the GPU whose tokens nobody has seen
+    submit(2)                                           # both slots are taken: it waits
+    engine.abort("r2")                                  # waiting: never ran
+    engine.abort("r0")                                  # running, with the step in flight
+    assert engine._inflight is None
+    assert engine.finished["r0"].finish_reason == "abort" and engine.finished["r2"].token_ids == []
+    kept = engine.finished["r0"].token_ids
+    assert 5 <= len(kept) <= 8 and kept == plain_gpt2.greedy_generate(cfg, weights, prompts[0], len(kept))
+    engine.cache.check_invariants()
+    done = engine.run_until_idle()
+    assert done["r1"].token_ids == plain_gpt2.greedy_generate(cfg, weights, prompts[1], 20)
+    engine.cache.assert_clean()

@@ -200,3 +200,134 @@ def test_xl_layer_sizes(dtype, tmp_path):
         session.cache.assert_clean()
         bad = trace_tools.first_difference(trace_tools.collect(trace, outputs), want, tolerance(dtype, want))
         assert bad is None, f"first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"
+
+
+@pytest.fixture(scope="module")
+def xl_full_depth(tmp_path_factory):
+    """All 48 layers of the XL shape, random weights, and the plain implementation's logits for two requests."""
+    import plain_gpt2
+    from ayaka_py_b200 import GPT2Config
+    from ayaka_py_b200.weights import write_random_model
+
+    folder = tmp_path_factory.mktemp("xl48") / "model"
+    write_random_model(str(folder), GPT2Config(vocab_size=50257, n_positions=1024, n_embd=1600, n_layer=48, n_head=25,
+                                               n_inner=6400), seed=7)
+    cfg, weights = plain_gpt2.read_model_folder(folder)
+    rs = np.random.RandomState(3)
+    reqs = {f"x{i}": [int(t) for t in rs.randint(0, 50257, size=n)] for i, n in enumerate([200, 33])}
+    want = trace_tools.oracle(cfg, weights, reqs)
+    del weights
+    return folder, reqs, want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_xl_full_depth(dtype, xl_full_depth):
+    """The benchmark's model at its full depth: two requests replayed mixed and with decoded tails.
+    The 32-bit path stays within 1e-4 of the plain implementation through 48 layers; bfloat16 within
+    its rounding (the largest logit is about 4.5)."""
+    import torch
+    from ayaka_py_b200.replay import ReplaySession
+    folder, reqs, want = xl_full_depth
+    worst = 0.0
+    for trace in (trace_tools.mixed(reqs, seed=1), trace_tools.tail_decoded(reqs, 32)):
+        session = ReplaySession(str(folder), dtype, trace_tools.tokens_needed(trace), 16)
+        outputs = []
+        for record in trace:
+            logits = session.step(record)
+            outputs.append(None if logits is None or logits.shape[0] == 0 else logits.cpu().numpy())
+        session.cache.assert_clean()
+        got = trace_tools.collect(trace, outputs)
+        limit = 1e-4 if dtype == "float32" else tolerance(dtype, want)
+        bad = trace_tools.first_difference(got, want, limit)
+        assert bad is None, f"first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"
+        worst = max(worst, max(float(np.abs(got[r][p] - want[r][p]).max()) for r in want for p in range(want[r].shape[0])))
+        del session
+        torch.cuda.empty_cache()
+    print(f"XL, 48 layers, {dtype}: largest |logit difference| {worst:.3e}")
+
+
+def reference_schedule():
+    """The schedule that the reference's own continuous scheduler made on tiny B with 40 pages of 8
+    (``tests/golden/make_reference_trace.py``), as replay records, with the reference's logits per step."""
+    stored = np.load(ROOT / "tests" / "golden" / "reference_paged_trace.npz")
+    lengths = stored["prompt_lengths"].tolist()
+    flat, prompts = stored["prompts"].tolist(), []
+    for n in lengths:
+        prompts.append(flat[:n])
+        flat = flat[n:]
+    known = [p + g for p, g in zip(prompts, stored["generated"].tolist())]
+    slices = stored["slices"]
+    steps, rows_of = [], []
+    held: dict[int, int] = {}
+    for index in range(int(slices[:, 0].max()) + 1):
+        entries, rows = [], 0
+        for _, r, start, count, sample in slices[slices[:, 0] == index].tolist():
+            if start == 0 and held.get(r, 0) > 0:              # preempted: it was dropped after its last step
+                for earlier in reversed(steps):
+                    if any(e["id"] == f"r{r}" for e in earlier["entries"]):
+                        earlier["end"].append(f"r{r}")
+                        break
+            assert start == (0 if start == 0 else held[r])
+            held[r] = start + count
+            entries.append({"id": f"r{r}", "tokens": known[r][start:start + count], "want": [count - 1] if sample else []})
+            rows += sample
+        steps.append({"step": index, "entries": entries, "end": []})
+        rows_of.append(rows)
+    for r, toks in enumerate(known):                            # finished: the last token is sampled, never fed
+        for earlier in reversed(steps):
+            if any(e["id"] == f"r{r}" for e in earlier["entries"]):
+                earlier["end"].append(f"r{r}")
+                break
+    logits, at = [], 0
+    for rows in rows_of:
+        logits.append(stored["logits"][at:at + rows])
+        at += rows
+    geometry = dict(zip(("pages", "page_size", "budget", "chunk", "new_tokens"), stored["geometry"].tolist()))
+    return steps, logits, geometry
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_of_the_reference_scheduler_with_its_paged_logits(dtype, model_folders):
+    """Trace family 5: what the reference's scheduler did under page pressure (portions of 24 beside
+    decoded tokens, one recompute preemption), replayed here step by step with as many pages as the
+    reference had; this engine's logits against the logits of the reference's *paged* path."""
+    from ayaka_py_b200.replay import ReplaySession
+    folder, cfg, _ = model_folders["B"]
+    steps, want, geometry = reference_schedule()
+    assert any(len(s["entries"]) > 1 and {len(e["tokens"]) for e in s["entries"]} != {1} for s in steps)   # mixed steps
+    assert sum(len(s["end"]) for s in steps) == 6                                   # five finishes and a preemption
+    session = ReplaySession(str(folder), dtype, (geometry["pages"] - 1) * geometry["page_size"], geometry["page_size"])
+    limit = 1e-4 if dtype == "float32" else 0.02 * float(np.abs(np.concatenate(want)).max())
+    for record, expect in zip(steps, want):
+        logits = session.step(record)
+        got = np.zeros((0, expect.shape[1]), np.float32) if logits is None else logits.cpu().numpy()
+        assert got.shape == expect.shape, record["step"]
+        if len(expect):
+            worst = float(np.abs(got - expect).max())
+            assert worst <= limit, f"step {record['step']}: |diff| {worst:.3e}"
+    session.cache.assert_clean()
+    assert session.cache.stats()["groups"]["group0"]["reused"] > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "D"])
+def test_request_dropped_midway_and_reopened(tag, dtype, model_folders, oracles):
+    """Trace family 6: a request is ended after 45 % of its tokens, its pages go to others, and its id
+    starts over from token 0 (what a recompute preemption does); both lives against the plain logits."""
+    folder, cfg, _ = model_folders[tag]
+    reqs, want = oracles[tag]
+    picked = dict(list(reqs.items())[-3:])
+    trace = trace_tools.reopened(picked, seed=5)
+    needed = trace_tools.tokens_needed(trace)
+    outputs, session = replay(folder, dtype, trace, PAGE[tag], max_tokens=needed)
+    assert session.cache.stats()["groups"]["group0"]["reused"] > 0
+    got = trace_tools.collect(trace, outputs, lives=True)
+    first = next(iter(picked))
+    expect = {f"{rid}#0": want[rid] for rid in picked if rid != first}
+    expect[f"{first}#1"] = want[first]
+    bad = trace_tools.first_difference(got, expect, tolerance(dtype, want))
+    assert bad is None, f"first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"
+    early = {f"{first}#0": want[first]}
+    assert len(got[f"{first}#0"]) == max(2, int(len(picked[first]) * 0.45))
+    bad = trace_tools.first_difference(got, early, tolerance(dtype, want), partial=(f"{first}#0",))
+    assert bad is None, f"first life: position {bad[1]} |diff| {bad[2]:.3e}"

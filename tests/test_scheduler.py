@@ -79,10 +79,20 @@ def test_stop_rules():
     sched.add(req(0, 3, max_tokens=10, stop_token_ids=(5,), min_tokens=3))
     sched.add(req(1, 3, max_tokens=10))
     sched.add(req(2, 3, max_tokens=10, ignore_eos=True))
-    tokens = {"r0": iter([5, 5, 5, 5]), "r1": iter([1, 9]), "r2": iter([9] * 10)}
-    done = drive(sched, cache, token=lambda s: next(tokens[s.request.request_id]))
+    # The sampler bans r0's stop id for its first min_tokens tokens (the fake model here obeys the ban);
+    # the first token that may be a stop is number min_tokens + 1 (request/stream.py:130-163).
+    assert sched.banned_tokens(sched.states["r0"]) == (5, 9) and sched.banned_tokens(sched.states["r1"]) == ()
+    assert sched.banned_tokens(sched.states["r0"], pending=3) == ()
+    tokens = {"r0": iter([1, 1, 1, 5, 5]), "r1": iter([1, 9]), "r2": iter([9] * 10)}
+
+    def fake(s):
+        token = next(tokens[s.request.request_id])
+        assert token not in sched.banned_tokens(s)
+        return token
+
+    done = drive(sched, cache, token=fake)
     by = {s.request.request_id: s for s in done}
-    assert by["r0"].finish_reason == "stop" and by["r0"].generated == 3      # not before min_tokens
+    assert by["r0"].finish_reason == "stop" and by["r0"].generated == 4      # not before min_tokens
     assert by["r1"].finish_reason == "eos" and by["r1"].generated == 2
     assert by["r2"].finish_reason == "length" and by["r2"].generated == 10
 
@@ -317,3 +327,79 @@ def test_two_recomputing_prompts_that_fill_the_pool():
     done = drive(sched, cache)
     assert sorted(s.request.request_id for s in done) == ["r0", "r1"]
     assert sched.stats.preemptions > 0
+
+
+def test_more_decoders_than_the_token_budget_take_turns():
+    """The cursor branch of decode-first: with more decoding requests than the step's token
+    budget every request advances, nobody starves, and the turns differ by at most one."""
+    sched, cache = make(pages=129, page_size=4, max_requests=12, batch_tokens=5, prefill_chunk=5, max_len=64)
+    for i in range(12):
+        sched.add(req(i, 2, max_tokens=9))
+    log = []
+    done = drive(sched, cache, log=log)
+    assert len(done) == 12 and all(s.generated == 9 and s.finish_reason == "length" for s in done)
+    decode_steps = [step for step in log if all(start > 0 and count == 1 for _, start, count, _ in step)]
+    crowded = [step for step in decode_steps if len(step) == 5]
+    assert len(crowded) >= 10                                   # the budget, not the request count, bounded them
+    turns = {f"r{i}": 0 for i in range(12)}
+    spread = 0
+    for step in log:
+        assert sum(c for _, _, c, _ in step) <= 5
+        for rid, start, count, _ in step:
+            if start > 0:
+                turns[rid] += 1
+        live = [turns[r] for r in turns if turns[r] < 8]       # requests that still decode
+        if len(live) > 5 and min(turns.values()) > 0:
+            spread = max(spread, max(live) - min(live))
+    assert spread <= 2, spread                                  # round robin: nobody runs ahead of the others
+
+
+def test_abort_of_waiting_and_running_requests():
+    sched, cache = make(pages=33, page_size=4, max_requests=2, batch_tokens=16, prefill_chunk=16)
+    for i in range(4):
+        sched.add(req(i, 6, max_tokens=8))
+    plan = sched.schedule()                                     # r0, r1 run; r2, r3 wait (two slots)
+    assert [e.state.request.request_id for e in plan.entries] == ["r0", "r1"]
+    with pytest.raises(RuntimeError):
+        sched.abort("r0")                                       # inside a reserved step
+    sched.update(plan, {"r0": 7, "r1": 7})
+    gone = sched.abort("r3")                                    # a waiting request: no slot, no pages
+    assert gone.finish_reason == "abort" and gone.slot is None and "r3" not in sched.states
+    held = cache.stats()["groups"]["g"]["free"]
+    gone = sched.abort("r0")                                    # a running request: its pages and slot return
+    assert gone.finish_reason == "abort" and sched.result_of(gone).token_ids == [7]
+    assert cache.stats()["groups"]["g"]["free"] > held and len(cache.free_slots) == 1
+    assert sched.abort("r0") is None and sched.abort("nobody") is None
+    cache.check_invariants()
+    done = drive(sched, cache)
+    assert sorted(s.request.request_id for s in done) == ["r1", "r2"]
+
+
+def test_lookahead_needs_pages_and_a_plain_decode_step():
+    # 6 usable pages of 4 tokens; two requests of 7 tokens: the next token of each needs no page, the one after does
+    sched, cache = make(pages=7, page_size=4, max_requests=2, batch_tokens=16, prefill_chunk=16, max_len=32)
+    sched.add(req(0, 7, max_tokens=12))
+    sched.add(req(1, 7, max_tokens=12))
+    plan = sched.schedule()
+    assert not plan.decode_only and sched.lookahead(plan) is None            # a prompt step is never looked past
+    sched.update(plan, {"r0": 1, "r1": 1})
+    plan = sched.schedule()                                                   # decode at position 7: the pages exist
+    assert plan.decode_only
+    sched.advance(plan)
+    ahead = sched.lookahead(plan)                                             # position 8 needs a page each: 2 are free
+    assert ahead is not None and [e.start for e in ahead.entries] == [8, 8]
+    sched.resolve(plan, {"r0": 1, "r1": 1})
+    sched.advance(ahead)
+    sched.resolve(ahead, {"r0": 1, "r1": 1})
+    for _ in range(2):                                                        # positions 9 and 10: no new page
+        plan = sched.schedule()
+        sched.update(plan, {"r0": 1, "r1": 1})
+    plan = sched.schedule()                                                   # position 11 is the last of page 2
+    assert plan is not None
+    sched.advance(plan)
+    free_before = cache.free_pages(0)
+    assert free_before == 0
+    assert sched.lookahead(plan) is None                                      # position 12 needs pages that are not there
+    assert cache.free_pages(0) == free_before                                 # and the refusal changed nothing
+    cache.check_invariants()
+    sched.resolve(plan, {"r0": 1, "r1": 1})

@@ -9,8 +9,8 @@ import plain_gpt2
 import tiny_models
 from ayaka_py_b200.config import GPT2Config
 from ayaka_py_b200.engine.loading import load_model, random_model
-from ayaka_py_b200.weights import (CheckpointCorruptError, SafetensorsFile, WeightMismatchError,
-                                   write_random_model, write_safetensors)
+from ayaka_py_b200.weights import (CheckpointCorruptError, SafetensorsFile, UnsupportedWeightFormatError,
+                                   WeightMismatchError, write_random_model, write_safetensors)
 
 
 def test_loads_by_name_with_conv1d_layout(model_folders):
@@ -33,7 +33,7 @@ def _rewrite(folder, tmp_path, change):
                plain_gpt2.read_safetensors(folder / "model.safetensors").items()}
     change(tensors)
     out = tmp_path / "changed"
-    out.mkdir()
+    out.mkdir(parents=True)
     (out / "config.json").write_text((folder / "config.json").read_text())
     write_safetensors(out / "model.safetensors", tensors)
     return out
@@ -99,7 +99,7 @@ def test_corrupt_files(tmp_path, damage):
         if damage == "duplicate":
             text = '{"a": {"dtype":"F32","shape":[1],"data_offsets":[0,4]}, "a": {"dtype":"F32","shape":[1],"data_offsets":[4,8]}}'
         if damage == "dtype":
-            text = text.replace('"F32", "shape": [2]', '"F4", "shape": [2]')
+            text = text.replace('"F32", "shape": [2]', '"F7", "shape": [2]')
         if damage == "offsets":
             text = text.replace("[8, 12]", "[8, 16]")
         if damage == "bytes":
@@ -111,6 +111,101 @@ def test_corrupt_files(tmp_path, damage):
         path.write_bytes(struct.pack("<Q", length) + raw + payload)
     with pytest.raises(CheckpointCorruptError):
         SafetensorsFile(path)
+
+
+@pytest.mark.parametrize("token", ["F4", "I4", "U4", "F8_E4M3", "F8_E5M2"])
+def test_packed_and_quantized_dtypes_are_refused_as_unsupported(tmp_path, token):
+    """``model_loader/st.py:98-131``: a known sub-byte or 8-bit float dtype is not a corrupt file."""
+    path = tmp_path / "model.safetensors"
+    raw = json.dumps({"w": {"dtype": token, "shape": [4], "data_offsets": [0, 4]}}).encode()
+    path.write_bytes(struct.pack("<Q", len(raw)) + raw + b"\0" * 4)
+    with pytest.raises(UnsupportedWeightFormatError) as err:
+        SafetensorsFile(path)
+    assert token in str(err.value) and not isinstance(err.value, CheckpointCorruptError)
+
+
+def test_dtype_rule_narrowing_and_widening(model_folders, tmp_path):
+    """``model_loader/validate.py:83-95``: float32 -> bfloat16 is the one narrowing; float16 read
+    as bfloat16 and float64 into anything are listed as wrong, together, in the one error."""
+    folder, cfg, weights = model_folders["A"]
+
+    def change(t):
+        t["transformer.h.0.mlp.c_fc.weight"] = t["transformer.h.0.mlp.c_fc.weight"].to(torch.float16)
+        t["transformer.h.1.attn.c_proj.weight"] = t["transformer.h.1.attn.c_proj.weight"].to(torch.float64)
+        t["transformer.ln_f.bias"] = t["transformer.ln_f.bias"].to(torch.float64)
+
+    changed = _rewrite(folder, tmp_path, change)
+    with pytest.raises(WeightMismatchError) as err:
+        load_model(changed, "bfloat16", "cpu")
+    wrong = "\n".join(err.value.wrong)
+    assert len(err.value.wrong) == 3 and not err.value.missing and not err.value.unexpected
+    assert "c_fc.weight: dtype torch.float16 cannot feed torch.bfloat16" in wrong
+    assert "attn.c_proj.weight: dtype torch.float64" in wrong and "ln_f.bias: dtype torch.float64" in wrong
+    with pytest.raises(WeightMismatchError) as err:              # 32-bit engine: float16 widens, float64 does not
+        load_model(changed, "float32", "cpu")
+    assert len(err.value.wrong) == 2 and all("float64" in w for w in err.value.wrong)
+    # float32 stored -> bfloat16 engine (narrowing) and bfloat16 stored -> float32 engine (widening) load
+    _, narrow = load_model(folder, "bfloat16", "cpu")
+    assert narrow.blocks[0].ffn.up_weight.dtype == torch.bfloat16
+    bf = _rewrite(folder, tmp_path / "bf", lambda t: t.update(
+        {k: v.to(torch.bfloat16) for k, v in t.items() if k.endswith("c_fc.weight")}))
+    _, wide = load_model(bf, "float32", "cpu")
+    assert wide.blocks[0].ffn.up_weight.dtype == torch.float32
+
+
+def _shard(folder, out, split, index_names=None):
+    """Writes ``folder``'s tensors as two shards with an index; ``index_names`` limits what the index lists."""
+    tensors = {k: torch.from_numpy(v.copy()) for k, v in
+               plain_gpt2.read_safetensors(folder / "model.safetensors").items()}
+    names = sorted(tensors)
+    parts = {"model-00001-of-00002.safetensors": names[:split], "model-00002-of-00002.safetensors": names[split:]}
+    out.mkdir(parents=True)
+    (out / "config.json").write_text((folder / "config.json").read_text())
+    weight_map = {}
+    for shard, members in parts.items():
+        write_safetensors(out / shard, {n: tensors[n] for n in members})
+        weight_map.update({n: shard for n in members if index_names is None or n in index_names})
+    (out / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    return out, tensors
+
+
+def test_sharded_folder_loads_and_reports_what_the_index_omits(model_folders, tmp_path):
+    folder, cfg, weights = model_folders["B"]
+    out, tensors = _shard(folder, tmp_path / "sharded", split=11)
+    _, model = load_model(out, "float32", "cpu")
+    assert np.array_equal(model.blocks[2].ffn.down_weight.numpy(), weights["transformer.h.2.mlp.c_proj.weight"].T)
+    assert np.array_equal(model.embedding.weight.numpy(), weights["transformer.wte.weight"])
+    # a shard holds a tensor that the index does not list and the model does not want: unexpected, not ignored
+    extra = tmp_path / "extra"
+    listed = set(tensors)
+    out2, _ = _shard(folder, extra, split=11, index_names=listed)
+    first = extra / "model-00001-of-00002.safetensors"
+    kept = {k: torch.from_numpy(v.copy()) for k, v in plain_gpt2.read_safetensors(first).items()}
+    kept["transformer.h.9.stray.weight"] = torch.zeros(2, 2)
+    write_safetensors(first, kept)
+    with pytest.raises(WeightMismatchError) as err:
+        load_model(out2, "float32", "cpu")
+    assert err.value.unexpected == ["transformer.h.9.stray.weight"] and not err.value.missing
+    # a tensor the model wants lies in a shard although the index forgot it: it is found
+    partial = tmp_path / "partial"
+    out3, _ = _shard(folder, partial, split=11, index_names=listed - {"transformer.ln_f.weight"})
+    _, model3 = load_model(out3, "float32", "cpu")
+    assert np.array_equal(model3.final_norm.weight.numpy(), weights["transformer.ln_f.weight"])
+
+
+def test_untied_head_is_loaded_and_used(model_folders, tmp_path):
+    folder, cfg, weights = model_folders["A"]
+    head = np.random.RandomState(3).standard_normal(weights["transformer.wte.weight"].shape).astype(np.float32) * 0.05
+
+    out = _rewrite(folder, tmp_path, lambda t: t.update({"lm_head.weight": torch.from_numpy(head.copy())}))
+    (out / "config.json").write_text(json.dumps({**cfg, "tie_word_embeddings": False}))
+    _, model = load_model(out, "float32", "cpu")
+    assert model.head.weight.data_ptr() != model.embedding.weight.data_ptr()
+    assert np.array_equal(model.head.weight.numpy(), head)
+    config, tensors = plain_gpt2.read_model_folder(out)
+    logits = plain_gpt2.forward(config, tensors, [5, 6, 7])
+    tied = plain_gpt2.forward(*plain_gpt2.read_model_folder(folder), [5, 6, 7])
+    assert np.abs(logits - tied).max() > 1e-3                    # the plain implementation uses the head it is given
 
 
 def test_random_mode_writes_a_loadable_folder(tmp_path):

@@ -80,16 +80,58 @@ class _PagePool:
         self.free.append(page)
 
 
+def pages_for_budget(groups: list[CacheGroupSpec], budget_bytes: int, *, page_size: int, max_requests: int,
+                     max_len: int, step_tokens: int, dtype: torch.dtype) -> list[int]:
+    """Pages per group (the padding page included; 0 for state groups) out of one byte
+    budget.  A group whose layers read a window never holds more than the window plus
+    one step's tokens per request, so it gets at most that; what remains is shared by
+    the groups that keep every key so that each holds the same number of tokens (a
+    request needs its tokens in all of them at once)."""
+    item = torch.empty((), dtype=dtype).element_size()
+    cost = [g.layers * page_size * g.need.elements_per_token() * item if isinstance(g.need, KVNeed) else 0
+            for g in groups]
+    pages = [0] * len(groups)
+    left = int(budget_bytes)
+    full = [i for i, g in enumerate(groups) if isinstance(g.need, KVNeed) and g.need.window is None]
+    windowed = [i for i, g in enumerate(groups) if isinstance(g.need, KVNeed) and g.need.window is not None]
+    per_token_page = sum(cost[i] for i in full + windowed)
+    if not per_token_page:
+        return pages
+    even = left // per_token_page                       # pages each group would get if all were alike
+    for i in windowed:
+        per_request = -(-(min(max_len, groups[i].need.window + step_tokens)) // page_size) + 1
+        pages[i] = max(2, min(even, max_requests * per_request + 1))
+        left -= pages[i] * cost[i]
+    if full:
+        share = left // sum(cost[i] for i in full)
+        for i in full:
+            pages[i] = max(0, share)
+    short = [groups[i].name for i in full + windowed if pages[i] < 2]
+    if short:
+        raise ValueError(f"a budget of {budget_bytes} bytes leaves no page for cache group(s) {short} "
+                         f"(a page of each costs {[cost[i] for i in full + windowed]} bytes)")
+    return pages
+
+
 class CacheManager:
-    def __init__(self, groups: list[CacheGroupSpec], *, kv_pages: int, page_size: int,
+    def __init__(self, groups: list[CacheGroupSpec], *, kv_pages, page_size: int,
                  max_requests: int, max_len: int, dtype: torch.dtype = torch.float32,
                  device=None):
-        """``device`` None: bookkeeping only (no tensors), for host tests."""
+        """``kv_pages``: pages of every KV group (one number), or one number per group
+        (see ``pages_for_budget``); the padding page counts.  ``device`` None: bookkeeping
+        only (no tensors), for host tests."""
         if page_size < 1 or page_size & (page_size - 1):
             raise ValueError("page_size must be a power of two")
         self.groups = list(groups)
         self.page_size = page_size
-        self.kv_pages = kv_pages
+        if isinstance(kv_pages, int):
+            per_group = [kv_pages if isinstance(g.need, KVNeed) else 0 for g in self.groups]
+        else:
+            per_group = [int(n) for n in kv_pages]
+            if len(per_group) != len(self.groups):
+                raise ValueError(f"{len(per_group)} page counts for {len(self.groups)} cache groups")
+        self.pages_of = per_group                       # pages of each group (0: a state group)
+        self.kv_pages = min((n for n, g in zip(per_group, self.groups) if isinstance(g.need, KVNeed)), default=0)
         self.max_requests = max_requests
         self.max_len = max_len
         self.columns = -(-max_len // page_size)
@@ -107,18 +149,20 @@ class CacheManager:
         self.num_pages: list[np.ndarray | None] = []    # logical pages ever assigned (= next logical index)
         self.kv: list[torch.Tensor | None] = []
         self.state: list[torch.Tensor | None] = []
-        for g in self.groups:
+        for g, n_pages in zip(self.groups, per_group):
             if isinstance(g.need, KVNeed):
-                self.pools.append(_PagePool(kv_pages))
+                if n_pages < 2:
+                    raise ValueError(f"cache group {g.name!r} needs at least 2 pages (one is the padding page)")
+                self.pools.append(_PagePool(n_pages))
                 self.tables.append(np.zeros((max_requests, self.columns), dtype=np.int32))
                 self.first_page.append(np.zeros(max_requests, dtype=np.int64))
                 self.num_pages.append(np.zeros(max_requests, dtype=np.int64))
                 self.state.append(None)
                 if device is not None:
-                    # [layer, K|V, page, token in page, kv head, head dim]
-                    self.kv.append(torch.zeros(
-                        (g.layers, 2, kv_pages, page_size, g.need.kv_heads, g.need.head_dim),
-                        dtype=dtype, device=device))
+                    # keys [layer, page, token in page, kv head, head dim]; values the same with their own heads and size
+                    self.kv.append((
+                        torch.zeros((g.layers, n_pages, page_size, g.need.kv_heads, g.need.head_dim), dtype=dtype, device=device),
+                        torch.zeros((g.layers, n_pages, page_size, g.need.v_heads, g.need.v_dim), dtype=dtype, device=device)))
                 else:
                     self.kv.append(None)
             elif isinstance(g.need, StateNeed):
@@ -286,9 +330,10 @@ class CacheManager:
         return self.tables[g][np.asarray(slots, dtype=np.int64)]
 
     def kv_layer(self, g: int, layer: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """(K, V) pages of one layer: each [pages, page_size, kv_heads, head_dim]."""
-        slab = self.kv[g]
-        return slab[layer, 0], slab[layer, 1]
+        """(K, V) pages of one layer: [pages, page_size, kv_heads, head_dim] and the same with the
+        values' heads and size."""
+        keys, values = self.kv[g]
+        return keys[layer], values[layer]
 
     def state_layer(self, g: int, layer: int) -> torch.Tensor:
         """State of one layer: [max_requests + 1, *shape], indexed by slot (the last is a spare)."""
@@ -299,7 +344,7 @@ class CacheManager:
         item = torch.empty((), dtype=self.dtype).element_size()
         for g in self.groups:
             if isinstance(g.need, KVNeed):
-                total += 2 * g.layers * g.need.kv_heads * g.need.head_dim * item
+                total += g.layers * g.need.elements_per_token() * item
         return total
 
     # ---------------------------------------------------------- diagnostics --

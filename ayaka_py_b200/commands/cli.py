@@ -30,13 +30,15 @@ PRESETS = {
 def _add_engine_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--dtype", choices=("float32", "bfloat16"), default="bfloat16")
     p.add_argument("--kv-pages", type=int, default=1024)
+    p.add_argument("--kv-cache-bytes", type=int, default=None,
+                   help="instead of --kv-pages: a byte budget for the whole cache, split over the cache groups")
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--max-requests", type=int, default=32)
     p.add_argument("--max-model-len", type=int, default=None)
     p.add_argument("--batch-tokens", type=int, default=256)
     p.add_argument("--prefill-chunk", type=int, default=128)
-    p.add_argument("--decode-graph", action="store_true", default=False,
-                   help="replay pure-decode steps from CUDA graphs")
+    p.add_argument("--decode-graph", action=argparse.BooleanOptionalAction, default=True,
+                   help="replay pure-decode steps from CUDA graphs (on by default; --no-decode-graph launches every kernel)")
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -83,7 +85,7 @@ def _generate(args) -> int:
     if not (args.model_path / "config.json").is_file():
         print(f"model_path does not contain config.json: {args.model_path}", file=sys.stderr)
         return 2
-    config = EngineConfig(dtype=args.dtype, kv_pages=args.kv_pages, page_size=args.page_size,
+    config = EngineConfig(dtype=args.dtype, kv_pages=args.kv_pages, kv_cache_bytes=args.kv_cache_bytes, page_size=args.page_size,
                           max_requests=args.max_requests, max_model_len=args.max_model_len,
                           batch_tokens=args.batch_tokens, prefill_chunk=args.prefill_chunk,
                           decode_graph=args.decode_graph)

@@ -17,12 +17,13 @@ _DTYPES = {"float32": "float32", "fp32": "float32", "bfloat16": "bfloat16", "bf1
 class EngineConfig:
     dtype: str = "bfloat16"
     kv_pages: int = 1024          # pages per cache group, the padding page included
+    kv_cache_bytes: int | None = None   # instead of kv_pages: one byte budget, split over the groups by what a page of each costs
     page_size: int = 16           # tokens in a page
     max_requests: int = 32        # live requests = state slots
     batch_tokens: int = 256       # token budget of one step
     prefill_chunk: int = 128      # largest portion of one prompt in a step
     max_model_len: int | None = None   # None: the model's own limit
-    decode_graph: bool = False    # replay pure-decode steps from CUDA graphs
+    decode_graph: bool = True     # replay pure-decode steps from CUDA graphs (False: every kernel launched from Python)
     lookahead: bool = True        # plan and launch the next decode step while this one's tokens are on their way
     seed: int = 0                 # base of the seeds of requests that name none
 
@@ -38,5 +39,8 @@ class EngineConfig:
             raise ConfigError(f"page_size must be a power of two, got {self.page_size}")
         if self.kv_pages < 2:
             raise ConfigError("kv_pages must be at least 2 (one page is the padding page)")
+        if self.kv_cache_bytes is not None and (isinstance(self.kv_cache_bytes, bool) or not isinstance(self.kv_cache_bytes, int)
+                                                or self.kv_cache_bytes < 1):
+            raise ConfigError(f"kv_cache_bytes must be a positive integer or None, got {self.kv_cache_bytes!r}")
         if self.max_model_len is not None and self.max_model_len < 1:
             raise ConfigError("max_model_len must be positive")

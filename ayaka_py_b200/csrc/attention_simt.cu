@@ -50,16 +50,17 @@ attention_simt_kernel(T* __restrict__ out, const T* __restrict__ q, int q_stride
   const int pos0 = req_pos0[req] + q0;          // its absolute position
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ldk = Dh + 1;
+  const int ldq = (Dh + 3) & ~3;       // query rows start on 16-byte boundaries whatever the head size
 
   extern __shared__ float smem[];
-  float* Qs = smem;                    // [BQ][Dh]
-  float* Ks = Qs + BQ * Dh;            // [BKEYS][Dh + 1]
+  float* Qs = smem;                    // [BQ][ldq]
+  float* Ks = Qs + BQ * ldq;           // [BKEYS][Dh + 1]
   float* Vs = Ks + BKEYS * ldk;        // [BKEYS][Dh]
   float* Ps = Vs + BKEYS * Dh;         // [BQ][BKEYS]
 
   for (int i = threadIdx.x; i < BQ * Dh; i += blockDim.x) {
     int r = i / Dh, d = i - r * Dh;
-    Qs[i] = r < rows ? to_float<T>(q[(size_t)(row0 + r) * q_stride + h * Dh + d]) : 0.f;
+    Qs[r * ldq + d] = r < rows ? to_float<T>(q[(size_t)(row0 + r) * q_stride + h * Dh + d]) : 0.f;
   }
 
   const int NC = (Dh + 31) / 32;       // head-dim columns per lane
@@ -104,16 +105,18 @@ attention_simt_kernel(T* __restrict__ out, const T* __restrict__ q, int q_stride
       const int row = warp * RQ + r;      // warp-uniform
       if (row >= rows) break;
       const int qpos = pos0 + row;
-      const float* qr = Qs + row * Dh;
+      const float* qr = Qs + row * ldq;
       const float* kr = Ks + lane * ldk;
       float s = 0.f;
-      for (int d = 0; d < Dh; d += 4) {
+      int d = 0;
+      for (; d + 4 <= Dh; d += 4) {
         float4 qv = *reinterpret_cast<const float4*>(qr + d);
         s = fmaf(qv.x, kr[d], s);
         s = fmaf(qv.y, kr[d + 1], s);
         s = fmaf(qv.z, kr[d + 2], s);
         s = fmaf(qv.w, kr[d + 3], s);
       }
+      for (; d < Dh; ++d) s = fmaf(qr[d], kr[d], s);      // head sizes that are no multiple of 4
       bool valid = page_ok && kp <= qpos && (window <= 0 || kp > qpos - window);
       s = valid ? s * scale : -INFINITY;
       float m_new = fmaxf(m_run[r], warp_max(s));
@@ -174,11 +177,11 @@ AYK_EXPORT int ayk_attention_simt(void* out, const void* q, int q_stride, const 
                                   int total_rows, int H, int Hkv, int Dh, int page_size, float scale,
                                   int window, int dtype, cudaStream_t stream) {
   if (num_req == 0 || total_rows == 0) return 0;
-  AYK_REQUIRE(Dh >= 4 && Dh % 4 == 0 && Dh <= MAX_DH, "ayk_attention_simt: head size %d is not a multiple of 4 in [4, %d]", Dh, MAX_DH);
+  AYK_REQUIRE(Dh >= 1 && Dh <= MAX_DH, "ayk_attention_simt: head size %d is not in [1, %d]", Dh, MAX_DH);
   AYK_REQUIRE(Hkv >= 1 && H % Hkv == 0, "ayk_attention_simt: %d heads cannot share %d key/value heads", H, Hkv);
   AYK_REQUIRE(H <= 65535, "ayk_attention_simt: too many heads (%d)", H);
   int max_tiles = total_rows / BQ + num_req;   // sum of ceil(len / BQ) never exceeds this
-  size_t smem = ((size_t)BQ * Dh + (size_t)BKEYS * (Dh + 1) + (size_t)BKEYS * Dh + (size_t)BQ * BKEYS) * sizeof(float);
+  size_t smem = ((size_t)BQ * ((Dh + 3) & ~3) + (size_t)BKEYS * (Dh + 1) + (size_t)BKEYS * Dh + (size_t)BQ * BKEYS) * sizeof(float);
   dim3 grid(max_tiles, H);
   cudaError_t err;
   static size_t configured[2] = {0, 0};      // largest shared-memory size asked for so far, per dtype

@@ -17,7 +17,7 @@ import time
 
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, pages_for_budget
 from ..config.engine import EngineConfig
 from ..sampling.sampler import Sampler
 from .request import GenerationResult, Request
@@ -30,7 +30,12 @@ class Engine:
         self.model = model
         self.config = config
         self.max_model_len = min(config.max_model_len or model.max_positions, model.max_positions)
-        self.cache = CacheManager(model.groups, kv_pages=config.kv_pages, page_size=config.page_size,
+        pages = config.kv_pages
+        if config.kv_cache_bytes is not None:
+            pages = pages_for_budget(model.groups, config.kv_cache_bytes, page_size=config.page_size,
+                                     max_requests=config.max_requests, max_len=self.max_model_len,
+                                     step_tokens=config.batch_tokens, dtype=model.dtype)
+        self.cache = CacheManager(model.groups, kv_pages=pages, page_size=config.page_size,
                                   max_requests=config.max_requests, max_len=self.max_model_len,
                                   dtype=model.dtype, device=model.device)
         self.runner = StepRunner(model, self.cache, max_tokens=config.batch_tokens,

@@ -117,11 +117,17 @@ class Scheduler:
                 f"exceeds the model length {self.max_model_len}")
         P = self.cache.page_size
         for g, group in enumerate(self.cache.groups):
-            if isinstance(group.need, KVNeed) and group.need.window is None:
-                if -(-request.max_total_len // P) > self.cache.kv_pages - 1:
-                    raise RequestRefused(
-                        f"the request needs {-(-request.max_total_len // P)} pages, the cache has "
-                        f"{self.cache.kv_pages - 1}")
+            if not isinstance(group.need, KVNeed):
+                continue
+            # what the request holds in this group at its longest: all its tokens, or, behind a
+            # window, the window plus the largest portion that one step may add
+            tokens = request.max_total_len
+            if group.need.window is not None:
+                tokens = min(tokens, group.need.window + min(self.prefill_chunk, self.batch_tokens) + P)
+            have = self.cache.pages_of[g] - 1
+            if -(-tokens // P) > have:
+                raise RequestRefused(
+                    f"the request needs {-(-tokens // P)} pages of cache group {group.name!r}, which has {have}")
         seed = request.sampling.seed
         if seed is None:
             seed = self._derive_seed(self.base_seed + self.ordinal)

@@ -10,7 +10,7 @@ from __future__ import annotations
 import math
 
 from ..config.model import GPT2Config
-from ..parts.base import Init, LayerSpec, ModelSpec, PartSpec, RunStep, Source
+from ..parts.base import Init, ModelSpec, PartSpec, RunStep, Source, pre_norm_layer
 from ..registry import Architecture, register_architecture
 
 # layers/activation.py:198-203
@@ -50,7 +50,7 @@ def gpt2_spec(config: GPT2Config) -> ModelSpec:
              "up_bias": Source(p + "mlp.c_fc.bias", init=bias),
              "down_weight": Source(p + "mlp.c_proj.weight", transposed=True, init=residual_proj),
              "down_bias": Source(p + "mlp.c_proj.bias", init=bias)})
-        layers.append(LayerSpec(norm(p + "ln_1"), mixer, norm(p + "ln_2"), ffn, block="pre_norm"))
+        layers.append(pre_norm_layer(norm(p + "ln_1"), mixer, norm(p + "ln_2"), ffn))
 
     head_source = "transformer.wte.weight" if config.tie_word_embeddings else "lm_head.weight"
     return ModelSpec(

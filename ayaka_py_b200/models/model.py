@@ -50,46 +50,50 @@ class Model:
         self.position = build(spec.position)
         self.blocks = []
         for layer in spec.layers:
-            block = make_block(layer.block, build(layer.norm1), build(layer.mixer),
-                               build(layer.norm2), build(layer.ffn))
-            if hasattr(block.mixer, "attach_position"):
-                block.mixer.attach_position(self.position)
-            self.blocks.append(block)
+            names = [name for name, _ in layer.parts]
+            if len(set(names)) != len(names):
+                raise ValueError(f"a layer names a part twice: {names}")
+            parts = {name: build(part_spec) for name, part_spec in layer.parts}
+            for part in parts.values():
+                part.set_position(self.position)
+            self.blocks.append(make_block(layer.block, parts))
         self.final_norm = build(spec.final_norm)
         self.head = build(spec.head)
 
-        # Cache groups: run steps whose mixers have the same need share a group
-        # (one page namespace, one block table); each keeps its own layer index.
+        # Cache groups: parts (of any run step) that declare the same need share a group (one
+        # namespace of pages and one block table, or one region of state slots); each keeps its
+        # own layer index inside the group.  ``bindings[i]``: part name -> binding, for run step i.
         self.groups: list[CacheGroupSpec] = []
-        self.bindings: list[CacheBinding | None] = []
+        self.bindings: list[dict[str, CacheBinding]] = []
         counts: list[int] = []
         for index, step in enumerate(spec.order):
             if not 0 <= step.layer < len(self.blocks):
                 raise ValueError(f"run step {index} names layer {step.layer}, the model has {len(self.blocks)}")
-            need = self.blocks[step.layer].mixer.cache_need()
+            needs = {name: part.cache_need() for name, part in self.blocks[step.layer].parts.items()}
+            needs = {name: need for name, need in needs.items() if need is not None}
             if step.cache_of is not None:
-                if not 0 <= step.cache_of < index or self.bindings[step.cache_of] is None:
+                if not 0 <= step.cache_of < index or not self.bindings[step.cache_of]:
                     raise ValueError(f"run step {index}: cache_of must name an earlier run step with a cache")
-                src = self.bindings[step.cache_of]
-                if self.groups[src.group].need != need:
+                theirs = self.bindings[step.cache_of]
+                if set(theirs) != set(needs) or any(self.groups[theirs[n].group].need != needs[n] for n in needs):
                     raise ValueError(f"run step {index} reads a cache of another geometry")
-                self.bindings.append(CacheBinding(src.group, src.name, src.layer, writes=False))
+                self.bindings.append({n: CacheBinding(b.group, b.name, b.layer, writes=False) for n, b in theirs.items()})
                 continue
-            if need is None:
-                self.bindings.append(None)
-                continue
-            if not isinstance(need, (KVNeed, StateNeed)):
-                raise TypeError(f"cache_need() of {type(self.blocks[step.layer].mixer).__name__} "
-                                f"must be KVNeed, StateNeed or None")
-            for g, group in enumerate(self.groups):
-                if group.need == need:
-                    break
-            else:
-                g = len(self.groups)
-                self.groups.append(CacheGroupSpec(name=f"group{g}", need=need, layers=0))
-                counts.append(0)
-            self.bindings.append(CacheBinding(g, self.groups[g].name, counts[g], writes=True))
-            counts[g] += 1
+            mine: dict[str, CacheBinding] = {}
+            for name, need in needs.items():
+                if not isinstance(need, (KVNeed, StateNeed)):
+                    raise TypeError(f"cache_need() of {type(self.blocks[step.layer].parts[name]).__name__} "
+                                    f"must be KVNeed, StateNeed or None")
+                for g, group in enumerate(self.groups):
+                    if group.need == need:
+                        break
+                else:
+                    g = len(self.groups)
+                    self.groups.append(CacheGroupSpec(name=f"group{g}", need=need, layers=0))
+                    counts.append(0)
+                mine[name] = CacheBinding(g, self.groups[g].name, counts[g], writes=True)
+                counts[g] += 1
+            self.bindings.append(mine)
         self.groups = [CacheGroupSpec(g.name, g.need, counts[i]) for i, g in enumerate(self.groups)]
         self.loaded = False
 
@@ -128,8 +132,8 @@ class Model:
         if not self.loaded:
             raise RuntimeError("the model has no weights yet")
         x = self.embedding.forward(ctx, self.position)
-        for step, binding in zip(self.spec.order, self.bindings):
-            x = self.blocks[step.layer].forward(x, ctx, binding)
+        for step, caches in zip(self.spec.order, self.bindings):
+            x = self.blocks[step.layer].forward(x, ctx, caches)
         if ctx.num_wanted == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=x.device)
         h = self.final_norm.forward(x, ctx, rows=ctx.want_rows)

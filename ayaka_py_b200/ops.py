@@ -535,11 +535,14 @@ def tc_error() -> int:
 def attention(q, kcache, vcache, table, ctx, num_heads: int, scale: float,
               window: int | None = None, append: tuple | None = None) -> torch.Tensor:
     """Attention of the step's rows (``ctx`` gives the rows of each request): the
-    split-context decode kernels when every request brings one row; the
-    tensor-core kernel for prompt portions in bfloat16 with head size 64; else
-    the general kernel.  ``append`` = (k, v): the rows' keys and values, which
+    split-context decode kernels when every request brings one row (head sizes in
+    steps of 16); the tensor-core kernel for prompt portions in bfloat16 with head
+    size 64, beside the decode kernels for the single rows of a mixed step; else
+    the general kernel, which takes every head size up to 256.  ``append`` = (k, v): the rows' keys and values, which
     go into the cache first (in a decode step, inside the attention kernel)."""
-    if ctx.max_q_len == 1:
+    # Head sizes that are no multiple of 16 are taken by the general kernel alone (the decode kernels
+    # read keys in 16-byte pieces and refuse them).
+    if ctx.max_q_len == 1 and kcache.shape[3] % 16 == 0:
         return attention_decode(q, kcache, vcache, table, ctx.req_pos0, num_heads, scale, window,
                                 ctx.cache.max_len,
                                 append=(append[0], append[1], ctx.row_req) if append is not None else None,

@@ -23,8 +23,9 @@ class Attention(Mixer):
         kv_heads = kv_heads or num_heads
         if num_heads % kv_heads:
             raise ValueError(f"{num_heads} heads cannot share {kv_heads} key/value heads")
-        if head_dim % 16 or not 16 <= head_dim <= 256:
-            raise ValueError(f"head size {head_dim} is not a multiple of 16 in [16, 256]")
+        if not 1 <= head_dim <= 256:
+            raise ValueError(f"head size {head_dim} is not in [1, 256]: the attention kernels keep a head's row in "
+                             f"registers and shared memory sized for at most 256 elements")
         if window is not None and window < 1:
             raise ValueError("window must be positive or None")
         self.width, self.num_heads, self.kv_heads, self.head_dim = width, num_heads, kv_heads, head_dim
@@ -35,7 +36,7 @@ class Attention(Mixer):
         self.qkv_weight = self.qkv_bias = self.out_weight = self.out_bias = None
         self.position = None
 
-    def attach_position(self, position) -> None:
+    def set_position(self, position) -> None:
         self.position = position
 
     def tensors(self):
@@ -53,7 +54,7 @@ class Attention(Mixer):
     def forward(self, h, residual, ctx, cache):
         kcache, vcache = ctx.cache.kv_layer(cache.group, cache.layer)
         table = ctx.tables[cache.group]
-        rotate = getattr(self.position, "rotate_qk", None)
+        rotate = self.position.rotate_qk if self.position is not None else None
         # Rows of prompts whose keys go into the cache as the projection makes them: the product may
         # file them itself.  (A decode step's are filed by its attention kernel, rotated keys after
         # the rotation.)

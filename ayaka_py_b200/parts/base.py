@@ -1,8 +1,9 @@
 """What a part is, and the registries that the model is built from.
 
 A model is put together from parts: an embedding, a position encoding, and for
-every layer a norm, a mixer (attention here), a second norm and a feed-forward,
-arranged by a block; then a final norm and a head.  Each part
+every layer a set of named parts (for GPT-2 a norm, a mixer (attention here), a
+second norm and a feed-forward) that a block arranges; then a final norm and a
+head.  Each part
 
 * is made from plain parameters (sizes and constants), never from a model
   configuration, and does not know which model it is in;
@@ -70,10 +71,26 @@ class PartSpec:
 class KVNeed:
     """Keys and values in pages.  ``window`` None: every earlier key is kept;
     an integer: only the last ``window`` keys are read, earlier pages may be
-    given back."""
+    given back.  Values have the keys' head count and size unless
+    ``value_heads`` / ``value_dim`` say otherwise (the pages of keys and of
+    values are separate tensors)."""
     kv_heads: int
     head_dim: int
     window: int | None = None
+    value_heads: int | None = None
+    value_dim: int | None = None
+
+    @property
+    def v_heads(self) -> int:
+        return self.kv_heads if self.value_heads is None else self.value_heads
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
+
+    def elements_per_token(self) -> int:
+        """Key and value elements that one token takes in one layer."""
+        return self.kv_heads * self.head_dim + self.v_heads * self.v_dim
 
 
 @dataclass(frozen=True)
@@ -101,6 +118,11 @@ class Part:
         """``KVNeed``, ``StateNeed`` or None."""
         return None
 
+    def set_position(self, position: "PositionEncoding") -> None:
+        """The model's position encoding, handed to every part of every layer when the
+        model is built.  Parts that apply positions themselves (an attention that
+        rotates queries and keys) keep it; the default ignores it."""
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, ctx, rows: torch.Tensor | None = None) -> torch.Tensor:
@@ -124,6 +146,11 @@ class FeedForward(Part):
 
 
 class PositionEncoding(Part):
+    # A position encoding that acts on queries and keys sets this to a method
+    # ``rotate_qk(q, k, heads, kv_heads, head_dim, ctx)`` that turns the step's q and k rows
+    # in place (``ctx.positions`` gives each row's position); None: nothing to do.
+    rotate_qk = None
+
     def embedding_table(self) -> torch.Tensor | None:
         """A [positions, d] table added to the token embedding, or None."""
         return None
@@ -145,14 +172,26 @@ class Head(Part):
 
 
 class Block:
-    """Arrangement of norm, mixer and feed-forward in one layer."""
+    """Arrangement of a layer's parts: which runs on what, in which order.
+
+    ``PARTS`` names the parts the arrangement needs (a layer's spec must name
+    exactly these); each is also reachable as an attribute.  ``forward`` gets the
+    residual stream and, for the parts that declared a cache need, their
+    ``CacheBinding`` by part name."""
 
     KIND: ClassVar[str] = ""
+    PARTS: ClassVar[tuple[str, ...]] = ()
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward):
-        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+    def __init__(self, parts: dict[str, Part]):
+        missing, extra = set(self.PARTS) - set(parts), set(parts) - set(self.PARTS)
+        if missing or extra:
+            raise ValueError(f"arrangement {self.KIND!r} takes the parts {list(self.PARTS)}: "
+                             f"missing {sorted(missing)}, not used {sorted(extra)}")
+        self.parts = dict(parts)
+        for name, part in parts.items():
+            setattr(self, name, part)
 
-    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, caches: dict) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -180,30 +219,40 @@ def make_part(spec: PartSpec, dtype: torch.dtype, device) -> Part:
     return factory(**spec.params, dtype=dtype, device=device)
 
 
-def make_block(kind: str, norm1, mixer, norm2, ffn) -> Block:
+def make_block(kind: str, parts: dict[str, Part]) -> Block:
     try:
         cls = _BLOCKS[kind]
     except KeyError:
         raise KeyError(f"no block arrangement {kind!r}; registered: {sorted(_BLOCKS)}") from None
-    return cls(norm1, mixer, norm2, ffn)
+    return cls(parts)
 
 
 # ------------------------------------------------------------ model as data --
 
 @dataclass(frozen=True)
 class LayerSpec:
-    norm1: PartSpec
-    mixer: PartSpec
-    norm2: PartSpec
-    ffn: PartSpec
+    """A layer as data: its parts by name, in the order in which they are built (and in
+    which their tensors are listed), and the arrangement (``register_block``) that runs
+    them.  Nothing fixes how many parts a layer has or what they are called: an
+    arrangement with four norms, with one norm that feeds mixer and feed-forward side
+    by side, or without a feed-forward is another ``Block`` and another tuple here."""
+    parts: tuple[tuple[str, PartSpec], ...]
     block: str = "pre_norm"
+
+    def part(self, name: str) -> PartSpec:
+        return dict(self.parts)[name]
+
+
+def pre_norm_layer(norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, ffn: PartSpec) -> LayerSpec:
+    """x += mixer(norm1(x)); x += ffn(norm2(x)): the arrangement ``pre_norm``."""
+    return LayerSpec((("norm1", norm1), ("mixer", mixer), ("norm2", norm2), ("ffn", ffn)), "pre_norm")
 
 
 @dataclass(frozen=True)
 class RunStep:
     """One entry of the run order.  ``layer`` indexes ``ModelSpec.layers`` (a
     layer may be named twice).  ``cache_of``: index of an earlier run step whose
-    cache this one reads instead of keeping its own."""
+    caches this one reads instead of keeping its own."""
     layer: int
     cache_of: int | None = None
 

@@ -1,4 +1,4 @@
-"""Arrangements of norm, mixer and feed-forward in a layer."""
+"""Arrangements of a layer's parts."""
 
 from __future__ import annotations
 
@@ -11,9 +11,10 @@ class PreNormBlock(Block):
     feed-forward's last epilogue."""
 
     KIND = "pre_norm"
+    PARTS = ("norm1", "mixer", "norm2", "ffn")
 
-    def forward(self, x, ctx, cache):
-        x = self.mixer.forward(self.norm1.forward(x, ctx), x, ctx, cache)
+    def forward(self, x, ctx, caches):
+        x = self.mixer.forward(self.norm1.forward(x, ctx), x, ctx, caches.get("mixer"))
         return self.ffn.forward(self.norm2.forward(x, ctx), x, ctx)
 
 

@@ -192,3 +192,48 @@ def test_random_orders(seed):
         m.close(s)
     m.assert_clean()
     assert done > 5
+
+
+def test_keys_and_values_may_differ_in_heads_and_size():
+    """A mixer may keep values of another head count and size than its keys: two tensors, one page table."""
+    import torch
+    need = KVNeed(kv_heads=2, head_dim=24, value_heads=1, value_dim=40)
+    assert (need.v_heads, need.v_dim, need.elements_per_token()) == (1, 40, 2 * 24 + 40)
+    assert KVNeed(3, 16).elements_per_token() == 2 * 3 * 16
+    m = CacheManager([CacheGroupSpec("odd", need, 3)], kv_pages=5, page_size=4, max_requests=2, max_len=16,
+                     dtype=torch.float32, device="cpu")
+    keys, values = m.kv_layer(0, 2)
+    assert keys.shape == (5, 4, 2, 24) and values.shape == (5, 4, 1, 40)
+    assert m.bytes_per_token() == 3 * (2 * 24 + 40) * 4
+
+
+def test_pages_per_group_out_of_one_byte_budget():
+    import torch
+    from ayaka_py_b200.cache.manager import pages_for_budget
+    full = CacheGroupSpec("full", KVNeed(4, 32), 6)                    # 6 layers, every key kept
+    wide = CacheGroupSpec("wide", KVNeed(8, 64), 2)                    # 2 layers, four times the bytes per token and layer
+    local = CacheGroupSpec("local", KVNeed(4, 32, window=48), 6)       # a window of 48 keys
+    state = CacheGroupSpec("state", StateNeed((7,)), 2)
+    kw = dict(page_size=16, max_requests=4, max_len=1024, step_tokens=64, dtype=torch.bfloat16)
+    cost = lambda g: g.layers * 16 * g.need.elements_per_token() * 2
+    budget = 64 << 20
+    pages = pages_for_budget([full, wide, local, state], budget, **kw)
+    assert pages[3] == 0
+    # behind a window a request never holds more than window + one step: 4 requests x (ceil(112 / 16) + 1) pages + padding
+    assert pages[2] == 4 * 8 + 1
+    # the groups that keep every key hold the same number of tokens, and the budget is used but not passed
+    assert pages[0] == pages[1]
+    spent = sum(p * cost(g) for p, g in zip(pages[:3], (full, wide, local)))
+    assert budget - (cost(full) + cost(wide)) < spent <= budget
+    m = CacheManager([full, wide, local, state], kv_pages=pages, page_size=16, max_requests=4, max_len=1024, device=None)
+    assert m.pages_of == pages and m.free_pages(0) == pages[0] - 1 and m.free_pages(2) == 32
+    a = m.open("a")
+    m.commit(m.reserve([(a, 0, 300)]))
+    assert m.free_pages(0) == pages[0] - 1 - 19 and m.free_pages(1) == pages[1] - 1 - 19
+    assert m.free_pages(2) == 32 - 4                                    # 300 tokens, window 48: pages 15..18 stay
+    m.close(a)
+    m.assert_clean()
+    with pytest.raises(ValueError):
+        pages_for_budget([full, wide], 1000, **kw)                      # not even one page each
+    with pytest.raises(ValueError):
+        CacheManager([full, wide], kv_pages=[9], page_size=16, max_requests=1, max_len=64, device=None)

@@ -56,11 +56,11 @@ def test_spec_has_no_size_of_its_own():
     cfg = GPT2Config.from_dict(tiny_models.TINY_B)
     spec = architecture_for(cfg.to_dict()).build_spec(cfg)
     assert len(spec.layers) == 3 and [s.layer for s in spec.order] == [0, 1, 2]
-    m = spec.layers[2].mixer
+    m = spec.layers[2].part("mixer")
     assert m.params["head_dim"] == 48 and m.params["num_heads"] == 2
     assert m.params["scale"] == pytest.approx(48 ** -0.5 / 3)
-    assert spec.layers[0].ffn.params == {"width": 96, "inner": 320, "activation": "gelu_erf", "bias": True}
-    assert spec.layers[0].norm1.params["eps"] == 1e-6
+    assert spec.layers[0].part("ffn").params == {"width": 96, "inner": 320, "activation": "gelu_erf", "bias": True}
+    assert spec.layers[0].part("norm1").params["eps"] == 1e-6
     assert spec.head.sources["weight"].name == "transformer.wte.weight"
     untied = GPT2Config.from_dict({**tiny_models.TINY_B, "tie_word_embeddings": False})
     assert architecture_for(untied.to_dict()).build_spec(untied).head.sources["weight"].name == "lm_head.weight"

@@ -125,7 +125,7 @@ def test_decode_graphs_give_the_same_tokens(model_folders, dtype):
     prompts = tiny_models.prompts(cfg, [3, 20, 41], seed=26)
     stop = [StopCriteria(max_tokens=n, ignore_eos=True) for n in (30, 12, 21)]     # the batch shrinks: 3 -> 2 -> 1
     params = [SamplingParams(temperature=0.0), SamplingParams(temperature=0.7, seed=5), SamplingParams(temperature=0.0)]
-    eager = LLM(folder, dtype=dtype, page_size=8, kv_pages=64, batch_tokens=64, prefill_chunk=32)
+    eager = LLM(folder, dtype=dtype, page_size=8, kv_pages=64, batch_tokens=64, prefill_chunk=32, decode_graph=False)
     graphs = LLM(folder, dtype=dtype, page_size=8, kv_pages=64, batch_tokens=64, prefill_chunk=32, decode_graph=True)
     want = [r.token_ids for r in eager.generate(prompts, params, stop)]
     got = [r.token_ids for r in graphs.generate(prompts, params, stop)]

@@ -135,6 +135,10 @@ ATTENTION_CASES = [
     ([70], [200], 1, 1, 256, 32, None),
     ([9, 1, 50], [40, 99, 0], 4, 2, 32, 4, 24),            # window
     ([1, 3], [63, 64], 5, 5, 64, 64, 7),
+    ([7, 1, 35], [0, 40, 3], 3, 3, 20, 8, None),           # head sizes that are no multiple of 16, of 4, of 2
+    ([40, 2], [0, 70], 4, 2, 36, 16, 30),
+    ([33, 1], [5, 64], 6, 3, 5, 4, None),
+    ([1, 1, 9], [99, 0, 12], 2, 2, 6, 16, None),
 ]
 
 

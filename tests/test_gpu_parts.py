@@ -170,7 +170,8 @@ def test_block_arrangement_and_run_order():
     twice = dataclasses.replace(spec, order=(RunStep(0), RunStep(1), RunStep(0), RunStep(1, cache_of=1)))
     model = Model(twice, torch.float32, "cuda")
     assert model.groups[0].layers == 3
-    assert [b.layer for b in model.bindings] == [0, 1, 2, 1] and [b.writes for b in model.bindings] == [True, True, True, False]
+    assert [b["mixer"].layer for b in model.bindings] == [0, 1, 2, 1]
+    assert [b["mixer"].writes for b in model.bindings] == [True, True, True, False]
     with pytest.raises(ValueError):
         Model(dataclasses.replace(spec, order=(RunStep(0, cache_of=0),)), torch.float32, "cuda")
     with pytest.raises(ValueError):
@@ -246,8 +247,8 @@ class ToyConfig:
 
 
 def register_toy():
-    from ayaka_py_b200.parts import (FeedForward, Init, LayerSpec, Mixer, ModelSpec, PartSpec, RunStep, Source,
-                                     StateNeed, TensorDecl, register_part)
+    from ayaka_py_b200.parts import (FeedForward, Init, Mixer, ModelSpec, PartSpec, RunStep, Source,
+                                     StateNeed, TensorDecl, pre_norm_layer, register_part)
     from ayaka_py_b200.registry import Architecture, register_architecture
 
     class RunningMeanMixer(Mixer):
@@ -294,7 +295,7 @@ def register_toy():
         d = cfg.width
         norm = lambda name: PartSpec("layernorm", {"width": d, "eps": 1e-5},
                                      {"weight": Source(name + ".g", init=Init(0.1, 1.0)), "bias": Source(name + ".b", init=Init(0.1))})
-        layers = tuple(LayerSpec(
+        layers = tuple(pre_norm_layer(
             norm(f"l{i}.n1"), PartSpec("toy_running_mean", {"width": d}, {"weight": Source(f"l{i}.mix", init=Init(0.3))}),
             norm(f"l{i}.n2"), PartSpec("toy_scale_ffn", {"width": d}, {"gain": Source(f"l{i}.gain", init=Init(0.5))}))
             for i in range(cfg.layers))
@@ -367,8 +368,8 @@ class ToyMixedConfig:
 
 
 def register_toy_mixed():
-    from ayaka_py_b200.parts import (FeedForward, Init, LayerSpec, ModelSpec, PartSpec, PositionEncoding, RunStep,
-                                     Source, TensorDecl, register_part)
+    from ayaka_py_b200.parts import (FeedForward, Init, ModelSpec, PartSpec, PositionEncoding, RunStep,
+                                     Source, TensorDecl, pre_norm_layer, register_part)
     from ayaka_py_b200.registry import Architecture, register_architecture
     register_toy()                               # the running-mean mixer
 
@@ -427,8 +428,8 @@ def register_toy_mixed():
         mlp = PartSpec("mlp", {"width": d, "inner": 40, "activation": "gelu_erf", "bias": True},
                        {"up_weight": Source("l1.up", init=Init(0.3)), "up_bias": Source("l1.up_b", init=Init(0.1)),
                         "down_weight": Source("l1.down", init=Init(0.3)), "down_bias": Source("l1.down_b", init=Init(0.1))})
-        layers = (LayerSpec(norm("l0.n1"), attention, norm("l0.n2"), routed),
-                  LayerSpec(norm("l1.n1"), mean, norm("l1.n2"), mlp))
+        layers = (pre_norm_layer(norm("l0.n1"), attention, norm("l0.n2"), routed),
+                  pre_norm_layer(norm("l1.n1"), mean, norm("l1.n2"), mlp))
         return ModelSpec(cfg.vocab_size, d, cfg.positions,
                          PartSpec("token_embedding", {"vocab": cfg.vocab_size, "width": d}, {"weight": Source("emb", init=Init(1.0))}),
                          PartSpec("toy_turning_positions", {"head_dim": Dh, "base": 50.0}, {}),
@@ -508,4 +509,124 @@ def test_toy_positions_routing_and_mixed_layers_without_touching_the_framework(t
         outs = [None if (o := session.step(rec)) is None or o.shape[0] == 0 else o.cpu().numpy() for rec in trace]
         got = trace_tools.collect(trace, outs)
         assert trace_tools.first_difference(got, want, 2e-4) is None
+        session.cache.assert_clean()
+
+
+# ------------------------------- toy arrangement: one norm, two parallel branches --
+
+@dataclass(frozen=True)
+class ToyParallelConfig:
+    """A third toy architecture: every layer has ONE norm whose output feeds the framework's
+    attention and the framework's MLP side by side, x += attention(norm(x)) + mlp(norm(x)); the last
+    layer has no feed-forward at all.  Only the arrangement is new, and it is defined here."""
+    ARCHITECTURE: ClassVar[str] = "ToyParallelLM"
+    vocab_size: int = 83
+    width: int = 64
+    heads: int = 2
+    inner: int = 88
+    layers: int = 3
+    positions: int = 160
+
+    @classmethod
+    def from_dict(cls, values):
+        names = ("vocab_size", "width", "heads", "inner", "layers", "positions")
+        return cls(**{k: values[k] for k in names if k in values})
+
+    def to_dict(self):
+        return {"architectures": [self.ARCHITECTURE], **{k: getattr(self, k) for k in
+                ("vocab_size", "width", "heads", "inner", "layers", "positions")}}
+
+
+def register_toy_parallel():
+    from ayaka_py_b200.parts import Block, Init, LayerSpec, ModelSpec, PartSpec, RunStep, Source, register_block
+    from ayaka_py_b200.registry import Architecture, register_architecture
+
+    class ParallelBlock(Block):
+        KIND = "toy_parallel"
+        PARTS = ("norm", "mixer", "ffn")
+
+        def forward(self, x, ctx, caches):
+            h = self.norm.forward(x, ctx)
+            x = self.mixer.forward(h, x, ctx, caches["mixer"])        # x + mix(h), summed in the projection's epilogue
+            return self.ffn.forward(h, x, ctx)                         # ... + ffn(h), the same h
+
+    class MixerOnlyBlock(Block):
+        KIND = "toy_mixer_only"
+        PARTS = ("norm", "mixer")
+
+        def forward(self, x, ctx, caches):
+            return self.mixer.forward(self.norm.forward(x, ctx), x, ctx, caches["mixer"])
+
+    register_block(ParallelBlock.KIND, ParallelBlock)
+    register_block(MixerOnlyBlock.KIND, MixerOnlyBlock)
+
+    def spec(cfg: ToyParallelConfig) -> ModelSpec:
+        d, H = cfg.width, cfg.heads
+        Dh = d // H
+        norm = lambda name: PartSpec("layernorm", {"width": d, "eps": 1e-5},
+                                     {"weight": Source(name + ".g", init=Init(0.1, 1.0)), "bias": Source(name + ".b", init=Init(0.1))})
+        layers = []
+        for i in range(cfg.layers):
+            attention = PartSpec("attention", {"width": d, "num_heads": H, "kv_heads": H, "head_dim": Dh,
+                                               "scale": Dh ** -0.5, "window": None, "bias": True},
+                                 {"qkv_weight": Source(f"l{i}.qkv", init=Init(0.2)), "qkv_bias": Source(f"l{i}.qkv_b", init=Init(0.1)),
+                                  "out_weight": Source(f"l{i}.out", init=Init(0.2)), "out_bias": Source(f"l{i}.out_b", init=Init(0.1))})
+            mlp = PartSpec("mlp", {"width": d, "inner": cfg.inner, "activation": "gelu_tanh", "bias": True},
+                           {"up_weight": Source(f"l{i}.up", init=Init(0.2)), "up_bias": Source(f"l{i}.up_b", init=Init(0.1)),
+                            "down_weight": Source(f"l{i}.down", init=Init(0.2)), "down_bias": Source(f"l{i}.down_b", init=Init(0.1))})
+            if i < cfg.layers - 1:
+                layers.append(LayerSpec((("norm", norm(f"l{i}.n")), ("mixer", attention), ("ffn", mlp)), "toy_parallel"))
+            else:
+                layers.append(LayerSpec((("norm", norm(f"l{i}.n")), ("mixer", attention)), "toy_mixer_only"))
+        return ModelSpec(cfg.vocab_size, d, cfg.positions,
+                         PartSpec("token_embedding", {"vocab": cfg.vocab_size, "width": d}, {"weight": Source("emb", init=Init(1.0))}),
+                         PartSpec("learned_positions", {"positions": cfg.positions, "width": d}, {"weight": Source("pos", init=Init(0.5))}),
+                         tuple(layers), tuple(RunStep(i) for i in range(cfg.layers)), norm("final"),
+                         PartSpec("lm_head", {"vocab": cfg.vocab_size, "width": d}, {"weight": Source("emb", init=Init(1.0))}))
+
+    register_architecture(Architecture("ToyParallelLM", "toy_parallel", ToyParallelConfig, spec))
+
+
+def plain_toy_parallel(cfg, t, tokens, round_to=None):
+    T, d, H = len(tokens), cfg.width, cfg.heads
+    Dh = d // H
+    x = t["emb"][tokens] + t["pos"][:T]
+    for i in range(cfg.layers):
+        h = plain_gpt2.layer_norm(x, t[f"l{i}.n.g"], t[f"l{i}.n.b"], 1e-5)
+        qkv = h @ t[f"l{i}.qkv"].T + t[f"l{i}.qkv_b"]
+        q, k, v = (qkv[:, j * d:(j + 1) * d].reshape(T, H, Dh) for j in range(3))
+        o = plain_gpt2.causal_attention(q, k, v, Dh ** -0.5).reshape(T, d)
+        branch = o @ t[f"l{i}.out"].T + t[f"l{i}.out_b"]
+        if i < cfg.layers - 1:
+            branch = branch + plain_gpt2.activation("gelu_new", h @ t[f"l{i}.up"].T + t[f"l{i}.up_b"]) @ t[f"l{i}.down"].T + t[f"l{i}.down_b"]
+        x = x + branch
+    return plain_gpt2.layer_norm(x, t["final.g"], t["final.b"], 1e-5) @ t["emb"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_arrangement_one_norm_two_branches_and_a_layer_without_feed_forward(tmp_path, dtype):
+    """Two arrangements that are not the framework's (a norm shared by a mixer and a feed-forward that run
+    side by side; a layer that is a mixer only), registered from this file with the framework's own parts,
+    through the loader, the cache manager, the step function and the replay program, nothing of which
+    changes.  In bfloat16 the prompt steps run the tensor-core kernels (head size 32 and width 64)."""
+    import trace_tools
+    from ayaka_py_b200.replay import ReplaySession
+    from ayaka_py_b200.weights import write_random_model
+
+    register_toy_parallel()
+    cfg = ToyParallelConfig()
+    folder = write_random_model(tmp_path / "parallel", cfg, seed=11, dtype="bfloat16")
+    tensors = {k: v.astype(np.float64) for k, v in plain_gpt2.read_safetensors(folder / "model.safetensors").items()}
+    rs = np.random.RandomState(7)
+    reqs = {f"p{i}": rs.randint(0, cfg.vocab_size, n).tolist() for i, n in enumerate([70, 9, 140, 33])}
+    want = {rid: plain_toy_parallel(cfg, tensors, toks) for rid, toks in reqs.items()}
+    limit = 2e-4 if dtype == "float32" else 0.02 * max(float(np.abs(w).max()) for w in want.values())
+    for trace in (trace_tools.whole(reqs), trace_tools.tail_decoded(reqs, tail=8), trace_tools.mixed(reqs, seed=6)):
+        session = ReplaySession(folder, dtype, max_tokens=trace_tools.tokens_needed(trace), page_size=16)
+        assert [len(b) for b in session.model.bindings] == [1, 1, 1] and session.model.groups[0].layers == 3
+        assert [type(b).KIND for b in session.model.blocks] == ["toy_parallel", "toy_parallel", "toy_mixer_only"]
+        outs = [None if (o := session.step(rec)) is None or o.shape[0] == 0 else o.cpu().numpy() for rec in trace]
+        got = trace_tools.collect(trace, outs)
+        bad = trace_tools.first_difference(got, want, limit)
+        assert bad is None, f"first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"
         session.cache.assert_clean()

@@ -202,6 +202,32 @@ def test_xl_layer_sizes(dtype, tmp_path):
         assert bad is None, f"first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,head_dim", [(3, 20), (2, 36), (6, 5), (5, 6), (1, 100)])
+def test_head_sizes_that_are_no_multiple_of_16(heads, head_dim, dtype, tmp_path):
+    """config.json only asks that the heads divide the width (``models/gpt2.py:120-121`` in the
+    reference): head sizes of 20, 36, 5, 6 and 100 run (on the general attention kernel and, where
+    the width is no multiple of 8, the FP32-pipe product) and match the plain implementation."""
+    from ayaka_py_b200.replay import ReplaySession
+    cfg = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_layer": 2, "n_embd": heads * head_dim,
+           "n_head": heads, "n_inner": 3 * heads * head_dim + 4, "vocab_size": 211, "n_positions": 200,
+           "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new", "scale_attn_weights": True,
+           "scale_attn_by_inverse_layer_idx": False, "tie_word_embeddings": True}
+    weights = tiny_models.numpy_weights(cfg, 50 + head_dim, scale=4.0, bf16_exact=True)
+    folder = tiny_models.write_folder(tmp_path / "m", cfg, weights)
+    reqs = {f"h{i}": t for i, t in enumerate(tiny_models.prompts(cfg, [70, 9, 140, 33], seed=head_dim))}
+    want = trace_tools.oracle(cfg, weights, reqs)
+    for trace in (trace_tools.mixed(reqs, seed=3), trace_tools.tail_decoded(reqs, 16)):
+        session = ReplaySession(folder, dtype, trace_tools.tokens_needed(trace), 16)
+        outputs = []
+        for record in trace:
+            logits = session.step(record)
+            outputs.append(None if logits is None or logits.shape[0] == 0 else logits.cpu().numpy())
+        session.cache.assert_clean()
+        bad = trace_tools.first_difference(trace_tools.collect(trace, outputs), want, tolerance(dtype, want))
+        assert bad is None, f"first wrong place: request {bad[0]} position {bad[1]} |diff| {bad[2]:.3e}"
+
+
 @pytest.fixture(scope="module")
 def xl_full_depth(tmp_path_factory):
     """All 48 layers of the XL shape, random weights, and the plain implementation's logits for two requests."""
@@ -296,7 +322,8 @@ def test_schedule_of_the_reference_scheduler_with_its_paged_logits(dtype, model_
     steps, want, geometry = reference_schedule()
     assert any(len(s["entries"]) > 1 and {len(e["tokens"]) for e in s["entries"]} != {1} for s in steps)   # mixed steps
     assert sum(len(s["end"]) for s in steps) == 6                                   # five finishes and a preemption
-    session = ReplaySession(str(folder), dtype, (geometry["pages"] - 1) * geometry["page_size"], geometry["page_size"])
+    session = ReplaySession(str(folder), dtype, (geometry["pages"] - 1) * geometry["page_size"], geometry["page_size"],
+                            max_requests=5)
     limit = 1e-4 if dtype == "float32" else 0.02 * float(np.abs(np.concatenate(want)).max())
     for record, expect in zip(steps, want):
         logits = session.step(record)

@@ -38,12 +38,12 @@ class DecodeGraphs:
 
     def _capture(self, bucket: int):
         ctx = self.runner.prepare([], pad_to=bucket)
-        self.model.forward(ctx)                      # eager once: first-use set-up, scratch buffers
+        self.runner.forward(ctx)                     # eager once: first-use set-up, scratch buffers
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
         with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx)
+            logits = self.runner.forward(ctx)
         kernels = ops.launches - before
         entry = (graph, logits, kernels)
         self.graphs[bucket] = entry

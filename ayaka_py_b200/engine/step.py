@@ -75,6 +75,8 @@ class StepRunner:
         self.max_requests = max_requests or cache.max_requests
         self.kv_groups = [g for g, spec in enumerate(cache.groups) if isinstance(spec.need, KVNeed)]
         self._allocate(max_tokens)
+        self._program = None              # the model's step as a native program; made at the first step
+        self._lowered = False
         self.steps = 0
         self.rows_run = 0
 
@@ -207,6 +209,18 @@ class StepRunner:
             max_q_len=int(counts.max()), max_kv_len=int(ends.max()), earlier_rows_settled=True,
             num_single=int((counts == 1).sum()))
 
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        """The model on a prepared step: through the native step program when every part of the
+        model can be lowered to one (``engine/program.py``), else through ``Model.forward``."""
+        if not self._lowered:
+            self._lowered = True
+            if getattr(self.model, "loaded", False) and hasattr(self.model, "spec"):
+                from .program import lower_model
+                self._program = lower_model(self.model, self.cache)
+        if self._program is not None:
+            return self._program.run(ctx)
+        return self.model.forward(ctx)
+
     def run(self, entries: Sequence[StepEntry], tokens_from: torch.Tensor | None = None) -> torch.Tensor:
         """Logits [S, V] float32 on the device.  The caller has reserved the
         step in the cache manager and commits it afterwards.  ``tokens_from``
@@ -217,4 +231,4 @@ class StepRunner:
             if ctx.num_rows != len(entries):      # then the packed order is the caller's order
                 raise ValueError("tokens can come from the device only for entries of one token each")
             ctx.tokens[:len(entries)].copy_(tokens_from[:len(entries)])
-        return self.model.forward(ctx)
+        return self.forward(ctx)

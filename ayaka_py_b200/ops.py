@@ -277,19 +277,9 @@ def tc_splits(M: int, N: int, K: int) -> int:
     Up to 64 rows the factor is 1, 2, 4, 8 or 16: those splits form a cluster.  16 (beyond the
     portable cluster size) only where each split still has four K blocks: a product of 13
     tiles and K = 6400 streamed at 3.6 TB/s from 104 CTAs, which do not keep enough
-    bytes in flight, and at the copy rate from 200."""
-    bt = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
-    tiles = -(-N // 128) * -(-M // bt)
-    blocks = -(-K // 64)
-    sms = sm_count()
-    if tiles >= sms or blocks < 4 or M > CLUSTER_ROWS:
-        return 1          # more rows: partial sums through global scratch cost more than the split saves (measured)
-    if tiles * 16 <= sms * 3 // 2 and blocks >= 64:
-        return 16
-    for p in (8, 4, 2):
-        if tiles * p <= sms * 14 // 10 and blocks >= p:
-            return p
-    return 1
+    bytes in flight, and at the copy rate from 200.  (The rule itself lives in the library,
+    where the native step program uses it too.)"""
+    return int(_ready().ayk_tc_splits(ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K)))
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
@@ -399,29 +389,51 @@ def gemm_tc_prefill(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None 
     return out
 
 
+class _KvTarget(ctypes.Structure):
+    _fields_ = [("kcache", ctypes.c_void_p), ("vcache", ctypes.c_void_p), ("row_req", ctypes.c_void_p),
+                ("positions", ctypes.c_void_p), ("table", ctypes.c_void_p), ("table_stride", ctypes.c_int32),
+                ("page_size", ctypes.c_int32), ("col0", ctypes.c_int32), ("width", ctypes.c_int32),
+                ("dtype", ctypes.c_int32)]
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            activation: str = "none", residual: torch.Tensor | None = None,
            out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
            kv: KVAppend | None = None) -> torch.Tensor:
     """act(a @ w^T + bias) (+ residual).  float32 operands run on the FP32
     pipes (true 32-bit); bfloat16 operands on the tensor cores (tcgen05) when
-    K is a multiple of 8, else on the FP32 pipes with 32-bit accumulation.
+    K is a multiple of 8, else on the FP32 pipes with 32-bit accumulation: up to 16 rows,
+    and up to 64 rows with few output tiles, the kernel whose CTAs split K inside a cluster;
+    above, the persistent kernel with 128-row tiles.  The choice is made in the library
+    (``ayk_linear``), by the same code that the native step program runs.
     ``kv``: see KVAppend; ``kv.done`` tells whether the product filed the rows."""
-    if a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.shape[0] > 0:
-        M, N, K = a.shape[0], w.shape[0], a.shape[1]
-        # Up to 64 rows with few output tiles: weights as the MMA's M side, K split over a cluster.
-        # More rows: tiles of 128 rows by a width that fills the SMs, no split along K.  (Up to 128
-        # rows with an out width that is no multiple of 8 stay with the first kernel, whose stores
-        # run along the features.)
-        if M <= PREFILL_ROWS or (M <= CLUSTER_ROWS and tc_splits(M, N, K) > 1):
-            return gemm_tc(a, w, bias, activation, residual, out_dtype, out)
-        if N % 8 == 0 or M > 128:
-            if (kv is not None and N % 8 == 0 and activation == "none" and residual is None
-                    and kv.fits(N, out_dtype or a.dtype) and (bias is None or bias.data_ptr() % 16 == 0)):
-                return gemm_tc_prefill(a, w, bias, activation, residual, out_dtype, out, kv=kv)
-            return gemm_tc_prefill(a, w, bias, activation, residual, out_dtype, out)
-        return gemm_tc(a, w, bias, activation, residual, out_dtype, out)
-    return gemm_simt(a, w, bias, activation, residual, out_dtype, out)
+    lib = _ready()
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or a.dtype != w.dtype or not a.is_contiguous() or not w.is_contiguous():
+        raise KernelError(f"linear: operands do not fit: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}")
+    out_dtype = out_dtype or a.dtype
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    elif tuple(out.shape) != (M, N) or out.dtype != out_dtype or not out.is_contiguous():
+        raise KernelError("linear: out must be a contiguous [M, N] tensor of the output dtype")
+    for name, t in (("bias", bias), ("residual", residual)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError(f"{name} must be contiguous float32")
+    if residual is not None and tuple(residual.shape) != (M, N):
+        raise KernelError("residual must have the output's shape")
+    target, filed = None, ctypes.c_int(0)
+    if kv is not None and kv.fits(N, out_dtype):
+        target = _KvTarget(kv.kcache.data_ptr(), kv.vcache.data_ptr(), _i32(kv.row_req, "row_req").data_ptr(),
+                           _i32(kv.positions, "positions").data_ptr(), _i32(kv.table, "table").data_ptr(),
+                           kv.table.stride(0), kv.kcache.shape[1], kv.col0, kv.width, _tag(kv.kcache.dtype))
+    _launch(lib.ayk_linear(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), ctypes.c_int(M), ctypes.c_int(N),
+                           ctypes.c_int(K), ctypes.c_int(ACTIVATIONS[activation]), ctypes.c_int(_tag(a.dtype)),
+                           ctypes.c_int(_tag(out_dtype)), ctypes.byref(target) if target is not None else None,
+                           ctypes.byref(filed), _stream()))
+    if kv is not None and filed.value:
+        kv.done = True
+    return out
 
 
 DECODE_PART = 128

@@ -74,4 +74,19 @@ class Attention(Mixer):
                           out_dtype=torch.float32, out=residual)
 
 
+    def lower(self, builder, h, residual, cache):
+        from .base import NotLowered
+        if self.position is not None and self.position.rotate_qk is not None:
+            raise NotLowered("queries and keys are turned by the position encoding's own code")
+        filing = (cache, self.q_width, self.kv_width) if cache.writes else None
+        made = builder.linear(h, self.qkv_weight, self.qkv_bias, out_dtype=self.dtype, filing=filing)
+        qkv, slot = made if filing is not None else (made, -1)
+        o = builder.attention(qkv, cache, heads=self.num_heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
+                              scale=self.scale, window=self.window, dtype=self.dtype, filed_slot=slot)
+        builder.release(qkv)
+        out = builder.linear(o, self.out_weight, self.out_bias, residual=residual, out_dtype=torch.float32, out=residual)
+        builder.release(o)
+        return out
+
+
 register_part(Attention.KIND, Attention)

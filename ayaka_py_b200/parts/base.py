@@ -102,6 +102,11 @@ class StateNeed:
 
 # ------------------------------------------------------------------- parts --
 
+class NotLowered(Exception):
+    """A part cannot describe its step as operations of the native step program; the model then
+    runs its steps through ``forward``."""
+
+
 class Part:
     """Base of every part.  Subclasses set ``KIND`` and implement ``tensors``."""
 
@@ -122,6 +127,13 @@ class Part:
         """The model's position encoding, handed to every part of every layer when the
         model is built.  Parts that apply positions themselves (an attention that
         rotates queries and keys) keep it; the default ignores it."""
+
+    def lower(self, builder, *args, **kwargs):
+        """Optional: record what ``forward`` launches as operations of a step program
+        (``engine/program.py``) and return the buffer that holds the result; the arguments
+        mirror ``forward`` with buffers in the place of tensors.  The default says that
+        the part cannot, which keeps its model on ``forward``."""
+        raise NotLowered(type(self).__name__)
 
 
 class Norm(Part):
@@ -193,6 +205,10 @@ class Block:
 
     def forward(self, x: torch.Tensor, ctx, caches: dict) -> torch.Tensor:
         raise NotImplementedError
+
+    def lower(self, builder, x: int, caches: dict) -> int:
+        """Optional, as ``Part.lower``: the arrangement over buffers."""
+        raise NotLowered(type(self).__name__)
 
 
 # -------------------------------------------------------------- registries --

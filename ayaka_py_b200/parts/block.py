@@ -17,5 +17,14 @@ class PreNormBlock(Block):
         x = self.mixer.forward(self.norm1.forward(x, ctx), x, ctx, caches.get("mixer"))
         return self.ffn.forward(self.norm2.forward(x, ctx), x, ctx)
 
+    def lower(self, builder, x, caches):
+        h = self.norm1.lower(builder, x)
+        x = self.mixer.lower(builder, h, x, caches.get("mixer"))
+        builder.release(h)
+        h = self.norm2.lower(builder, x)
+        x = self.ffn.lower(builder, h, x)
+        builder.release(h)
+        return x
+
 
 register_block(PreNormBlock.KIND, PreNormBlock)

@@ -22,5 +22,8 @@ class TokenEmbedding(Embedding):
     def forward(self, ctx, position):
         return ops.embed(ctx.tokens, ctx.positions, self.weight, position.embedding_table())
 
+    def lower(self, builder, position):
+        return builder.embed(self.weight, position.embedding_table())
+
 
 register_part(TokenEmbedding.KIND, TokenEmbedding)

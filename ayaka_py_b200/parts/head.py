@@ -22,5 +22,9 @@ class LMHead(Head):
     def forward(self, h, ctx):
         return ops.linear(h, self.weight, None, out_dtype=torch.float32)
 
+    def lower(self, builder, h):
+        from ..engine.program import LOGITS
+        return builder.linear(h, self.weight, None, out_dtype=torch.float32, out=LOGITS, wanted=True)
+
 
 register_part(LMHead.KIND, LMHead)

@@ -34,5 +34,11 @@ class MLP(FeedForward):
         return ops.linear(u, self.down_weight, self.down_bias, residual=residual,
                           out_dtype=torch.float32, out=residual)
 
+    def lower(self, builder, h, residual):
+        u = builder.linear(h, self.up_weight, self.up_bias, activation=self.activation, out_dtype=self.dtype)
+        out = builder.linear(u, self.down_weight, self.down_bias, residual=residual, out_dtype=torch.float32, out=residual)
+        builder.release(u)
+        return out
+
 
 register_part(MLP.KIND, MLP)

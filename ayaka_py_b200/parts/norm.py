@@ -26,5 +26,8 @@ class LayerNorm(Norm):
     def forward(self, x, ctx, rows=None):
         return ops.layernorm(x, self.weight, self.bias, self.eps, self.dtype, rows=rows)
 
+    def lower(self, builder, x, wanted=False):
+        return builder.layernorm(x, self.weight, self.bias, self.eps, self.width, self.dtype, wanted=wanted)
+
 
 register_part(LayerNorm.KIND, LayerNorm)

@@ -27,9 +27,10 @@ def model_folders(tmp_path_factory):
 
     out = {}
     base = tmp_path_factory.mktemp("models")
-    for tag, cfg, seed in (("A", tiny_models.TINY_A, 11), ("B", tiny_models.TINY_B, 12),
-                           ("C", tiny_models.TINY_C, 13), ("D", tiny_models.TINY_D, 14)):
-        weights = tiny_models.numpy_weights(cfg, seed, scale=4.0, bf16_exact=True)
+    for tag, cfg, seed, scale in (("A", tiny_models.TINY_A, 11, 4.0), ("B", tiny_models.TINY_B, 12, 4.0),
+                                  ("C", tiny_models.TINY_C, 13, 4.0), ("D", tiny_models.TINY_D, 14, 4.0),
+                                  ("E", tiny_models.TINY_E, 15, 2.0)):
+        weights = tiny_models.numpy_weights(cfg, seed, scale=scale, bf16_exact=True)
         folder = tiny_models.write_folder(base / tag, cfg, weights)
         out[tag] = (folder, cfg, weights)
     return out

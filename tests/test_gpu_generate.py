@@ -84,6 +84,30 @@ def test_few_pages_preempt_and_recompute_same_tokens(model_folders):
     tight.engine.cache.assert_clean()
 
 
+def test_few_pages_preempt_and_recompute_in_bfloat16_with_decode_graphs(model_folders):
+    """The same pressure in bfloat16 with pure-decode steps replayed from CUDA graphs: requests are
+    preempted, recompute their prompt and what they had generated through the prompt kernels, and go
+    on decoding from graphs.  Every token is, by the plain model's logits, within bfloat16 rounding of
+    the best one, and all of them arrive."""
+    from ayaka_py_b200 import LLM, SamplingParams, StopCriteria
+    folder, cfg, weights = model_folders["D"]
+    prompts = tiny_models.prompts(cfg, [150, 140, 165, 120], seed=29)
+    stop = StopCriteria(max_tokens=40, ignore_eos=True)
+    tight = LLM(folder, dtype="bfloat16", page_size=16, kv_pages=34, batch_tokens=256, prefill_chunk=128,
+                max_requests=4, decode_graph=True)                       # 528 tokens for up to 820
+    got = tight.generate(prompts, SamplingParams(temperature=0.0), stop)
+    assert tight.engine.scheduler.stats.preemptions > 0 and any(r.preemptions for r in got)
+    assert tight.engine.decode_graphs.launches > 0
+    for p, r in zip(prompts, got):
+        assert len(r.token_ids) == 40 and r.finish_reason == "length"
+        logits = plain_gpt2.forward(cfg, weights, p + r.token_ids)
+        slack = 2 * 0.02 * float(np.abs(logits).max())
+        for i, token in enumerate(r.token_ids):
+            row = logits[len(p) - 1 + i]
+            assert row[token] >= row.max() - slack, (i, token)
+    tight.engine.cache.assert_clean()
+
+
 def test_filters_keep_the_twins_support(model_folders):
     from ayaka_py_b200 import LLM, SamplingParams, StopCriteria
     folder, cfg, weights = model_folders["A"]

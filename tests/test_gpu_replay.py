@@ -16,8 +16,9 @@ import trace_tools
 pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
-LENGTHS = {"A": [5, 17, 40, 75, 128], "B": [1, 9, 33, 64, 120, 201], "C": [37, 90], "D": [3, 130, 260, 77, 401]}
-PAGE = {"A": 16, "B": 8, "C": 16, "D": 16}
+LENGTHS = {"A": [5, 17, 40, 75, 128], "B": [1, 9, 33, 64, 120, 201], "C": [37, 90], "D": [3, 130, 260, 77, 401],
+           "E": [2, 31, 96, 50]}
+PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16}
 
 
 def tolerance(dtype, want):
@@ -71,7 +72,7 @@ def test_each_request_alone_and_whole(tag, dtype, model_folders, oracles):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B", "D"])
+@pytest.mark.parametrize("tag", ["A", "B", "D", "E"])
 def test_last_32_tokens_one_by_one(tag, dtype, model_folders, oracles):
     check(tag, dtype, trace_tools.tail_decoded(oracles[tag][0], 32), model_folders, oracles)
 
@@ -83,7 +84,7 @@ def test_portions_of_changing_size(tag, dtype, model_folders, oracles):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B", "D"])
+@pytest.mark.parametrize("tag", ["A", "B", "D", "E"])
 def test_mixed_with_pages_used_again(tag, dtype, model_folders, oracles):
     for seed in (0, 1):
         trace = trace_tools.mixed(oracles[tag][0], seed=seed)
@@ -358,3 +359,29 @@ def test_request_dropped_midway_and_reopened(tag, dtype, model_folders, oracles)
     assert len(got[f"{first}#0"]) == max(2, int(len(picked[first]) * 0.45))
     bad = trace_tools.first_difference(got, early, tolerance(dtype, want), partial=(f"{first}#0",))
     assert bad is None, f"first life: position {bad[1]} |diff| {bad[2]:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["B", "D"])
+def test_native_step_program_and_python_path_launch_the_same_kernels(tag, dtype, model_folders, oracles, monkeypatch):
+    """A model whose parts can all be lowered runs its steps as one native program; with
+    AYAKA_B200_NATIVE_STEP=0 the same steps go through ``Model.forward``.  Both launch the same kernels
+    with the same arguments, so the logits are equal bit for bit, and so is the count of launches."""
+    from ayaka_py_b200 import ops
+    folder, cfg, _ = model_folders[tag]
+    reqs, want = oracles[tag]
+    trace = trace_tools.mixed(reqs, seed=8) + trace_tools.tail_decoded(dict(list(reqs.items())[:2]), 8)
+    for i, record in enumerate(trace):
+        record["step"] = i
+    results = {}
+    for native in (True, False):
+        monkeypatch.setenv("AYAKA_B200_NATIVE_STEP", "1" if native else "0")
+        before = ops.launches
+        outputs, session = replay(folder, dtype, trace, PAGE[tag])
+        assert (session.runner._program is not None) == native
+        results[native] = (outputs, ops.launches - before)
+    assert results[True][1] == results[False][1] > 0
+    for a, b in zip(results[True][0], results[False][0]):
+        assert (a is None) == (b is None)
+        if a is not None:
+            assert np.array_equal(a, b)

@@ -13,11 +13,11 @@ GOLDEN = np.load(Path(__file__).parent / "golden" / "reference_logits.npz")
 
 
 def test_golden_file_records_agreement():
-    assert float(GOLDEN["A_maxdiff"]) < 1e-5 and float(GOLDEN["B_maxdiff"]) < 1e-5
+    assert all(float(GOLDEN[f"{tag}_maxdiff"]) < 1e-5 for tag in "ABE")
 
 
-def _check(tag, cfg, seed):
-    weights = tiny_models.numpy_weights(cfg, seed, scale=4.0, bf16_exact=False)
+def _check(tag, cfg, seed, scale=4.0):
+    weights = tiny_models.numpy_weights(cfg, seed, scale=scale, bf16_exact=False)
     tokens = GOLDEN[f"{tag}_tokens"].tolist()
     mine = plain_gpt2.forward(cfg, weights, tokens)
     assert mine.shape == GOLDEN[f"{tag}_logits"].shape
@@ -30,6 +30,19 @@ def test_plain_matches_reference_tiny_a():
 
 def test_plain_matches_reference_tiny_b_inverse_layer_scaling():
     _check("B", tiny_models.TINY_B, 12)
+
+
+def test_plain_matches_reference_tiny_e_quick_gelu_unscaled_scores_untied_head():
+    """The options that A and B leave at their defaults, which the reference accepts
+    (``models/gpt2.py:64-66``, ``:147-149``, ``:253-254``)."""
+    _check("E", tiny_models.TINY_E, 15, scale=2.0)
+    cfg, weights = tiny_models.TINY_E, tiny_models.numpy_weights(tiny_models.TINY_E, 15, scale=2.0, bf16_exact=False)
+    tokens = GOLDEN["E_tokens"].tolist()
+    tied = plain_gpt2.forward({**cfg, "tie_word_embeddings": True}, weights, tokens)
+    scaled = plain_gpt2.forward({**cfg, "scale_attn_weights": True}, weights, tokens)
+    gelu = plain_gpt2.forward({**cfg, "activation_function": "gelu_new"}, weights, tokens)
+    for other in (tied, scaled, gelu):                         # each option moves the logits: none is ignored
+        assert np.abs(other - GOLDEN["E_logits"]).max() > 1e-3
 
 
 def test_float64_and_float32_agree():

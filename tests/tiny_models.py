@@ -41,6 +41,16 @@ TINY_C = {
 }
 
 
+# The options that A and B leave at their defaults: quick_gelu, unscaled scores, a head of its own.
+TINY_E = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 2, "n_embd": 48, "n_head": 3, "n_inner": 100, "vocab_size": 130,
+    "n_positions": 96, "layer_norm_epsilon": 1e-5, "activation_function": "quick_gelu",
+    "scale_attn_weights": False, "scale_attn_by_inverse_layer_idx": False,
+    "tie_word_embeddings": False,
+}
+
+
 # Head size 64 (the tensor-core attention kernel's), three heads, width 192.
 TINY_D = {
     "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
@@ -71,6 +81,8 @@ def tensor_shapes(cfg: dict) -> dict[str, tuple]:
         shapes[p + "mlp.c_proj.bias"] = (d,)
     shapes["transformer.ln_f.weight"] = (d,)
     shapes["transformer.ln_f.bias"] = (d,)
+    if not cfg.get("tie_word_embeddings", True):
+        shapes["lm_head.weight"] = (V, d)
     return shapes
 
 

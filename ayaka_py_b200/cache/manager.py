@@ -271,31 +271,41 @@ class CacheManager:
                 raise ValueError(f"slot {slot}: entry starts at {start}, the cache holds {self.length[slot]} tokens")
             if start + count > self.max_len:
                 raise ValueError(f"slot {slot}: {start + count} tokens exceed the limit of {self.max_len}")
-        needs = self.pages_needed(entries)
+        # pages that each entry's last token needs, against the pages its request has (all entries at once)
+        slots_a = np.fromiter((e[0] for e in entries), dtype=np.int64, count=len(entries))
+        end_pages = -(-np.fromiter((e[1] + e[2] for e in entries), dtype=np.int64, count=len(entries)) // self.page_size)
+        news = []
         for g, pool in enumerate(self.pools):
-            if pool is not None and needs[g] > len(pool.free):
-                raise OutOfPages(self.groups[g].name, needs[g], len(pool.free))
+            if pool is None:
+                news.append(None)
+                continue
+            new = np.maximum(0, end_pages - self.num_pages[g][slots_a])
+            need = int(new.sum())
+            if need > len(pool.free):
+                raise OutOfPages(self.groups[g].name, need, len(pool.free))
+            news.append(new)
         res = Reservation(entries)
         for g, pool in enumerate(self.pools):
             taken = []
             if pool is not None:
-                for slot, start, count in entries:
-                    have, new = self._first_and_new(g, slot, start, count)
-                    for logical in range(have, have + new):
+                for i in np.flatnonzero(news[g]):          # most decode entries need no new page
+                    slot = int(slots_a[i])
+                    have = int(self.num_pages[g][slot])
+                    for logical in range(have, have + int(news[g][i])):
                         page = pool.take(slot)
                         self.tables[g][slot, logical] = page
                         taken.append((slot, logical, page))
-                    self.num_pages[g][slot] = have + new
+                    self.num_pages[g][slot] = have + int(news[g][i])
             res.taken.append(taken)
-        for slot, _, _ in entries:
-            self.in_step[slot] = True
+        self.in_step[slots_a] = True
         return res
 
     def commit(self, res: Reservation) -> None:
         """The step ran: lengths advance; pages that a window has passed return."""
         self._settle(res)
-        for slot, start, count in res.entries:
-            self.length[slot] = start + count
+        if res.entries:
+            slots_a = np.fromiter((e[0] for e in res.entries), dtype=np.int64, count=len(res.entries))
+            self.length[slots_a] = np.fromiter((e[1] + e[2] for e in res.entries), dtype=np.int64, count=len(res.entries))
         for g, group in enumerate(self.groups):
             if self.pools[g] is None or group.need.window is None:
                 continue
@@ -321,8 +331,8 @@ class CacheManager:
         if res.settled:
             raise RuntimeError("this step was already committed or rolled back")
         res.settled = True
-        for slot, _, _ in res.entries:
-            self.in_step[slot] = False
+        if res.entries:
+            self.in_step[[e[0] for e in res.entries]] = False
 
     # ---------------------------------------------------------------- views --
     def table_rows(self, g: int, slots) -> np.ndarray:

@@ -104,14 +104,16 @@ class Engine:
                                  [0] * e.count if ahead else e.state.tokens[e.start:e.start + e.count],
                                  [e.count - 1] if e.sample else []) for e in plan.entries]
             rows = [e.state for e in plan.entries if e.sample]
+            take = plan.token_rows if ahead else None
             if self.decode_graphs is not None and plan.decode_only:
-                logits = self.decode_graphs.run(entries, tokens_from=tokens_from)
+                logits = self.decode_graphs.run(entries, tokens_from=tokens_from, take_rows=take)
             else:
-                logits = self.runner.run(entries, tokens_from=tokens_from)
+                logits = self.runner.run(entries, tokens_from=tokens_from, take_rows=take)
             sampled = host = done = None
             if rows:
                 pending = 1 if ahead else 0         # a token of each row is still on its way
-                banned = [(i, t) for i, s in enumerate(rows) for t in self.scheduler.banned_tokens(s, pending)]
+                banned = ([(i, t) for i, s in enumerate(rows) for t in self.scheduler.banned_tokens(s, pending)]
+                          if self.scheduler.with_min_tokens else ())
                 sampled = self.sampler.sample(logits, [s.request.sampling for s in rows], [s.seed for s in rows],
                                               [s.generated + pending for s in rows], banned=banned)
                 host = self._pinned.pop() if self._pinned else None

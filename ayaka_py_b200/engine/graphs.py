@@ -49,7 +49,7 @@ class DecodeGraphs:
         self.graphs[bucket] = entry
         return entry
 
-    def run(self, entries: list[StepEntry], tokens_from: torch.Tensor | None = None) -> torch.Tensor:
+    def run(self, entries: list[StepEntry], tokens_from: torch.Tensor | None = None, take_rows=None) -> torch.Tensor:
         """Logits [len(entries), V] of a step whose entries all bring one token
         and want its logits.  ``tokens_from``: int32 on the device, the entries'
         tokens in order (their host copies are not known yet): they are copied into
@@ -61,9 +61,9 @@ class DecodeGraphs:
         bucket = self.bucket_for(n)
         entry = self.graphs.get(bucket) or self._capture(bucket)
         graph, logits, kernels = entry
-        ctx = self.runner.prepare(entries, pad_to=bucket)
+        ctx = self.runner.prepare(entries, pad_to=bucket, take_rows=take_rows)
         if tokens_from is not None:
-            ctx.tokens[:n].copy_(tokens_from[:n])
+            self.runner.place_tokens(ctx, n, tokens_from, take_rows)
         self.h2d_bytes = self.runner.h2d_bytes
         graph.replay()
         self.launches += kernels

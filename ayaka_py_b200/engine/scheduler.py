@@ -67,7 +67,8 @@ class ScheduledEntry:
     @property
     def is_decode(self) -> bool:
         """One token of a request whose other tokens are all cached."""
-        return self.state.remaining == 1 and self.state.computed > 0
+        state = self.state
+        return len(state.tokens) - state.computed == 1 and state.computed > 0
 
 
 @dataclass
@@ -75,6 +76,9 @@ class ScheduledStep:
     entries: list[ScheduledEntry]
     reservation: Reservation
     decode_only: bool
+    # A step planned ahead of the tokens of the step before it: for each entry, the row of that
+    # step's sampled tokens that is this entry's token (None: the same rows in the same order).
+    token_rows: list[int] | None = None
 
 
 @dataclass
@@ -106,6 +110,7 @@ class Scheduler:
         self.cursor = 0
         self.ordinal = 0
         self.stats = SchedulerStats()
+        self.with_min_tokens = 0          # live requests that ask for a minimum of tokens (their stop ids are banned at first)
 
     # ------------------------------------------------------------ admission --
     def add(self, request: Request) -> RequestState:
@@ -135,6 +140,8 @@ class Scheduler:
         self.ordinal += 1
         self.states[request.request_id] = state
         self.waiting.append(state)
+        if request.stop.min_tokens > 0:
+            self.with_min_tokens += 1
         return state
 
     def has_work(self) -> bool:
@@ -163,7 +170,7 @@ class Scheduler:
         entries: list[ScheduledEntry] = []
 
         # 1. decoding first, round robin from the cursor
-        decoders = [s for s in self.running if s.remaining == 1 and s.computed > 0]
+        decoders = [s for s in self.running if len(s.tokens) - s.computed == 1 and s.computed > 0]
         if decoders:
             if len(decoders) > budget:          # not all fit: take turns
                 start = self.cursor % len(decoders)
@@ -174,7 +181,7 @@ class Scheduler:
                 budget -= 1
 
         # 2. prompt portions: the unfinished prompt first, then waiting requests
-        partial = [s for s in self.running if s.remaining > 1 or s.computed == 0]
+        partial = [s for s in self.running if len(s.tokens) - s.computed > 1 or s.computed == 0]
         for s in partial:
             if budget < 1:
                 break
@@ -227,13 +234,10 @@ class Scheduler:
         if not entries:
             return None
         self.stats.steps += 1
-        decode_only = all(e.is_decode for e in entries)
-        for e in entries:
-            if e.is_decode:
-                self.stats.decode_tokens += 1
-            else:
-                self.stats.prefill_tokens += e.count
-        return ScheduledStep(entries, reservation, decode_only)
+        decoding = sum(1 for e in entries if e.is_decode)
+        self.stats.decode_tokens += decoding
+        self.stats.prefill_tokens += sum(e.count for e in entries) - decoding
+        return ScheduledStep(entries, reservation, decoding == len(entries))
 
     def _pick_victim(self, entries) -> RequestState | None:
         """The newest running request that holds pages; never the only one."""
@@ -286,32 +290,39 @@ class Scheduler:
 
     def lookahead(self, step: ScheduledStep) -> ScheduledStep | None:
         """The step after ``step``, planned before ``step``'s tokens are known, or
-        None when that cannot be done without guessing more than "nobody stops":
-        ``step`` (already advanced) must be a pure decode step of every running
-        request, nobody waits, nobody reaches a length limit with the token that is
-        on its way, and the pages are there.  A request that stops on the token on
-        its way (EOS, a stop id) has then one more token computed than it needed;
-        ``resolve`` drops it.  The reference keeps one step in flight
-        (``configs/scheduler.py:131``); this is the same loop with the host's share
-        of the next step done while the GPU works on this one."""
+        None when that cannot be done without guessing more than "nobody stops on a
+        stop id": ``step`` (already advanced) must be a pure decode step of every
+        running request, nobody waits, and the pages are there.  A request that
+        reaches a length limit with the token on its way is known to finish: it is
+        left out of the next step (its token is its last) and the others go on.  A
+        request that stops on the token on its way (EOS, a stop id) has then one
+        more token computed than it needed; ``resolve`` drops it.  The reference
+        keeps one step in flight (``configs/scheduler.py:131``); this is the same
+        loop with the host's share of the next step done while the GPU works on
+        this one."""
         if not step.decode_only or self.waiting or len(step.entries) != len(self.running):
             return None
         if len(step.entries) > self.batch_tokens:
             return None
-        for e, s in zip(step.entries, self.running):
-            if e.state is not s or not e.sample or s.finish_reason is not None or s.remaining != 0:
+        rows, going_on = [], []
+        for row, (e, s) in enumerate(zip(step.entries, self.running)):
+            if e.state is not s or not e.sample or s.finish_reason is not None or len(s.tokens) != s.computed:
                 return None
             stop = s.request.stop
             if s.generated + 1 >= stop.max_tokens or len(s.tokens) + 1 >= self.max_model_len:
-                return None                        # finishes by length when its token arrives
-        entries = [ScheduledEntry(s, s.computed, 1, True) for s in self.running]
+                continue                           # finishes by length when its token arrives: not in the next step
+            rows.append(row)
+            going_on.append(s)
+        if not going_on:
+            return None
+        entries = [ScheduledEntry(s, s.computed, 1, True) for s in going_on]
         try:
             reservation = self.cache.reserve([(e.state.slot, e.start, 1) for e in entries])
         except OutOfPages:
             return None
         self.stats.steps += 1
         self.stats.decode_tokens += len(entries)
-        return ScheduledStep(entries, reservation, True)
+        return ScheduledStep(entries, reservation, True, None if len(rows) == len(step.entries) else rows)
 
     def banned_tokens(self, s: RequestState, pending: int = 0) -> tuple[int, ...]:
         """Token ids that ``s`` must not sample next: its stop ids, and EOS unless it
@@ -350,6 +361,8 @@ class Scheduler:
         if s in self.waiting:
             self.waiting.remove(s)
         del self.states[s.request.request_id]
+        if s.request.stop.min_tokens > 0:
+            self.with_min_tokens -= 1
 
     def abort(self, request_id: str) -> RequestState | None:
         s = self.states.get(request_id)

@@ -53,6 +53,7 @@ class StepContext:
     req_pos0: torch.Tensor       # [R] position of each request's first row
     req_slot: torch.Tensor       # [R] cache slot of each request
     req_kv_len: torch.Tensor     # [R] tokens cached after this step
+    take_rows: torch.Tensor      # [R] for a step whose tokens come from another step's sampled rows: which row each takes
     tables: list                 # per cache group: [R, columns] block-table rows, or None
     cache: CacheManager
     dtype: torch.dtype
@@ -94,7 +95,7 @@ class StepRunner:
         """Offsets of the step's fields, packed back to back (16-byte aligned),
         so that one copy of ``total`` ints brings exactly what the step needs."""
         sizes = {"tokens": T, "positions": T, "row_req": T, "want_rows": S,
-                 "req_q_start": R + 1, "req_pos0": R, "req_slot": R, "req_kv_len": R}
+                 "req_q_start": R + 1, "req_pos0": R, "req_slot": R, "req_kv_len": R, "take_rows": R}
         for g in self.kv_groups:
             sizes[f"table{g}"] = R * self.cache.columns
         offsets, total = {}, 0
@@ -107,7 +108,8 @@ class StepRunner:
         lo, cap = self.offsets[name]
         return buf[lo:lo + n]
 
-    def prepare(self, entries: Sequence[StepEntry], pad_to: int | None = None) -> StepContext:
+    def prepare(self, entries: Sequence[StepEntry], pad_to: int | None = None,
+                take_rows: Sequence[int] | None = None) -> StepContext:
         """Validates, packs and uploads a step.  ``pad_to``: for a pure-decode
         step, add padding lanes up to that many requests (position 0, the
         padding page, the spare state slot, token 0): they read nothing that
@@ -121,11 +123,14 @@ class StepRunner:
         if R > max(self.max_requests, pad_to or 0):
             raise ValueError(f"{R} requests in one step, the engine was built for {self.max_requests}")
         # single-token entries first (stable): packed place -> index in ``entries``
-        order = sorted(range(n), key=lambda i: len(entries[i].tokens) != 1)
-        given = entries
-        entries = [given[i] for i in order]
+        lengths = [len(e.tokens) for e in entries]
+        if all(k == 1 for k in lengths):
+            order = list(range(n))
+        else:
+            order = sorted(range(n), key=lambda i: lengths[i] != 1)
+            entries = [entries[i] for i in order]
         counts = np.ones(R, dtype=np.int64)
-        counts[:n] = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=n)
+        counts[:n] = [lengths[i] for i in order]
         if (counts < 1).any():
             raise ValueError("every entry must bring at least one token")
         if pad_to and (counts != 1).any():
@@ -135,22 +140,27 @@ class StepRunner:
             self.max_requests = max(R, self.max_requests)
             self._allocate(max(T, 2 * self.max_tokens))
         slots = np.full(R, self.cache.max_requests, dtype=np.int64)        # padding lanes: the spare slot
-        slots[:n] = np.fromiter((e.slot for e in entries), dtype=np.int64, count=n)
-        if len(set(slots[:n].tolist())) != n:
-            raise ValueError("a request appears twice in one step")
+        slots[:n] = [e.slot for e in entries]
         starts = np.zeros(R, dtype=np.int64)
-        starts[:n] = np.fromiter((e.start for e in entries), dtype=np.int64, count=n)
+        starts[:n] = [e.start for e in entries]
         ends = starts + counts
-        for e in entries:
-            if e.slot not in self.cache.request_of or not self.cache.in_step[e.slot]:
-                raise RuntimeError(f"slot {e.slot} was not reserved for this step")
-            if e.start != self.cache.length[e.slot]:
-                raise ValueError(f"slot {e.slot}: entry starts at {e.start}, the cache holds {self.cache.length[e.slot]}")
+        live = slots[:n]
+        if n:
+            if live.min() < 0 or live.max() >= self.cache.max_requests or len(np.unique(live)) != n:
+                raise ValueError("a request appears twice in one step, or a slot that does not exist")
+            if not self.cache.in_step[live].all():          # only open slots of a reserved step are marked
+                bad = int(live[~self.cache.in_step[live]][0])
+                raise RuntimeError(f"slot {bad} was not reserved for this step")
+            wrong = starts[:n] != self.cache.length[live]
+            if wrong.any():
+                i = int(np.flatnonzero(wrong)[0])
+                raise ValueError(f"slot {int(live[i])}: entry starts at {int(starts[i])}, the cache holds {int(self.cache.length[live[i]])}")
         limit = self.model.max_positions
         if int(ends.max()) > limit:
             raise ValueError(f"a request would reach {int(ends.max())} tokens, the model has {limit} positions")
 
-        S = sum(len(e.want) for e in entries) + (R - n)
+        want_counts = [len(e.want) for e in entries]
+        S = sum(want_counts) + (R - n)
         self.offsets, total = self._layout(T, R, S)
         h = self.host_np
         q_start = np.zeros(R + 1, dtype=np.int64)
@@ -158,17 +168,22 @@ class StepRunner:
         tok = self._field(h, "tokens", T)
         pos = self._field(h, "positions", T)
         row_req = self._field(h, "row_req", T)
+        # rows of the live entries, packed: tokens in order, positions = start + place within the entry
+        live_rows = int(q_start[n])
+        if live_rows:
+            tok[:live_rows] = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=live_rows)
+            of_row = np.repeat(np.arange(n, dtype=np.int64), counts[:n])
+            row_req[:live_rows] = of_row
+            pos[:live_rows] = starts[of_row] + (np.arange(live_rows, dtype=np.int64) - q_start[of_row])
         wanted_of = [None] * n          # by place in the caller's list: the logits keep the caller's order
         for r, e in enumerate(entries):
-            a, b = int(q_start[r]), int(q_start[r + 1])
-            tok[a:b] = np.asarray(e.tokens, dtype=np.int64)
-            pos[a:b] = np.arange(e.start, e.start + (b - a))
-            row_req[a:b] = r
-            for w in e.want:
-                if not 0 <= w < b - a:
-                    raise ValueError(f"want {w} is outside the entry's {b - a} tokens")
-            wanted_of[order[r]] = [a + int(w) for w in e.want]
-        wanted = [row for rows in wanted_of for row in rows]
+            if want_counts[r]:
+                a, width = int(q_start[r]), int(counts[r])
+                for w in e.want:
+                    if not 0 <= w < width:
+                        raise ValueError(f"want {w} is outside the entry's {width} tokens")
+                wanted_of[order[r]] = [a + int(w) for w in e.want]
+        wanted = [row for rows in wanted_of if rows for row in rows]
         for r in range(n, R):                      # padding lanes
             a = int(q_start[r])
             tok[a], pos[a], row_req[a] = 0, 0, r
@@ -180,6 +195,10 @@ class StepRunner:
         self._field(h, "req_pos0", R)[:] = starts
         self._field(h, "req_slot", R)[:] = slots
         self._field(h, "req_kv_len", R)[:] = ends
+        if take_rows is not None:
+            if len(take_rows) != n or T != R:
+                raise ValueError("rows of another step's tokens can be named only for entries of one token each")
+            self._field(h, "take_rows", R)[:n] = take_rows
         C = self.cache.columns
         for g in self.kv_groups:
             rows = self._field(h, f"table{g}", R * C).reshape(R, C)
@@ -203,6 +222,7 @@ class StepRunner:
             row_req=self._field(d, "row_req", T), want_rows=self._field(d, "want_rows", S),
             req_q_start=self._field(d, "req_q_start", R + 1), req_pos0=self._field(d, "req_pos0", R),
             req_slot=self._field(d, "req_slot", R), req_kv_len=self._field(d, "req_kv_len", R),
+            take_rows=self._field(d, "take_rows", R),
             tables=tables, cache=self.cache, dtype=self.model.dtype,
             host={"q_start": q_start, "pos0": starts, "slots": slots, "kv_len": ends, "counts": counts,
                   "order": np.asarray(order + list(range(n, R)), dtype=np.int64)},   # packed place -> caller's index
@@ -221,14 +241,23 @@ class StepRunner:
             return self._program.run(ctx)
         return self.model.forward(ctx)
 
-    def run(self, entries: Sequence[StepEntry], tokens_from: torch.Tensor | None = None) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], tokens_from: torch.Tensor | None = None,
+            take_rows: Sequence[int] | None = None) -> torch.Tensor:
         """Logits [S, V] float32 on the device.  The caller has reserved the
         step in the cache manager and commits it afterwards.  ``tokens_from``
-        (int32 on the device, one token per entry): the tokens of a step of single
-        tokens whose host copies are not known yet."""
-        ctx = self.prepare(entries)
+        (int32 on the device): the tokens of a step of single tokens whose host copies
+        are not known yet, entry i taking row ``take_rows[i]`` of it (None: row i)."""
+        ctx = self.prepare(entries, take_rows=take_rows)
         if tokens_from is not None:
-            if ctx.num_rows != len(entries):      # then the packed order is the caller's order
-                raise ValueError("tokens can come from the device only for entries of one token each")
-            ctx.tokens[:len(entries)].copy_(tokens_from[:len(entries)])
+            self.place_tokens(ctx, len(entries), tokens_from, take_rows)
         return self.forward(ctx)
+
+    @staticmethod
+    def place_tokens(ctx: StepContext, n: int, tokens_from: torch.Tensor, take_rows) -> None:
+        """Copies the step's tokens on the device from the sampled tokens of the step before."""
+        if ctx.num_rows != ctx.num_requests:      # then the packed order is the caller's order
+            raise ValueError("tokens can come from the device only for entries of one token each")
+        if take_rows is None:
+            ctx.tokens[:n].copy_(tokens_from[:n])
+        else:
+            torch.index_select(tokens_from, 0, ctx.take_rows[:n], out=ctx.tokens[:n])

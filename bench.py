@@ -231,16 +231,17 @@ def run_prefill(engine, config, repeats: int = 3):
 def run_small_continuous(layers: int | None = None, requests: int = 256, seed: int = 5):
     """GPT-2 small shape, 256 requests at t = 0 through ``LLM.generate``: prompts U[16,1024],
     outputs U[16,256] (cut where prompt + output would pass the model's 1,024 positions),
-    chunked prefill under a 2,048-token step budget, greedy.  The cache holds 8,192 pages of
-    16 tokens: less than the 256 requests need at their longest, so pages run out and
-    come back."""
+    chunked prefill under a 2,048-token step budget, greedy.  The cache holds 6,144 pages of
+    16 tokens: less than the 256 requests need at their longest (about 7,500), so pages run
+    out, requests are preempted and recompute, and pages come back."""
     import numpy as np
     import torch
 
     from ayaka_py_b200 import LLM, GPT2Config, SamplingParams, StopCriteria
 
     config = GPT2Config(**{**SMALL, "n_layer": layers or SMALL["n_layer"]})
-    llm = LLM(config, seed=3, dtype="bfloat16", kv_pages=8192, page_size=16, max_requests=requests,
+    pages = 6144
+    llm = LLM(config, seed=3, dtype="bfloat16", kv_pages=pages, page_size=16, max_requests=requests,
               batch_tokens=2048, prefill_chunk=2048, decode_graph=True)
     rs = np.random.RandomState(seed)
     prompts, stops = [], []
@@ -251,8 +252,9 @@ def run_small_continuous(layers: int | None = None, requests: int = 256, seed: i
         out = min(out, config.n_positions - n)
         prompts.append(rs.randint(0, config.vocab_size, n).tolist())
         stops.append(StopCriteria(max_tokens=out, ignore_eos=True))
-    warm = llm.generate(prompts[:4], SamplingParams(temperature=0.0), [StopCriteria(max_tokens=4, ignore_eos=True)] * 4)
-    assert len(warm) == 4
+    # once untimed (the decode graphs of every batch bucket are captured on the way), then timed
+    warm = llm.generate(prompts, SamplingParams(temperature=0.0), stops)
+    assert len(warm) == requests
     engine = llm.engine
     steps0 = engine.steps_run
     stats0 = engine.scheduler.stats
@@ -272,7 +274,7 @@ def run_small_continuous(layers: int | None = None, requests: int = 256, seed: i
     return {"total_tok_s": (prompt_tokens + generated) / seconds, "output_tok_s": generated / seconds,
             "seconds": seconds, "steps": stats.steps - base[0], "preemptions": stats.preemptions - base[1],
             "computed_prompt_tokens": stats.prefill_tokens - base[2], "prompt_tokens": prompt_tokens,
-            "generated": generated, "page_high_water": high, "pages": 8191,
+            "generated": generated, "page_high_water": high, "pages": pages - 1,
             "engine_steps": engine.steps_run - steps0}
 
 

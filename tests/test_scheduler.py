@@ -259,28 +259,57 @@ def test_lookahead_gives_the_same_tokens_and_reasons(seed):
 
 def test_lookahead_refuses_what_it_cannot_know():
     sched, cache = make(pages=20, page_size=4, max_requests=4, batch_tokens=8)
-    sched.add(req(0, 3, max_tokens=4))
+    sched.add(req(0, 3, max_tokens=5))
     sched.add(req(1, 2, max_tokens=2))
     plan = sched.schedule()                        # both prompts: not a decode step
     sched.advance(plan)
     assert sched.lookahead(plan) is None
     sched.resolve(plan, {"r0": 7, "r1": 7})
     plan = sched.schedule()                        # decode step; r1 reaches max_tokens with the token on its way
-    assert plan.decode_only
+    assert plan.decode_only and [e.state.request.request_id for e in plan.entries] == ["r0", "r1"]
     sched.advance(plan)
-    assert sched.lookahead(plan) is None
+    ahead = sched.lookahead(plan)                  # ... so it is left out of the next step, and r0 takes row 0 of the tokens
+    assert ahead is not None and [e.state.request.request_id for e in ahead.entries] == ["r0"]
+    assert ahead.token_rows == [0] and [(e.start, e.count) for e in ahead.entries] == [(4, 1)]
+    sched.advance(ahead)
     done = sched.resolve(plan, {"r0": 7, "r1": 7})
     assert [s.request.request_id for s in done] == ["r1"]
+    cache.check_invariants()
+    sched.resolve(ahead, {"r0": 7})
     plan = sched.schedule()
     sched.advance(plan)
-    ahead = sched.lookahead(plan)                  # r0 alone, two tokens to go
-    assert ahead is not None and [(e.start, e.count) for e in ahead.entries] == [(5, 1)]
+    ahead = sched.lookahead(plan)                  # r0 alone, two tokens to go: the same rows, no map
+    assert ahead is not None and [(e.start, e.count) for e in ahead.entries] == [(6, 1)] and ahead.token_rows is None
     sched.advance(ahead)
     sched.add(req(2, 2))                           # somebody waits now: no further lookahead
     sched.resolve(plan, {"r0": 7})
     assert sched.lookahead(ahead) is None
     sched.resolve(ahead, {"r0": 7})
     assert "r0" not in sched.states
+
+
+def test_lookahead_leaves_out_every_request_that_finishes_by_length():
+    """Three decoding requests of which the middle one and then the last reach max_tokens: the steps
+    planned ahead name the rows of the sampled tokens that the survivors take."""
+    sched, cache = make(pages=40, page_size=4, max_requests=4, batch_tokens=8)
+    for i, limit in enumerate([9, 3, 5]):
+        sched.add(req(i, 2, max_tokens=limit))
+    plan = sched.schedule()
+    sched.update(plan, {"r0": 7, "r1": 7, "r2": 7})
+    plan = sched.schedule()
+    sched.advance(plan)
+    seen = []
+    for _ in range(4):
+        ahead = sched.lookahead(plan)
+        assert ahead is not None
+        seen.append(([e.state.request.request_id for e in ahead.entries], ahead.token_rows))
+        sched.advance(ahead)
+        sched.resolve(plan, {e.state.request.request_id: 7 for e in plan.entries})
+        cache.check_invariants()
+        plan = ahead
+    assert seen == [(["r0", "r1", "r2"], None), (["r0", "r2"], [0, 2]), (["r0", "r2"], None), (["r0"], [0])]
+    sched.resolve(plan, {"r0": 7})
+    assert sorted(sched.states) == ["r0"]
 
 
 @pytest.mark.parametrize("block", range(6))

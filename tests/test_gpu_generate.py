@@ -135,6 +135,16 @@ def test_command_line(model_folders, tmp_path):
     assert record["finish_reason"] == "length"
 
 
+def test_command_line_bench(model_folders):
+    folder, cfg, _ = model_folders["D"]
+    proc = subprocess.run(
+        [sys.executable, "-m", "ayaka_py_b200", "bench", str(folder), "--batch", "3", "--prompt-len", "40", "--steps", "6",
+         "--warmup", "3", "--kv-pages", "8"], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    record = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert record["batch"] == 3 and record["steps"] == 6 and record["decode_tokens_per_s"] > 0 and record["prompt_tokens_per_s"] > 0
+
+
 def test_smoke_entry():
     sys.path.insert(0, str(ROOT))
     import __graft_entry__

@@ -31,8 +31,8 @@ __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, flo
 
 template <typename TA, typename TW, typename TO, bool VEC>
 __global__ void __launch_bounds__(256)
-gemm_simt_kernel(TO* __restrict__ C, const TA* __restrict__ A, const TW* __restrict__ W,
-                 const float* __restrict__ bias, const float* __restrict__ residual,
+gemm_simt_kernel(TO* C, const TA* __restrict__ A, const TW* __restrict__ W,
+                 const float* __restrict__ bias, const float* residual,      // C and residual may be one buffer (the residual stream in place)
                  int M, int N, int K, int act) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];

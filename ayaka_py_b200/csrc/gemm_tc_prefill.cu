@@ -23,6 +23,7 @@
 #include <cstdlib>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 #include "common.cuh"
 #include "tcgen05.cuh"
@@ -56,6 +57,15 @@ struct PrefillArgs {
   const int* kv_pos;         // [M] the row's position
   const int* kv_table;       // [requests, kv_table_stride] pages
   int kv_table_stride, kv_page_size, kv_col0, kv_width;
+  // Split along K (one-SM form, when the tiles alone would leave most SMs idle): `splits` CTAs share a tile,
+  // each running an equal part of its K blocks.  Every CTA leaves its sums in its slot of `sk_ws` (128 x BN
+  // floats, column by column) and raises `sk_ready[cta]`; then each of the CTAs adds up, in the CTAs' order,
+  // the BN / splits columns that are its share and finishes them (bias, activation, residual, store).  The last of
+  // a tile's CTAs to finish (counted in `sk_done`) clears the tile's flags for the next launch.
+  int splits;
+  float* sk_ws;
+  int* sk_ready;
+  int* sk_done;
 };
 
 // Where the keys of row `row` go: element offset of the row's place in a cache tensor, or -1 (a row
@@ -82,19 +92,21 @@ __device__ __forceinline__ void epilogue_chunk(const PrefillArgs& a, uint32_t ta
   if (W == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
   const size_t idx = (size_t)row * a.N + n;
   const bool out_bf16 = MODE == 3 ? a.out_bf16 != 0 : MODE != 1;       // modes 0, 2 and 4 store bfloat16
-  if (a.vec_ok && n + W <= a.N) {
+  if (a.vec_ok) {            // N is a multiple of 8: every group of 8 columns lies inside the matrix or outside
     const bool with_res = (MODE == 1 || MODE == 3) && a.residual != nullptr && row_ok;
     float4 res[(MODE == 1 || MODE == 3) ? W / 4 : 1];
     if (MODE == 1 || MODE == 3) {
       if (with_res) {     // every load of the chunk before its first store: the residual may be C itself
 #pragma unroll
-        for (int j = 0; j < W / 4; ++j) res[j] = *reinterpret_cast<const float4*>(a.residual + idx + 4 * j);
+        for (int j = 0; j < W / 4; ++j)
+          if (n + 4 * j < a.N) res[j] = *reinterpret_cast<const float4*>(a.residual + idx + 4 * j);
       }
     }
     tmem_ld_wait();
     if (!row_ok) return;
 #pragma unroll
     for (int j = 0; j < W; j += 8) {
+      if (n + j >= a.N) break;
       float y[8];
 #pragma unroll
       for (int u = 0; u < 8; u += 4) {
@@ -170,6 +182,89 @@ __device__ __forceinline__ void epilogue_row_any(const PrefillArgs& a, uint32_t 
   else epilogue_row<3>(a, taddr, row, n, cols, row_ok, place);
 }
 
+// The raw sums of `cols` columns of one accumulator row (cols a multiple of 16) into a slot of the split
+// form.  A slot holds a tile column by column, 128 rows each: a thread owns a row, so the 32 threads of a
+// warp write (and later read) 128 contiguous bytes per column.  `dst`: the row's place in the first column.
+__device__ __forceinline__ void store_partial_row(uint32_t taddr, float* dst, int cols) {
+  int c = 0;
+  for (; c + 32 <= cols; c += 32) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dst[(c + j) * BM] = __uint_as_float(r[j]);
+  }
+  if (c < cols) {
+    uint32_t r[16];
+    tmem_ld16(taddr + c, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) dst[(c + j) * BM] = __uint_as_float(r[j]);
+  }
+}
+
+// This CTA's share of a tile whose K blocks were split over `splits` CTAs: `cols` columns (a multiple of 8)
+// from column `c0` of the tile on, for the row `row_in_tile`, summed over the CTAs' slots (`slots` is the
+// first CTA's; in the CTAs' order, so every run adds alike) and finished eight columns at a time.
+__device__ __forceinline__ void finish_split_cols(const PrefillArgs& a, const float* slots, int splits, int BN, int m0, int n0,
+                                                  int row_in_tile, int c0, int cols) {
+  const int row = m0 + row_in_tile;
+  if (row >= a.M) return;
+  const long long slot_floats = (long long)BM * BN;
+  const long long place = cache_place(a, row);
+  for (int c = c0; c < c0 + cols; c += 8) {
+    const int col = n0 + c;
+    if (col >= a.N) break;                         // N is a multiple of 8: a group lies inside the matrix or outside
+    const float* src = slots + (long long)c * BM + row_in_tile;
+    float y[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = __ldcg(src + j * BM);
+    for (int p = 1; p < splits; ++p) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + p * slot_floats + j * BM);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] += v[j];
+    }
+    if (a.bias) {
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(a.bias + col)), b1 = __ldg(reinterpret_cast<const float4*>(a.bias + col + 4));
+      y[0] += b0.x; y[1] += b0.y; y[2] += b0.z; y[3] += b0.w; y[4] += b1.x; y[5] += b1.y; y[6] += b1.z; y[7] += b1.w;
+    }
+    if (a.act == AYK_ACT_GELU_TANH) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = apply_activation_tc<AYK_ACT_GELU_TANH>(y[j], a.act);
+    } else if (a.act != AYK_ACT_NONE) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = apply_activation(y[j], a.act);
+    }
+    const size_t idx = (size_t)row * a.N + col;
+    if (a.residual) {
+      const float4 r0 = *reinterpret_cast<const float4*>(a.residual + idx), r1 = *reinterpret_cast<const float4*>(a.residual + idx + 4);
+      y[0] += r0.x; y[1] += r0.y; y[2] += r0.z; y[3] += r0.w; y[4] += r1.x; y[5] += r1.y; y[6] += r1.z; y[7] += r1.w;
+    }
+    if (a.out_bf16) {
+      uint32_t w[4];
+#pragma unroll
+      for (int u = 0; u < 8; u += 2) {
+        __nv_bfloat162 pr = __floats2bfloat162_rn(y[u], y[u + 1]);
+        w[u >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+      }
+      *reinterpret_cast<uint4*>((__nv_bfloat16*)a.C + idx) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (a.mode == 4) {
+        const int off = col - a.kv_col0;             // kv_col0 and kv_width are multiples of 8: a group is all key or all value
+        if (place >= 0 && off >= 0) {
+          __nv_bfloat16* dst = off < a.kv_width ? a.kcache + place + off : a.vcache + place + (off - a.kv_width);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    } else {
+      float* dst = (float*)a.C + idx;
+      *reinterpret_cast<float4*>(dst) = make_float4(y[0], y[1], y[2], y[3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(y[4], y[5], y[6], y[7]);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                        const PrefillArgs args) {
@@ -194,7 +289,15 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = args.m_tiles * args.n_tiles;
   const int num_kb = (args.K + BLOCK_K - 1) / BLOCK_K;
-  const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  // Whole tiles go round the CTAs; with a split along K a CTA has one tile and one part of its K blocks.
+  const int splits = args.splits;
+  const int first_tile = splits > 1 ? (int)blockIdx.x / splits : (int)blockIdx.x;
+  const int tile_step = splits > 1 ? total_tiles : (int)gridDim.x;          // one tile per CTA when K is split
+  const int part_kb = splits > 1 ? (num_kb + splits - 1) / splits : num_kb;
+  const int kb_first = splits > 1 ? ((int)blockIdx.x % splits) * part_kb : 0;
+  const int kb_last = min(num_kb, kb_first + part_kb);                       // this CTA's K blocks of each of its tiles
+  const int my_kb = kb_last - kb_first;
+  const int my_tiles = (first_tile < total_tiles) ? (total_tiles - 1 - first_tile) / tile_step + 1 : 0;
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -218,17 +321,17 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     if (lane == 0) {
       // A cursor walks this CTA's tiles and their K blocks; no division or modulo per K block
       // (one thread issues every copy, and its arithmetic set the pace of the whole pipeline).
-      const int total_it = my_tiles * num_kb;
+      const int total_it = my_tiles * my_kb;
       struct Cursor { int tile, kx, m0, n0, kb; };
       auto start = [&]() {
-        Cursor c; c.tile = blockIdx.x; c.kb = 0; c.kx = 0;
+        Cursor c; c.tile = first_tile; c.kb = kb_first; c.kx = kb_first * BLOCK_K;
         c.m0 = (c.tile / args.n_tiles) * BM; c.n0 = (c.tile % args.n_tiles) * BN;
         return c;
       };
       auto advance = [&](Cursor& c) {
         c.kx += BLOCK_K;
-        if (++c.kb == num_kb) {
-          c.kb = 0; c.kx = 0; c.tile += gridDim.x;
+        if (++c.kb == kb_last) {
+          c.kb = kb_first; c.kx = kb_first * BLOCK_K; c.tile += tile_step;
           c.m0 = (c.tile / args.n_tiles) * BM; c.n0 = (c.tile % args.n_tiles) * BN;
         }
       };
@@ -281,7 +384,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           tc_fence_after();
         }
         const uint32_t acc = tmem_base + (uint32_t)b * 256u;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
+        for (int kb = 0; kb < my_kb && ok; ++kb) {
           ok = mbar_wait(full_bar(s), full_parity, args.error, 24);
           if (!ok) break;
           tc_fence_after();
@@ -297,6 +400,60 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       }
     }
     __syncwarp();
+  } else if (splits > 1) {
+    // ---- K split over `splits` CTAs: one tile, one part of its K blocks (see PrefillArgs)
+    pdl_wait();
+    const int e = warp - 2;
+    const int quarter = warp & 3, half = e >> 2;
+    const int half_cols = BN >> 1;
+    bool ok = my_tiles == 1;
+    if (ok) {
+      const int tile = first_tile, part = (int)blockIdx.x % splits, cta0 = (int)blockIdx.x - part;
+      const int m0 = (tile / args.n_tiles) * BM, n0 = (tile % args.n_tiles) * BN;
+      const long long slot_floats = (long long)BM * BN;
+      if (lane == 0) ok = mbar_wait(tmem_full(0), 0u, args.error, 25);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (ok) {
+        tc_fence_after();
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
+        store_partial_row(taddr, args.sk_ws + (long long)blockIdx.x * slot_floats + (long long)(half * half_cols) * BM + row_in_tile,
+                          half_cols);
+        tc_fence_before();
+        __threadfence();
+        asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        if (warp == 2 && lane == 0)
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(args.sk_ready + blockIdx.x), "r"(1) : "memory");
+        if (lane == 0) {
+          for (int p = 0; p < splits && ok; ++p) {
+            const int* flag = args.sk_ready + cta0 + p;
+            bool seen = false;
+            for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+              int v;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+              if (v != 0) { seen = true; break; }
+            }
+            if (!seen) { atomicExch(args.error, 26); ok = false; }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (ok) {
+          // this CTA's columns of the tile, half of them for each of the two warps that own a row
+          const int share = BN / splits, mine = share >> 1;
+          finish_split_cols(args, args.sk_ws + (long long)cta0 * slot_floats, splits, BN, m0, n0, row_in_tile,
+                            part * share + half * mine, mine);
+        }
+        // The tile's last CTA out clears its flags (each CTA counts itself once, finished or given up).
+        asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        if (warp == 2 && lane == 0) {
+          __threadfence();
+          if (atomicAdd(args.sk_done + cta0, 1) == splits - 1) {
+            for (int p = 0; p < splits; ++p) args.sk_ready[cta0 + p] = 0;
+            args.sk_done[cta0] = 0;
+          }
+        }
+      }
+    }
   } else {
     pdl_wait();            // residual and C belong to earlier kernels until here
     const int e = warp - 2;
@@ -571,6 +728,82 @@ int encode(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
   return 0;
 }
 
+// Split along K in the one-SM form: -1 the library decides per product, 0 or 1 never, 2 / 4 / 8 that many
+// CTAs per tile wherever the tiles allow it.
+int g_split = -1;
+int g_last_splits = 1;          // parts per tile of the last one-SM launch (1: whole tiles), for tests and tuning
+
+// Scratch of the split form, per device and stream: a slot of 128 x 256 floats and two flags per CTA.  The
+// kernels of one stream run one after the other and clear their flags themselves, so they share a space;
+// a second stream that runs products at the same time gets its own.  Made at the first use, never while the
+// stream is being captured (the product then runs unsplit).
+struct SplitSpace { int device; cudaStream_t stream; float* ws; int* ready; int* done; int ctas; };
+std::vector<SplitSpace*> g_split_spaces;
+SplitSpace* split_space(int ctas, cudaStream_t stream) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (SplitSpace* sp : g_split_spaces)
+    if (sp->device == device && sp->stream == stream && sp->ctas >= ctas) return sp;
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (g_split_spaces.size() >= 16) return nullptr;
+  SplitSpace* sp = new SplitSpace{device, stream, nullptr, nullptr, nullptr, ctas};
+  if (cudaMalloc((void**)&sp->ws, (size_t)ctas * BM * 256 * sizeof(float)) != cudaSuccess ||
+      cudaMalloc((void**)&sp->ready, 2 * (size_t)ctas * sizeof(int)) != cudaSuccess ||
+      cudaMemset(sp->ready, 0, 2 * (size_t)ctas * sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    if (sp->ws) cudaFree(sp->ws);
+    if (sp->ready) cudaFree(sp->ready);
+    delete sp;
+    return nullptr;
+  }
+  sp->done = sp->ready + ctas;
+  g_split_spaces.push_back(sp);
+  return sp;
+}
+
+// May a tile's K blocks be split `splits` ways?  Every part must hold a K block.
+bool split_fits(int tiles, int num_kb, int splits, int sms, int bn) {
+  if (splits < 2 || splits > 8 || bn % (16 * splits) != 0 || (long long)tiles * splits > sms) return false;
+  const int part = (num_kb + splits - 1) / splits;
+  return part >= 2 && (splits - 1) * part < num_kb;
+}
+
+double kblock_us(int a_rows, int bn, int active);              // the model of the product's time, below
+double whole_tiles_us(int M, int N, int K, int bn, int sms, bool wide_rows);
+
+// Does splitting K beat whole tiles going round the CTAs, and with which tile width and how many parts?
+// Times from the model above; leaving the sums in scratch, waiting for the other parts and adding them up
+// costs the split form about 6 us + 25 ns per column of the tile on top of its K blocks (measured 7 us at 64
+// columns, 12 us at 256).
+double g_split_fix_us = 6.0, g_split_fix_per_col = 0.025;
+bool split_pays(int M, int N, int K, int sms, int tile_n, bool wide_rows, int* bn_out, int* splits_out) {
+  const int m_tiles = (M + BM - 1) / BM, num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  if (N % 8 != 0) return false;
+  double best_whole = -1.0;
+  for (int bn = 32; bn <= 256; bn += 32) {
+    if (tile_n > 0 && bn != tile_n) continue;
+    const double us = whole_tiles_us(M, N, K, bn, sms, wide_rows);
+    if (best_whole < 0 || us < best_whole) best_whole = us;
+  }
+  double best_split = -1.0;
+  for (int bn = 32; bn <= 256; bn += 32) {
+    if (tile_n > 0 && bn != tile_n) continue;
+    const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
+    for (int sp = 2; sp <= 8; sp *= 2) {
+      if (!split_fits((int)tiles, num_kb, sp, sms, bn)) continue;
+      const double us = 3.4 + (double)((num_kb + sp - 1) / sp) * kblock_us(M >= BM ? BM : (M + 7) / 8 * 8, bn, (int)tiles * sp) +
+                        g_split_fix_us + g_split_fix_per_col * bn;
+      if (best_split < 0 || us < best_split) { best_split = us; *bn_out = bn; *splits_out = sp; }
+    }
+  }
+  return best_split > 0 && best_split < 0.9 * best_whole;
+}
+
 int epilogue_mode(int act, bool with_residual, bool out_bf16) {
   if (act == AYK_ACT_NONE && !with_residual && out_bf16) return 0;
   if (act == AYK_ACT_NONE && !out_bf16) return 1;
@@ -581,20 +814,47 @@ int epilogue_mode(int act, bool with_residual, bool out_bf16) {
 }  // namespace
 
 AYK_EXPORT int ayk_gemm_tc_prefill_error() { return g_error_host ? *g_error_host : 0; }
+// Split along K in the one-SM product for many rows: -1 the library decides (default), 0 never, 2 / 4 / 8
+// that many CTAs per tile wherever the tiles allow it.
+AYK_EXPORT void ayk_gemm_tc_prefill_split(int mode) { g_split = mode; }
+// Into how many parts the last one-SM product split the K blocks of its tiles (1: it did not).
+AYK_EXPORT int ayk_gemm_tc_prefill_last_split() { return g_last_splits; }
+AYK_EXPORT void ayk_gemm_tc_prefill_split_cost(double fix_us, double per_col) { g_split_fix_us = fix_us; g_split_fix_per_col = per_col; }
 
-// The tile width (out features per tile) that fills whole waves of `sms` SMs best.
-AYK_EXPORT int ayk_gemm_tc_prefill_tile(int M, int N, int sms) {
+// A model of the one-SM product's time in microseconds, fitted to measurements on a B200 (graphs of 24
+// products, GPT-2 XL and GPT-2 small shapes, 96 to 2,048 rows, tile widths 64 to 256; mean error 8 %):
+// a fixed 3.4 us; per K block of a tile the larger of a latency floor (0.256 us + 0.285 ns per column) and
+// the tile's operand bytes times the CTAs that run at once over 18 TB/s (what the SMs together draw
+// from L2); the last tile's epilogue, which no main loop hides: 15.8 ns per column, and 26 ns more where it
+// reads and writes 32-bit rows (a residual sum).  On the 80 measured cases the width it picks is within
+// 0.1 % of the best measured one.
+namespace {
+double kblock_us(int a_rows, int bn, int active) {
+  const double floor_us = 0.256 + 0.000285 * bn;
+  const double stream_us = (double)(a_rows + bn) * 128.0 * active / 18.0e6;
+  return floor_us > stream_us ? floor_us : stream_us;
+}
+double whole_tiles_us(int M, int N, int K, int bn, int sms, bool wide_rows) {
+  const int m_tiles = (M + BM - 1) / BM, num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  const int a_rows = M >= BM ? BM : (M + 7) / 8 * 8;
+  const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
+  const long full = tiles / sms, rest = tiles % sms;
+  double t = 3.4 + (double)full * num_kb * kblock_us(a_rows, bn, sms) + (wide_rows ? 0.0418 : 0.0158) * bn;
+  if (rest) t += (double)num_kb * kblock_us(a_rows, bn, (int)rest);
+  return t;
+}
+}  // namespace
+
+// The tile width (out features per tile) with the shortest modelled time on `sms` SMs.
+// wide_rows: the epilogue reads or writes 32-bit rows (a residual sum, float32 out).
+AYK_EXPORT int ayk_gemm_tc_prefill_tile_k(int M, int N, int K, int sms, int wide_rows);
+AYK_EXPORT int ayk_gemm_tc_prefill_tile(int M, int N, int sms) { return ayk_gemm_tc_prefill_tile_k(M, N, 1600, sms, 0); }
+AYK_EXPORT int ayk_gemm_tc_prefill_tile_k(int M, int N, int K, int sms, int wide_rows) {
   int best = 256;
-  long best_cost = -1;
-  const int m_tiles = (M + BM - 1) / BM;
+  double best_us = -1.0;
   for (int bn = 32; bn <= 256; bn += 32) {
-    const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
-    const long waves = (tiles + sms - 1) / sms;
-    // Many rows: the main loop's MMA time, proportional to the tile width, plus a fixed cost per
-    // tile.  One row tile (up to 128 rows): a tile is bound by the bytes an SM can take in, its
-    // rows of X plus bn rows of W per K block, so narrow tiles on many SMs win.
-    const long cost = m_tiles > 1 ? waves * (bn + 24) : waves * (bn + (M < BM ? M : BM));
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    const double us = whole_tiles_us(M, N, K, bn, sms, wide_rows != 0);
+    if (best_us < 0 || us < best_us) { best_us = us; best = bn; }
   }
   return best;
 }
@@ -725,7 +985,15 @@ int prefill_product(void* C, const void* X, const void* W, const float* bias, co
     cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mx, mw, args);
     return ayk_check_launch("ayk_gemm_tc_prefill (pairs)");
   }
-  int BN = tile_n > 0 ? tile_n : ayk_gemm_tc_prefill_tile(M, N, sms);
+  const bool wide_rows = residual != nullptr || out_dtype == AYK_DTYPE_F32;
+  int BN = tile_n > 0 ? tile_n : ayk_gemm_tc_prefill_tile_k(M, N, K, sms, wide_rows ? 1 : 0);
+  int splits = 1;
+  if (g_split < 0) {
+    int sbn = 0, ssp = 0;
+    if (split_pays(M, N, K, sms, tile_n, wide_rows, &sbn, &ssp)) { BN = sbn; splits = ssp; }
+  } else if (g_split >= 2) {
+    splits = g_split;
+  }
   AYK_REQUIRE(BN >= 32 && BN <= 256 && BN % 32 == 0, "ayk_gemm_tc_prefill: tile width %d is not a multiple of 32 in [32, 256]", BN);
   {
     std::lock_guard<std::mutex> lock(g_mutex);
@@ -759,7 +1027,17 @@ int prefill_product(void* C, const void* X, const void* W, const float* bias, co
   args.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
   // Rows whose 16-byte segments are not aligned take the scalar path of the epilogue; N % 8 keeps them aligned.
   const int total = args.m_tiles * args.n_tiles;
-  dim3 grid(total < sms ? total : sms);
+  int grid_x = total < sms ? total : sms;
+  args.splits = 1;
+  if (splits > 1 && N % 8 == 0 && args.vec_ok && split_fits(total, (K + BLOCK_K - 1) / BLOCK_K, splits, sms, BN)) {
+    SplitSpace* space = split_space(sms, stream);
+    if (space != nullptr) {
+      args.splits = splits; args.sk_ws = space->ws; args.sk_ready = space->ready; args.sk_done = space->done;
+      grid_x = total * splits;
+    }
+  }
+  g_last_splits = args.splits;
+  dim3 grid(grid_x);
   ayk_launch(gemm_tc_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mx, mw, args);
   return ayk_check_launch("ayk_gemm_tc_prefill");
 }

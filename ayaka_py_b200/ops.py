@@ -68,6 +68,19 @@ def set_pdl(on: bool) -> None:
     _ready().ayk_set_pdl(ctypes.c_int(1 if on else 0))
 
 
+def set_split(parts: int | None) -> None:
+    """Split along K in the product for many rows (``gemm_tc_prefill``, one-SM form): when the tiles
+    alone would leave most SMs idle, 2, 4 or 8 CTAs share a tile, each with an equal part of its K
+    blocks; they leave their sums in scratch and each finishes a share of the tile's rows.  None: the
+    library decides per product (the default); 0: never; 2, 4, 8: wherever the tiles allow it."""
+    _ready().ayk_gemm_tc_prefill_split(ctypes.c_int(-1 if parts is None else int(parts)))
+
+
+def last_split() -> int:
+    """Into how many parts the last ``gemm_tc_prefill`` (one-SM form) split the K blocks of its tiles."""
+    return int(_ready().ayk_gemm_tc_prefill_last_split())
+
+
 def _check(code: int) -> None:
     if code != 0:
         raise KernelError(library().ayk_last_error().decode("utf-8", "replace"))

@@ -480,6 +480,91 @@ def test_gemm_tcgen05_many_rows(M, N, K, tile_n, act, out_dtype, pair):
         assert float((few - out[:64]).abs().max()) < 1e-4                     # the few-row kernel agrees
 
 
+SPLIT_GEMM_CASES = [
+    # M, N, K, tile_n, parts: tiles * parts fit the SMs, the tile width is a multiple of 16 * parts
+    (128, 1600, 6400, 128, 8), (300, 200, 1600, 64, 4), (130, 328, 1000, 96, 2), (576, 1600, 6400, 256, 4),
+    (129, 72, 4096, 32, 2), (1024, 264, 712, 128, 2), (200, 768, 3072, 128, 8), (70, 1600, 6400, 128, 8), (17, 64, 512, 64, 4),
+]
+
+
+@pytest.mark.parametrize("M,N,K,tile_n,parts", SPLIT_GEMM_CASES)
+@pytest.mark.parametrize("act,out_dtype", [("none", "float32"), ("gelu_tanh", "bfloat16")])
+def test_gemm_tcgen05_many_rows_split_along_k(M, N, K, tile_n, parts, act, out_dtype):
+    """The many-row product with the K blocks of a tile split over 2, 4 or 8 CTAs (sums left in scratch,
+    each CTA finishing its share of the columns): the plain float32 product, the unsplit kernel to
+    rounding of the sums, the same bits in a second run (flags cleared, sums added in a fixed order), in
+    place over the residual, and the library's own choice."""
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(31)
+    a, w = rs.randn(M, K).astype(np.float32), (rs.randn(N, K) / np.sqrt(K)).astype(np.float32)
+    bias, res = rs.randn(N).astype(np.float32), rs.randn(M, N).astype(np.float32)
+    A, W = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    y = (A.float() @ W.float().t()).double().cpu().numpy() + bias
+    if act != "none":
+        y = plain_gpt2.activation("gelu_new", y)
+    want = y + res
+    R = dev(res)
+    try:
+        ops.set_split(0)
+        whole = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=DTYPES[out_dtype], tile_n=tile_n, pair=False)
+        ops.set_split(parts)
+        before = ops.launches
+        out = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=DTYPES[out_dtype], tile_n=tile_n, pair=False)
+        assert ops.last_split() == parts
+        again = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=DTYPES[out_dtype], tile_n=tile_n, pair=False)
+        assert ops.launches == before + 2
+        torch.cuda.synchronize()
+        assert ops.tc_error() == 0
+        err = np.abs(out.float().cpu().numpy() - want).max()
+        assert err < (1e-3 if out_dtype == "float32" else 5e-2), err
+        assert torch.equal(out, again)
+        assert float((out.float() - whole.float()).abs().max()) < (1e-4 if out_dtype == "float32" else 5e-2)
+        if out_dtype == "float32":
+            R2 = dev(res)
+            in_place = ops.gemm_tc_prefill(A, W, dev(bias), act, R2, out_dtype=torch.float32, out=R2, tile_n=tile_n, pair=False)
+            assert torch.equal(in_place, out)
+        ops.set_split(None)
+        chosen = ops.gemm_tc_prefill(A, W, dev(bias), act, R, out_dtype=DTYPES[out_dtype], pair=False)
+        torch.cuda.synchronize()
+        assert ops.tc_error() == 0
+        assert np.abs(chosen.float().cpu().numpy() - want).max() < (1e-3 if out_dtype == "float32" else 5e-2)
+    finally:
+        ops.set_split(None)
+
+
+def test_gemm_prefill_split_files_keys_and_values():
+    """The split form as a q | k | v projection: the CTA that finishes a share of the columns also stores
+    the keys and values among them into the paged cache."""
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(22)
+    lens_q, lens_ctx, H, Hkv, Dh, P, K = [130, 70], [3, 40], 4, 2, 32, 16, 2048
+    x, _ = paged_case(rs, lens_q, lens_ctx, H, Hkv, Dh, P, "bfloat16")
+    T, qw, kvw = sum(lens_q), H * Dh, Hkv * Dh
+    N = qw + 2 * kvw
+    a = dev(rs.randn(T, K).astype(np.float32), torch.bfloat16)
+    w = dev((rs.randn(N, K) / np.sqrt(K)).astype(np.float32), torch.bfloat16)
+    bias = dev(rs.randn(N).astype(np.float32))
+    try:
+        ops.set_split(0)
+        plain_out = ops.gemm_tc_prefill(a, w, bias, out_dtype=torch.bfloat16, tile_n=64, pair=False)
+        kc1, vc1 = x["kc"].clone(), x["vc"].clone()
+        ops.kv_append(kc1, vc1, plain_out[:, qw:qw + kvw], plain_out[:, qw + kvw:], x["row_req"], x["pos"], x["table"])
+        ops.set_split(4)
+        kc2, vc2 = x["kc"].clone(), x["vc"].clone()
+        filing = ops.KVAppend(kc2, vc2, x["row_req"], x["pos"], x["table"], qw, kvw)
+        out = ops.gemm_tc_prefill(a, w, bias, out_dtype=torch.bfloat16, tile_n=64, pair=False, kv=filing)
+        torch.cuda.synchronize()
+        assert ops.tc_error() == 0 and filing.done and ops.last_split() == 4
+        assert float((out.float() - plain_out.float()).abs().max()) < 5e-2
+        # the cache holds what the output holds
+        kc3, vc3 = x["kc"].clone(), x["vc"].clone()
+        ops.kv_append(kc3, vc3, out[:, qw:qw + kvw], out[:, qw + kvw:], x["row_req"], x["pos"], x["table"])
+        assert torch.equal(kc2, kc3) and torch.equal(vc2, vc3)
+        assert not torch.equal(kc2, x["kc"])
+    finally:
+        ops.set_split(None)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("width", [64, 1600, 2048])
 def test_layernorm_many_rows(dtype, width):

@@ -5,8 +5,8 @@
 //   C[M, N] = act(X[M, K] * W[N, K]^T + bias[N]) (+ residual[M, N])
 //
 // A tile is 128 rows of X (the MMA's M side, one row per TMEM lane) by BN out
-// features (its N side, BN = 32 ... 256 in steps of 32, chosen by the host so
-// that the tiles fill whole waves of the 148 SMs).  Operands come by TMA in
+// features (its N side, BN = 32 ... 256 in steps of 32, chosen by the host from
+// a fitted model of the kernel's time, see whole_tiles_us).  Operands come by TMA in
 // 64-element K blocks with the 128-byte swizzle through a ring of stages.
 // Warp 0: TMA producer; warp 1: MMA issue and TMEM allocation; warps 2..9:
 // epilogue, two warps per TMEM lane quarter, each taking half of the tile's
@@ -15,9 +15,14 @@
 // 32-bit residual (all loads of a chunk issued before its stores: the residual
 // may alias C) and stores 128 contiguous bytes.
 //
-// Every mbarrier wait is bounded; a wait that runs out records a code (21..25,
-// 31..35 in the two-SM form) in the error word of the tensor-core kernels and
-// the CTA winds down.
+// Where the tiles alone would leave most SMs idle (few out features, a long K)
+// 2, 4 or 8 CTAs share a tile, each with an equal part of its K blocks: see
+// PrefillArgs::splits.  (The reference leaves such choices to the library behind
+// F.linear, layers/linear/methods.py:76.)
+//
+// Every wait is bounded; a wait that runs out records a code (21..26, 31..35 in
+// the two-SM form) in the error word of the tensor-core kernels and the CTA
+// winds down.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -780,7 +785,7 @@ double whole_tiles_us(int M, int N, int K, int bn, int sms, bool wide_rows);
 // Times from the model above; leaving the sums in scratch, waiting for the other parts and adding them up
 // costs the split form about 6 us + 25 ns per column of the tile on top of its K blocks (measured 7 us at 64
 // columns, 12 us at 256).
-double g_split_fix_us = 6.0, g_split_fix_per_col = 0.025;
+constexpr double SPLIT_FIX_US = 6.0, SPLIT_FIX_PER_COL = 0.025;
 bool split_pays(int M, int N, int K, int sms, int tile_n, bool wide_rows, int* bn_out, int* splits_out) {
   const int m_tiles = (M + BM - 1) / BM, num_kb = (K + BLOCK_K - 1) / BLOCK_K;
   if (N % 8 != 0) return false;
@@ -797,7 +802,7 @@ bool split_pays(int M, int N, int K, int sms, int tile_n, bool wide_rows, int* b
     for (int sp = 2; sp <= 8; sp *= 2) {
       if (!split_fits((int)tiles, num_kb, sp, sms, bn)) continue;
       const double us = 3.4 + (double)((num_kb + sp - 1) / sp) * kblock_us(M >= BM ? BM : (M + 7) / 8 * 8, bn, (int)tiles * sp) +
-                        g_split_fix_us + g_split_fix_per_col * bn;
+                        SPLIT_FIX_US + SPLIT_FIX_PER_COL * bn;
       if (best_split < 0 || us < best_split) { best_split = us; *bn_out = bn; *splits_out = sp; }
     }
   }
@@ -819,7 +824,6 @@ AYK_EXPORT int ayk_gemm_tc_prefill_error() { return g_error_host ? *g_error_host
 AYK_EXPORT void ayk_gemm_tc_prefill_split(int mode) { g_split = mode; }
 // Into how many parts the last one-SM product split the K blocks of its tiles (1: it did not).
 AYK_EXPORT int ayk_gemm_tc_prefill_last_split() { return g_last_splits; }
-AYK_EXPORT void ayk_gemm_tc_prefill_split_cost(double fix_us, double per_col) { g_split_fix_us = fix_us; g_split_fix_per_col = per_col; }
 
 // A model of the one-SM product's time in microseconds, fitted to measurements on a B200 (graphs of 24
 // products, GPT-2 XL and GPT-2 small shapes, 96 to 2,048 rows, tile widths 64 to 256; mean error 8 %):

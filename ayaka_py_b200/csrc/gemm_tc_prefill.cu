@@ -13,7 +13,8 @@
 // columns.  An epilogue thread owns one row: it reads 32 accumulator columns
 // with tcgen05.ld, adds the bias, applies the activation in 32-bit, adds the
 // 32-bit residual (all loads of a chunk issued before its stores: the residual
-// may alias C) and stores 128 contiguous bytes.
+// may alias C) and stores 128 contiguous bytes.  Where the output and the residual
+// are 32-bit rows, both go through shared memory by TMA instead (PrefillArgs::staged).
 //
 // Where the tiles alone would leave most SMs idle (few out features, a long K)
 // 2, 4 or 8 CTAs share a tile, each with an equal part of its K blocks: see
@@ -42,6 +43,7 @@ constexpr int THREADS = 320;
 constexpr int EPI_WARPS = 8;
 constexpr int MAX_STAGES = 8;
 constexpr int SMEM_TILES = 196608;             // bytes available to the stage ring
+constexpr int STAGED_CHUNK = 16384;            // a buffer of the staged residual epilogue: 128 rows x 32 floats; it takes 2 halves x 1 or 2 of them
 
 struct PrefillArgs {
   void* C;
@@ -67,6 +69,12 @@ struct PrefillArgs {
   // floats, column by column) and raises `sk_ready[cta]`; then each of the CTAs adds up, in the CTAs' order,
   // the BN / splits columns that are its share and finishes them (bias, activation, residual, store).  The last of
   // a tile's CTAs to finish (counted in `sk_done`) clears the tile's flags for the next launch.
+  // Staged residual epilogue (one-SM form, float32 out over a float32 residual): the residual rows come by
+  // TMA into shared memory, 128 rows x 32 columns at a time and a chunk ahead, the sums go back to the same
+  // place and leave by a TMA store: whole 128-byte lines both ways, where a thread that owns a row would
+  // otherwise read and write 16 bytes of 32 different lines per instruction.  staged = buffers per half of
+  // the tile's columns (1 or 2; 0: the form is not taken): two where the ring keeps four stages beside them.
+  int staged;
   int splits;
   float* sk_ws;
   int* sk_ready;
@@ -187,6 +195,14 @@ __device__ __forceinline__ void epilogue_row_any(const PrefillArgs& a, uint32_t 
   else epilogue_row<3>(a, taddr, row, n, cols, row_ok, place);
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // The raw sums of `cols` columns of one accumulator row (cols a multiple of 16) into a slot of the split
 // form.  A slot holds a tile column by column, 128 rows each: a thread owns a row, so the 32 threads of a
 // warp write (and later read) 128 contiguous bytes per column.  `dst`: the row's place in the first column.
@@ -272,6 +288,7 @@ __device__ __forceinline__ void finish_split_cols(const PrefillArgs& a, const fl
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                       const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_c,
                        const PrefillArgs args) {
   const int BN = args.BN, STAGES = args.stages;
   const uint32_t B_BYTES = (uint32_t)BN * BLOCK_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -289,6 +306,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   auto tmem_full = [&](int b) { return bars + 8u * (2 * MAX_STAGES + b); };
   auto tmem_empty = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 2 + b); };
   const uint32_t tmem_slot = bars + 8u * (2 * MAX_STAGES + 4);
+  auto res_full = [&](int half, int buf) { return bars + 8u * (2 * MAX_STAGES + 5 + 2 * half + buf); };
   volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -309,6 +327,11 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     for (int s = 0; s < MAX_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(tmem_full(b), 1); mbar_init(tmem_empty(b), EPI_WARPS); }
+    for (int h = 0; h < 2; ++h) { mbar_init(res_full(h, 0), 1); mbar_init(res_full(h, 1), 1); }
+    if (args.staged) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_r) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -459,6 +482,79 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         }
       }
     }
+  } else if (args.staged) {
+    // ---- float32 out over a float32 residual, both through shared memory by TMA (see PrefillArgs)
+    pdl_wait();
+    const int e = warp - 2;
+    const int quarter = warp & 3, half = e >> 2;
+    const int half_cols = BN >> 1, chunks = half_cols >> 5;                  // 32 columns a chunk
+    const bool chief = (e & 3) == 0 && lane == 0;                            // issues the copies of this half of the columns
+    const int nbuf = args.staged;
+    const uint32_t stage0 = tiles + (uint32_t)(SMEM_TILES - 2 * nbuf * STAGED_CHUNK) + (uint32_t)(half * nbuf) * STAGED_CHUNK;
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t fills[2] = {0u, 0u};                // how often each buffer has been filled: the phase of its barrier
+    bool ok = true;
+    for (int t = 0; t < my_tiles && ok; ++t) {
+      const int b = t & 1;
+      const int tile = blockIdx.x + t * gridDim.x;
+      const int m0 = (tile / args.n_tiles) * BM, nh = (tile % args.n_tiles) * BN + half * half_cols;
+      // The tile's first chunks of the residual are asked for now and land under the main loop.  The
+      // stores of the tile before must have read their buffers first.
+      if (chief) {
+        bulk_wait_read();
+        for (int c = 0; c < nbuf && c < chunks; ++c) {
+          mbar_expect_tx(res_full(half, c), STAGED_CHUNK);
+          tma_load_2d(stage0 + c * STAGED_CHUNK, &map_r, nh + 32 * c, m0, res_full(half, c));
+        }
+      }
+      if (lane == 0) ok = mbar_wait(tmem_full(b), (uint32_t)(t >> 1) & 1u, args.error, 25);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t)b * 256u + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
+      for (int c = 0; c < chunks && ok; ++c) {
+        const int buf = nbuf == 2 ? (c & 1) : 0;
+        uint32_t r[32];
+        tmem_ld32(taddr + 32 * c, r);
+        if (lane == 0) ok = mbar_wait(res_full(half, buf), fills[buf] & 1u, args.error, 27);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        ++fills[buf];
+        tmem_ld_wait();
+        if (!ok) break;
+        if (c == chunks - 1) {                   // the accumulator is in registers: the MMA warp may have it back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tmem_empty(b));
+        }
+        const uint32_t mine = stage0 + buf * STAGED_CHUNK + (uint32_t)row_in_tile * 128u;
+        const int col0 = nh + 32 * c;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t at = mine + (uint32_t)((j ^ (row_in_tile & 7)) << 4);     // the 128-byte swizzle of the copy
+          float4 v;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(at));
+          float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (args.bias && col0 + 4 * j < args.N) bv = __ldg(reinterpret_cast<const float4*>(args.bias + col0 + 4 * j));
+          v.x += __uint_as_float(r[4 * j]) + bv.x;
+          v.y += __uint_as_float(r[4 * j + 1]) + bv.y;
+          v.z += __uint_as_float(r[4 * j + 2]) + bv.z;
+          v.w += __uint_as_float(r[4 * j + 3]) + bv.w;
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(at), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");           // the sums are there before the copy engine reads them
+        if (half == 0) asm volatile("bar.sync 2, 128;" ::: "memory"); else asm volatile("bar.sync 3, 128;" ::: "memory");
+        if (chief) {
+          tma_store_2d(&map_c, col0, m0, stage0 + buf * STAGED_CHUNK);
+          bulk_commit();
+          if (c + nbuf < chunks) {               // this buffer's next chunk, once the store has read it
+            bulk_wait_read();
+            mbar_expect_tx(res_full(half, buf), STAGED_CHUNK);
+            tma_load_2d(stage0 + buf * STAGED_CHUNK, &map_r, col0 + 32 * nbuf, m0, res_full(half, buf));
+          }
+        }
+      }
+    }
+    if (chief) bulk_wait_all();                  // the last stores are out before the shared memory is given back
   } else {
     pdl_wait();            // residual and C belong to earlier kernels until here
     const int e = warp - 2;
@@ -689,7 +785,7 @@ int* g_error_host = nullptr;
 int* g_error_dev = nullptr;
 bool g_configured = false;
 std::mutex g_mutex;
-constexpr size_t SMEM_BYTES = 1024 + SMEM_TILES + 8 * (2 * MAX_STAGES + 5);
+constexpr size_t SMEM_BYTES = 1024 + SMEM_TILES + 8 * (2 * MAX_STAGES + 9);
 
 struct MapKey {
   const void* ptr; int rows, k, box;
@@ -809,6 +905,22 @@ bool split_pays(int M, int N, int K, int sms, int tile_n, bool wide_rows, int* b
   return best_split > 0 && best_split < 0.9 * best_whole;
 }
 
+// rows x n float32, row-major; box of 128 rows x 32 columns (128 bytes), 128-byte swizzle: a chunk of the
+// staged residual epilogue.
+int encode_f32(CUtensorMap* map, const void* ptr, int rows, int n) {
+  cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)n * 4};
+  cuuint32_t box[2] = {32u, (cuuint32_t)BM};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return ayk_fail("ayk_gemm_tc_prefill: cuTensorMapEncodeTiled (float32 rows) failed with %d", (int)r);
+  return 0;
+}
+int g_staged = 1;             // the staged residual epilogue where it applies (0: the row-per-thread epilogue everywhere)
+int g_last_staged = 0;        // buffers per half that the last one-SM launch staged its residual through (0: it did not)
+
 int epilogue_mode(int act, bool with_residual, bool out_bf16) {
   if (act == AYK_ACT_NONE && !with_residual && out_bf16) return 0;
   if (act == AYK_ACT_NONE && !out_bf16) return 1;
@@ -822,6 +934,10 @@ AYK_EXPORT int ayk_gemm_tc_prefill_error() { return g_error_host ? *g_error_host
 // Split along K in the one-SM product for many rows: -1 the library decides (default), 0 never, 2 / 4 / 8
 // that many CTAs per tile wherever the tiles allow it.
 AYK_EXPORT void ayk_gemm_tc_prefill_split(int mode) { g_split = mode; }
+// The staged residual epilogue (float32 out over a float32 residual through shared memory by TMA): 1 where it
+// applies (default), 0 never.
+AYK_EXPORT void ayk_gemm_tc_prefill_staged(int on) { g_staged = on ? 1 : 0; }
+AYK_EXPORT int ayk_gemm_tc_prefill_last_staged() { return g_last_staged; }
 // Into how many parts the last one-SM product split the K blocks of its tiles (1: it did not).
 AYK_EXPORT int ayk_gemm_tc_prefill_last_split() { return g_last_splits; }
 
@@ -843,7 +959,9 @@ double whole_tiles_us(int M, int N, int K, int bn, int sms, bool wide_rows) {
   const int a_rows = M >= BM ? BM : (M + 7) / 8 * 8;
   const long tiles = (long)m_tiles * ((N + bn - 1) / bn);
   const long full = tiles / sms, rest = tiles % sms;
-  double t = 3.4 + (double)full * num_kb * kblock_us(a_rows, bn, sms) + (wide_rows ? 0.0418 : 0.0158) * bn;
+  // 32-bit rows cost the epilogue 26 ns more per column unless they go through the staged form (widths 64, 128, 192)
+  const bool staged = wide_rows && bn % 64 == 0 && bn <= 192 && M >= BM;
+  double t = 3.4 + (double)full * num_kb * kblock_us(a_rows, bn, sms) + (wide_rows && !staged ? 0.0418 : 0.0158) * bn;
   if (rest) t += (double)num_kb * kblock_us(a_rows, bn, (int)rest);
   return t;
 }
@@ -1041,8 +1159,27 @@ int prefill_product(void* C, const void* X, const void* W, const float* bias, co
     }
   }
   g_last_splits = args.splits;
+  // float32 out over a float32 residual: both through shared memory by TMA when the tile's halves are whole
+  // 32-column chunks; two buffers per half where the ring keeps four stages beside them (three for a short K),
+  // else one (a long K wants its stages more than the epilogue wants its second buffer: proj2 at 2,048 rows
+  // 44.0 us with two buffers and three stages, 40.7 with one and four), none below three stages
+  CUtensorMap mr = mx, mc = mx;              // placeholders when the form is not taken
+  args.staged = 0;
+  if (g_staged && args.splits == 1 && args.mode == 1 && residual != nullptr && args.vec_ok && BN % 64 == 0 && box_m == BM &&
+      (uintptr_t)C % 16 == 0 && (uintptr_t)residual % 16 == 0) {
+    const int stage_bytes = A_BYTES + BN * BLOCK_K * 2;
+    const int with_two = (SMEM_TILES - 4 * STAGED_CHUNK) / stage_bytes;
+    const int nbuf = (with_two >= 4 || (with_two >= 3 && K <= 32 * BLOCK_K)) ? 2 : 1;     // a short K gets by with three stages
+    const int left = (SMEM_TILES - 2 * nbuf * STAGED_CHUNK) / stage_bytes;
+    if (left >= 3) {
+      if (encode_f32(&mr, residual, M, N) != 0 || encode_f32(&mc, C, M, N) != 0) return -1;
+      args.staged = nbuf;
+      args.stages = left > MAX_STAGES ? MAX_STAGES : left;
+    }
+  }
+  g_last_staged = args.staged;
   dim3 grid(grid_x);
-  ayk_launch(gemm_tc_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mx, mw, args);
+  ayk_launch(gemm_tc_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mx, mw, mr, mc, args);
   return ayk_check_launch("ayk_gemm_tc_prefill");
 }
 }  // namespace

@@ -76,6 +76,17 @@ def set_split(parts: int | None) -> None:
     _ready().ayk_gemm_tc_prefill_split(ctypes.c_int(-1 if parts is None else int(parts)))
 
 
+def set_staged(on: bool) -> None:
+    """The staged residual epilogue of ``gemm_tc_prefill`` (float32 out over a float32 residual: both
+    through shared memory by TMA, whole lines at a time) where it applies (the default), or never."""
+    _ready().ayk_gemm_tc_prefill_staged(ctypes.c_int(1 if on else 0))
+
+
+def last_staged() -> int:
+    """Buffers per half through which the last ``gemm_tc_prefill`` staged its residual (0: it did not)."""
+    return int(_ready().ayk_gemm_tc_prefill_last_staged())
+
+
 def last_split() -> int:
     """Into how many parts the last ``gemm_tc_prefill`` (one-SM form) split the K blocks of its tiles."""
     return int(_ready().ayk_gemm_tc_prefill_last_split())

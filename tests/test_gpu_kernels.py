@@ -532,6 +532,39 @@ def test_gemm_tcgen05_many_rows_split_along_k(M, N, K, tile_n, parts, act, out_d
         ops.set_split(None)
 
 
+@pytest.mark.parametrize("M,N,K,tile_n", [(2048, 1600, 1600, 192), (640, 1600, 6400, 128), (300, 1000, 328, 64),
+                                          (129, 72, 64, 64), (1000, 1608, 712, 192), (131, 6400, 128, 128)])
+@pytest.mark.parametrize("in_place", [False, True], ids=["apart", "in_place"])
+def test_gemm_tcgen05_many_rows_staged_residual(M, N, K, tile_n, in_place):
+    """The residual epilogue through shared memory by TMA (rows that end inside a tile, columns that end inside
+    a chunk, the residual apart from the output or the output itself): the same bits as the epilogue in which
+    a thread owns a row, and the plain float32 product."""
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(41)
+    a, w = rs.randn(M, K).astype(np.float32), (rs.randn(N, K) / np.sqrt(K)).astype(np.float32)
+    bias, res = rs.randn(N).astype(np.float32), rs.randn(M, N).astype(np.float32)
+    A, W = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    want = (A.float() @ W.float().t()).double().cpu().numpy() + bias + res
+    try:
+        ops.set_split(0)
+        outs = []
+        for staged in (False, True):
+            ops.set_staged(staged)
+            R = dev(res)
+            out = ops.gemm_tc_prefill(A, W, dev(bias), "none", R, out_dtype=torch.float32, out=R if in_place else None,
+                                      tile_n=tile_n, pair=False)
+            torch.cuda.synchronize()
+            assert ops.tc_error() == 0
+            assert in_place or torch.equal(R, dev(res))        # the residual is only read
+            assert (ops.last_staged() > 0) == (staged and M >= 128)
+            outs.append(out.clone())
+        assert np.abs(outs[1].cpu().numpy() - want).max() < 1e-3
+        assert torch.equal(outs[0], outs[1])
+    finally:
+        ops.set_staged(True)
+        ops.set_split(None)
+
+
 def test_gemm_prefill_split_files_keys_and_values():
     """The split form as a q | k | v projection: the CTA that finishes a share of the columns also stores
     the keys and values among them into the paged cache."""

@@ -981,6 +981,15 @@ AYK_EXPORT int ayk_gemm_tc_prefill_tile_k(int M, int N, int K, int sms, int wide
   return best;
 }
 
+// What the one-SM product would do for this shape on `sms` SMs: its tile width, and into how many parts it
+// would split the K blocks of a tile (1: whole tiles).  Host arithmetic only; needs no device.
+AYK_EXPORT void ayk_gemm_tc_prefill_plan(int M, int N, int K, int sms, int wide_rows, int* tile, int* parts) {
+  int bn = ayk_gemm_tc_prefill_tile_k(M, N, K, sms, wide_rows), sp = 1, sbn = 0, ssp = 0;
+  if (split_pays(M, N, K, sms, 0, wide_rows != 0, &sbn, &ssp)) { bn = sbn; sp = ssp; }
+  if (tile) *tile = bn;
+  if (parts) *parts = sp;
+}
+
 // The same for pairs of SMs on tiles of 256 rows (sms / 2 pairs).
 AYK_EXPORT int ayk_gemm_tc_pair_tile(int M, int N, int sms) {
   int best = 256;

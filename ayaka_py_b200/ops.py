@@ -82,6 +82,16 @@ def set_staged(on: bool) -> None:
     _ready().ayk_gemm_tc_prefill_staged(ctypes.c_int(1 if on else 0))
 
 
+def prefill_plan(M: int, N: int, K: int, sms: int = 148, wide_rows: bool = False) -> tuple[int, int]:
+    """(tile width, parts of K per tile) that ``gemm_tc_prefill`` picks for an [M, K] x [N, K]^T product
+    on ``sms`` SMs; ``wide_rows``: the epilogue reads or writes 32-bit rows.  Host arithmetic from the
+    kernel's fitted time model: works without a GPU."""
+    tile, parts = ctypes.c_int(0), ctypes.c_int(0)
+    library().ayk_gemm_tc_prefill_plan(ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(sms),
+                                       ctypes.c_int(1 if wide_rows else 0), ctypes.byref(tile), ctypes.byref(parts))
+    return tile.value, parts.value
+
+
 def last_staged() -> int:
     """Buffers per half through which the last ``gemm_tc_prefill`` staged its residual (0: it did not)."""
     return int(_ready().ayk_gemm_tc_prefill_last_staged())

@@ -228,6 +228,61 @@ def run_prefill(engine, config, repeats: int = 3):
     return {"tokens": T, "ms": ms, "flops": flops}
 
 
+def run_products(rows=(16, 64, 128, 256, 512, 576, 1024, 2048, 4096)):
+    """The four products of an XL layer through ``ops.linear`` (the engine's dispatcher) over row
+    counts, each timed as a CUDA graph of 24 products with eight weights in turn (160 MB for the
+    widest: larger than L2), beside ``torch.matmul`` on the same operands as a yardstick (a library
+    product is nowhere on the engine's path).  Plain bfloat16 out, no bias."""
+    import torch
+
+    from ayaka_py_b200 import ops
+
+    dev = "cuda"
+    side = torch.cuda.Stream()
+
+    def chain(fn, n=24, reps=6):
+        with torch.cuda.stream(side):
+            fn()                                   # eager on the stream that is captured next: first-use set-up
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(n):
+                fn()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1000 / reps / n
+
+    d, inner = XL["n_embd"], XL["n_inner"]
+    out = []
+    for name, N, K in (("qkv", 3 * d, d), ("proj", d, d), ("fc", inner, d), ("proj2", d, inner)):
+        weights = [(torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(8)]
+        for M in rows:
+            x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+            y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            turn = [0]
+
+            def ours():
+                turn[0] += 1
+                ops.linear(x, weights[turn[0] % 8], out=y, out_dtype=torch.bfloat16)
+
+            def library():
+                turn[0] += 1
+                torch.matmul(x, weights[turn[0] % 8].t(), out=y)
+
+            t_ours, t_lib = chain(ours), chain(library)
+            tile, parts = ops.prefill_plan(M, N, K, ops.sm_count()) if M > 64 else (0, 0)
+            out.append({"product": name, "rows": M, "us": round(t_ours, 1), "library_us": round(t_lib, 1),
+                        "tflops": round(2.0 * M * N * K / t_ours / 1e6), "tile": tile, "k_parts": parts})
+    return out
+
+
 def run_small_continuous(layers: int | None = None, requests: int = 256, seed: int = 5):
     """GPT-2 small shape, 256 requests at t = 0 through ``LLM.generate``: prompts U[16,1024],
     outputs U[16,256] (cut where prompt + output would pass the model's 1,024 positions),
@@ -401,9 +456,10 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-graph", action="store_true", help="run decode steps eagerly")
     parser.add_argument("--no-points", action="store_true", help="only the decode steps at --batch")
-    parser.add_argument("--only", default=None, choices=("prefill", "small", "large"),
+    parser.add_argument("--only", default=None, choices=("prefill", "small", "large", "products"),
                         help="run one workload alone and print its numbers (for profiling): the 2,048-token prefill "
-                             "step, the small shape's continuous batching, or the large shape's mixed steps")
+                             "step, the small shape's continuous batching, the large shape's mixed steps, or the four "
+                             "products of an XL layer over row counts beside the library's matmul")
     args = parser.parse_args()
 
     if args.gpus != 1:
@@ -423,6 +479,10 @@ def main() -> int:
 
     pk = peaks()
     graph = not args.no_graph
+    if args.only == "products":
+        for row in run_products():
+            print(json.dumps(row))
+        return 0
     if args.only == "small":
         print(json.dumps({"small_continuous": run_small_continuous(None if args.layers == XL["n_layer"] else args.layers)}))
         return 0

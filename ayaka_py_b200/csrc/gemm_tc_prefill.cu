@@ -64,21 +64,18 @@ struct PrefillArgs {
   const int* kv_pos;         // [M] the row's position
   const int* kv_table;       // [requests, kv_table_stride] pages
   int kv_table_stride, kv_page_size, kv_col0, kv_width;
-  // Split along K (one-SM form, when the tiles alone would leave most SMs idle): `splits` CTAs share a tile,
-  // each running an equal part of its K blocks.  Every CTA leaves its sums in its slot of `sk_ws` (128 x BN
-  // floats, column by column) and raises `sk_ready[cta]`; then each of the CTAs adds up, in the CTAs' order,
-  // the BN / splits columns that are its share and finishes them (bias, activation, residual, store).  The last of
-  // a tile's CTAs to finish (counted in `sk_done`) clears the tile's flags for the next launch.
+  // Split along K (one-SM form, when the tiles alone would leave most SMs idle): the `splits` CTAs of a
+  // thread-block cluster share a tile, each running an equal part of its K blocks.  When every CTA of the
+  // cluster is through with its main loop, each sends the others the columns of its sums that are theirs,
+  // into their shared memory (the ring, idle by then); then each adds up, in the CTAs' order, the BN / splits
+  // columns that are its share and finishes them (bias, activation, residual, store).  No global scratch.
+  int splits;
   // Staged residual epilogue (one-SM form, float32 out over a float32 residual): the residual rows come by
   // TMA into shared memory, 128 rows x 32 columns at a time and a chunk ahead, the sums go back to the same
   // place and leave by a TMA store: whole 128-byte lines both ways, where a thread that owns a row would
   // otherwise read and write 16 bytes of 32 different lines per instruction.  staged = buffers per half of
   // the tile's columns (1 or 2; 0: the form is not taken): two where the ring keeps four stages beside them.
   int staged;
-  int splits;
-  float* sk_ws;
-  int* sk_ready;
-  int* sk_done;
 };
 
 // Where the keys of row `row` go: element offset of the row's place in a cache tensor, or -1 (a row
@@ -203,49 +200,49 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// The raw sums of `cols` columns of one accumulator row (cols a multiple of 16) into a slot of the split
-// form.  A slot holds a tile column by column, 128 rows each: a thread owns a row, so the 32 threads of a
-// warp write (and later read) 128 contiguous bytes per column.  `dst`: the row's place in the first column.
-__device__ __forceinline__ void store_partial_row(uint32_t taddr, float* dst, int cols) {
-  int c = 0;
-  for (; c + 32 <= cols; c += 32) {
-    uint32_t r[32];
-    tmem_ld32(taddr + c, r);
-    tmem_ld_wait();
-#pragma unroll
-    for (int j = 0; j < 32; ++j) dst[(c + j) * BM] = __uint_as_float(r[j]);
-  }
-  if (c < cols) {
+// Split along K: where the sums of the cluster's CTAs meet.  In every CTA the ring holds `splits` slots, one per
+// sending CTA, of 128 rows by (share + 4) floats (share = BN / splits columns; the 16 bytes more keep the rows of
+// a warp off each other's banks).
+__device__ __forceinline__ uint32_t split_row_bytes(int share) { return (uint32_t)(share + 4) * 4u; }
+
+// This thread's `cols` accumulator columns (a multiple of 16, from tile column c0 on) of row `row_in_tile`, each
+// 16-byte piece into the shared memory of the CTA that owns its columns.
+__device__ __forceinline__ void send_partial_row(uint32_t taddr, uint32_t recv, int my_rank, int share, int row_in_tile, int c0,
+                                                 int cols) {
+  const uint32_t row_bytes = split_row_bytes(share);
+  const uint32_t mine = recv + ((uint32_t)my_rank * BM + (uint32_t)row_in_tile) * row_bytes;     // offset within any CTA
+  for (int c = 0; c < cols; c += 16) {
     uint32_t r[16];
     tmem_ld16(taddr + c, r);
     tmem_ld_wait();
 #pragma unroll
-    for (int j = 0; j < 16; ++j) dst[(c + j) * BM] = __uint_as_float(r[j]);
+    for (int j = 0; j < 16; j += 4) {
+      const int col = c0 + c + j, owner = col / share;
+      st_cluster_v4(map_to_cta(mine + (uint32_t)(col - owner * share) * 4u, (uint32_t)owner), __uint_as_float(r[j]),
+                    __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+    }
   }
 }
 
-// This CTA's share of a tile whose K blocks were split over `splits` CTAs: `cols` columns (a multiple of 8)
-// from column `c0` of the tile on, for the row `row_in_tile`, summed over the CTAs' slots (`slots` is the
-// first CTA's; in the CTAs' order, so every run adds alike) and finished eight columns at a time.
-__device__ __forceinline__ void finish_split_cols(const PrefillArgs& a, const float* slots, int splits, int BN, int m0, int n0,
+// This CTA's share of the tile: `cols` columns (a multiple of 8) from column `c0` of the share on, for the row
+// `row_in_tile`, summed over the slots (in the CTAs' order, so every run adds alike) and finished eight columns
+// at a time.  n0: the first column of the share in the matrix.
+__device__ __forceinline__ void finish_split_cols(const PrefillArgs& a, uint32_t recv, int splits, int share, int m0, int n0,
                                                   int row_in_tile, int c0, int cols) {
   const int row = m0 + row_in_tile;
   if (row >= a.M) return;
-  const long long slot_floats = (long long)BM * BN;
+  const uint32_t row_bytes = split_row_bytes(share), slot_bytes = BM * row_bytes;
   const long long place = cache_place(a, row);
   for (int c = c0; c < c0 + cols; c += 8) {
     const int col = n0 + c;
     if (col >= a.N) break;                         // N is a multiple of 8: a group lies inside the matrix or outside
-    const float* src = slots + (long long)c * BM + row_in_tile;
-    float y[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) y[j] = __ldcg(src + j * BM);
-    for (int p = 1; p < splits; ++p) {
-      float v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + p * slot_floats + j * BM);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) y[j] += v[j];
+    const uint32_t at = recv + (uint32_t)row_in_tile * row_bytes + (uint32_t)c * 4u;
+    float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < splits; ++p) {
+      float4 lo, hi;
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w) : "r"(at + p * slot_bytes));
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w) : "r"(at + p * slot_bytes + 16u));
+      y[0] += lo.x; y[1] += lo.y; y[2] += lo.z; y[3] += lo.w; y[4] += hi.x; y[5] += hi.y; y[6] += hi.z; y[7] += hi.w;
     }
     if (a.bias) {
       const float4 b0 = __ldg(reinterpret_cast<const float4*>(a.bias + col)), b1 = __ldg(reinterpret_cast<const float4*>(a.bias + col + 4));
@@ -317,7 +314,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   const int first_tile = splits > 1 ? (int)blockIdx.x / splits : (int)blockIdx.x;
   const int tile_step = splits > 1 ? total_tiles : (int)gridDim.x;          // one tile per CTA when K is split
   const int part_kb = splits > 1 ? (num_kb + splits - 1) / splits : num_kb;
-  const int kb_first = splits > 1 ? ((int)blockIdx.x % splits) * part_kb : 0;
+  const int kb_first = splits > 1 ? ((int)blockIdx.x % splits) * part_kb : 0;      // the cluster runs along x: rank = blockIdx.x % splits
   const int kb_last = min(num_kb, kb_first + part_kb);                       // this CTA's K blocks of each of its tiles
   const int my_kb = kb_last - kb_first;
   const int my_tiles = (first_tile < total_tiles) ? (total_tiles - 1 - first_tile) / tile_step + 1 : 0;
@@ -429,59 +426,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     }
     __syncwarp();
   } else if (splits > 1) {
-    // ---- K split over `splits` CTAs: one tile, one part of its K blocks (see PrefillArgs)
-    pdl_wait();
-    const int e = warp - 2;
-    const int quarter = warp & 3, half = e >> 2;
-    const int half_cols = BN >> 1;
-    bool ok = my_tiles == 1;
-    if (ok) {
-      const int tile = first_tile, part = (int)blockIdx.x % splits, cta0 = (int)blockIdx.x - part;
-      const int m0 = (tile / args.n_tiles) * BM, n0 = (tile % args.n_tiles) * BN;
-      const long long slot_floats = (long long)BM * BN;
-      if (lane == 0) ok = mbar_wait(tmem_full(0), 0u, args.error, 25);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (ok) {
-        tc_fence_after();
-        const int row_in_tile = quarter * 32 + lane;
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
-        store_partial_row(taddr, args.sk_ws + (long long)blockIdx.x * slot_floats + (long long)(half * half_cols) * BM + row_in_tile,
-                          half_cols);
-        tc_fence_before();
-        __threadfence();
-        asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
-        if (warp == 2 && lane == 0)
-          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(args.sk_ready + blockIdx.x), "r"(1) : "memory");
-        if (lane == 0) {
-          for (int p = 0; p < splits && ok; ++p) {
-            const int* flag = args.sk_ready + cta0 + p;
-            bool seen = false;
-            for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-              int v;
-              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-              if (v != 0) { seen = true; break; }
-            }
-            if (!seen) { atomicExch(args.error, 26); ok = false; }
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (ok) {
-          // this CTA's columns of the tile, half of them for each of the two warps that own a row
-          const int share = BN / splits, mine = share >> 1;
-          finish_split_cols(args, args.sk_ws + (long long)cta0 * slot_floats, splits, BN, m0, n0, row_in_tile,
-                            part * share + half * mine, mine);
-        }
-        // The tile's last CTA out clears its flags (each CTA counts itself once, finished or given up).
-        asm volatile("bar.sync 2, %0;" ::"n"(EPI_WARPS * 32) : "memory");
-        if (warp == 2 && lane == 0) {
-          __threadfence();
-          if (atomicAdd(args.sk_done + cta0, 1) == splits - 1) {
-            for (int p = 0; p < splits; ++p) args.sk_ready[cta0 + p] = 0;
-            args.sk_done[cta0] = 0;
-          }
-        }
-      }
-    }
+    pdl_wait();            // the residual and C belong to earlier kernels until here; the work follows below, with the whole CTA
   } else if (args.staged) {
     // ---- float32 out over a float32 residual, both through shared memory by TMA (see PrefillArgs)
     pdl_wait();
@@ -578,6 +523,35 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty(b));
+    }
+  }
+
+  if (splits > 1) {
+    // ---- K split over the CTAs of a cluster: one tile, one part of its K blocks each (see PrefillArgs).  Every
+    // thread of the cluster meets at the two barriers, whatever happened to its waits.
+    const int e = warp - 2;
+    const int quarter = warp & 3, half = e >> 2;
+    const int half_cols = BN >> 1, share = BN / splits;
+    const int part = (int)cluster_rank();
+    const int row_in_tile = quarter * 32 + lane;
+    bool ok = my_tiles == 1;
+    if (warp >= 2 && ok) {
+      if (lane == 0) ok = mbar_wait(tmem_full(0), 0u, args.error, 25);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      tc_fence_after();
+    }
+    cluster_sync_all();                          // every CTA's MMAs have read its ring for the last time
+    if (warp >= 2 && ok) {
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
+      send_partial_row(taddr, tiles, part, share, row_in_tile, half * half_cols, half_cols);
+      tc_fence_before();
+    }
+    cluster_sync_all();                          // the sums of all CTAs have arrived (release / acquire at cluster scope)
+    if (warp >= 2 && ok) {
+      const int tile = first_tile;
+      const int m0 = (tile / args.n_tiles) * BM, n0 = (tile % args.n_tiles) * BN + part * share;
+      const int mine = share >> 1;               // half of the share for each of the two warps that own a row
+      finish_split_cols(args, tiles, splits, share, m0, n0, row_in_tile, half * mine, mine);
     }
   }
 
@@ -777,6 +751,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
 // ------------------------------------------------------------------- host --
 
+void prefill_kernel_symbol(const void** fn) { *fn = (const void*)gemm_tc_prefill_kernel; }
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -834,42 +810,45 @@ int encode(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
 int g_split = -1;
 int g_last_splits = 1;          // parts per tile of the last one-SM launch (1: whole tiles), for tests and tuning
 
-// Scratch of the split form, per device and stream: a slot of 128 x 256 floats and two flags per CTA.  The
-// kernels of one stream run one after the other and clear their flags themselves, so they share a space;
-// a second stream that runs products at the same time gets its own.  Made at the first use, never while the
-// stream is being captured (the product then runs unsplit).
-struct SplitSpace { int device; cudaStream_t stream; float* ws; int* ready; int* done; int ctas; };
-std::vector<SplitSpace*> g_split_spaces;
-SplitSpace* split_space(int ctas, cudaStream_t stream) {
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
-  std::lock_guard<std::mutex> lock(g_mutex);
-  for (SplitSpace* sp : g_split_spaces)
-    if (sp->device == device && sp->stream == stream && sp->ctas >= ctas) return sp;
-  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+// How many clusters of `size` CTAs of the one-SM kernel the device runs at once.  A cluster lives inside one
+// GPC, so fewer CTAs run at once the larger the cluster (on a B200 of 148 SMs: 72 pairs, 32 clusters of 4,
+// 16 of 8).  Asked of the driver once per device where there is one; estimated from GPCs of 18 SMs otherwise
+// (the plan can be asked for without a GPU).
+void prefill_kernel_symbol(const void** fn);
+int cluster_capacity(int sms, int size) {
+  static int cached[64][9] = {};
+  int device = -1;
+  if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < 64 && size <= 8) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (cached[device][size] == 0 && g_configured) {         // once the kernel's shared memory has been granted
+      const void* fn = nullptr;
+      prefill_kernel_symbol(&fn);
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(size * 64);
+      cfg.blockDim = dim3(THREADS);
+      cfg.dynamicSmemBytes = SMEM_BYTES;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = size; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) == cudaSuccess && n > 0) cached[device][size] = n;
+      else { cudaGetLastError(); cached[device][size] = -1; }
+    }
+    if (cached[device][size] > 0) return cached[device][size];
+  } else {
     cudaGetLastError();
-    return nullptr;
   }
-  if (g_split_spaces.size() >= 16) return nullptr;
-  SplitSpace* sp = new SplitSpace{device, stream, nullptr, nullptr, nullptr, ctas};
-  if (cudaMalloc((void**)&sp->ws, (size_t)ctas * BM * 256 * sizeof(float)) != cudaSuccess ||
-      cudaMalloc((void**)&sp->ready, 2 * (size_t)ctas * sizeof(int)) != cudaSuccess ||
-      cudaMemset(sp->ready, 0, 2 * (size_t)ctas * sizeof(int)) != cudaSuccess) {
-    cudaGetLastError();
-    if (sp->ws) cudaFree(sp->ws);
-    if (sp->ready) cudaFree(sp->ready);
-    delete sp;
-    return nullptr;
-  }
-  sp->done = sp->ready + ctas;
-  g_split_spaces.push_back(sp);
-  return sp;
+  const int gpcs = sms / 18 > 0 ? sms / 18 : 1;
+  return gpcs * (18 / size);
 }
 
-// May a tile's K blocks be split `splits` ways?  Every part must hold a K block.
+// May a tile's K blocks be split over a cluster of `splits` CTAs?  Every tile's cluster runs at once, every
+// part holds a K block, every CTA's share of the columns is whole 16-column pieces.
 bool split_fits(int tiles, int num_kb, int splits, int sms, int bn) {
-  if (splits < 2 || splits > 8 || bn % (16 * splits) != 0 || (long long)tiles * splits > sms) return false;
+  if (splits < 2 || splits > 8 || bn % (16 * splits) != 0 || tiles > cluster_capacity(sms, splits)) return false;
+  if (BM * (bn + 4 * splits) * 4 > SMEM_TILES) return false;        // the sums meet in the ring
   const int part = (num_kb + splits - 1) / splits;
   return part >= 2 && (splits - 1) * part < num_kb;
 }
@@ -878,10 +857,11 @@ double kblock_us(int a_rows, int bn, int active);              // the model of t
 double whole_tiles_us(int M, int N, int K, int bn, int sms, bool wide_rows);
 
 // Does splitting K beat whole tiles going round the CTAs, and with which tile width and how many parts?
-// Times from the model above; leaving the sums in scratch, waiting for the other parts and adding them up
-// costs the split form about 6 us + 25 ns per column of the tile on top of its K blocks (measured 7 us at 64
-// columns, 12 us at 256).
-constexpr double SPLIT_FIX_US = 6.0, SPLIT_FIX_PER_COL = 0.025;
+// Times from the model above; the two cluster barriers, the exchange of the sums through shared memory and
+// their addition cost the split form about 1 us + 24 ns per column of the tile + 0.45 us per CTA of the
+// cluster on top of its K blocks (measured: 2 us for two CTAs and 64 columns, 5.5 for two and 192, 3.5 for
+// four and 64, 7.6 for eight and 128).
+constexpr double SPLIT_FIX_US = 1.0, SPLIT_FIX_PER_COL = 0.024, SPLIT_FIX_PER_CTA = 0.45;
 bool split_pays(int M, int N, int K, int sms, int tile_n, bool wide_rows, int* bn_out, int* splits_out) {
   const int m_tiles = (M + BM - 1) / BM, num_kb = (K + BLOCK_K - 1) / BLOCK_K;
   if (N % 8 != 0) return false;
@@ -898,11 +878,11 @@ bool split_pays(int M, int N, int K, int sms, int tile_n, bool wide_rows, int* b
     for (int sp = 2; sp <= 8; sp *= 2) {
       if (!split_fits((int)tiles, num_kb, sp, sms, bn)) continue;
       const double us = 3.4 + (double)((num_kb + sp - 1) / sp) * kblock_us(M >= BM ? BM : (M + 7) / 8 * 8, bn, (int)tiles * sp) +
-                        SPLIT_FIX_US + SPLIT_FIX_PER_COL * bn;
+                        SPLIT_FIX_US + SPLIT_FIX_PER_COL * bn + SPLIT_FIX_PER_CTA * sp;
       if (best_split < 0 || us < best_split) { best_split = us; *bn_out = bn; *splits_out = sp; }
     }
   }
-  return best_split > 0 && best_split < 0.9 * best_whole;
+  return best_split > 0 && best_split < 0.95 * best_whole;
 }
 
 // rows x n float32, row-major; box of 128 rows x 32 columns (128 bytes), 128-byte swizzle: a chunk of the
@@ -1161,11 +1141,8 @@ int prefill_product(void* C, const void* X, const void* W, const float* bias, co
   int grid_x = total < sms ? total : sms;
   args.splits = 1;
   if (splits > 1 && N % 8 == 0 && args.vec_ok && split_fits(total, (K + BLOCK_K - 1) / BLOCK_K, splits, sms, BN)) {
-    SplitSpace* space = split_space(sms, stream);
-    if (space != nullptr) {
-      args.splits = splits; args.sk_ws = space->ws; args.sk_ready = space->ready; args.sk_done = space->done;
-      grid_x = total * splits;
-    }
+    args.splits = splits;
+    grid_x = total * splits;
   }
   g_last_splits = args.splits;
   // float32 out over a float32 residual: both through shared memory by TMA when the tile's halves are whole
@@ -1187,6 +1164,22 @@ int prefill_product(void* C, const void* X, const void* W, const float* bias, co
     }
   }
   g_last_staged = args.staged;
+  if (args.splits > 1) {                          // the CTAs of a tile as one cluster along x
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid_x);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = args.splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ayk_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, gemm_tc_prefill_kernel, mx, mw, mr, mc, args);
+    return ayk_check_launch("ayk_gemm_tc_prefill (K split over a cluster)");
+  }
   dim3 grid(grid_x);
   ayk_launch(gemm_tc_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mx, mw, mr, mc, args);
   return ayk_check_launch("ayk_gemm_tc_prefill");

@@ -70,8 +70,9 @@ def set_pdl(on: bool) -> None:
 
 def set_split(parts: int | None) -> None:
     """Split along K in the product for many rows (``gemm_tc_prefill``, one-SM form): when the tiles
-    alone would leave most SMs idle, 2, 4 or 8 CTAs share a tile, each with an equal part of its K
-    blocks; they leave their sums in scratch and each finishes a share of the tile's rows.  None: the
+    alone would leave most SMs idle, the 2, 4 or 8 CTAs of a cluster share a tile, each with an equal
+    part of its K blocks; they exchange their sums through shared memory and each finishes a share of
+    the tile's columns.  None: the
     library decides per product (the default); 0: never; 2, 4, 8: wherever the tiles allow it."""
     _ready().ayk_gemm_tc_prefill_split(ctypes.c_int(-1 if parts is None else int(parts)))
 

@@ -481,19 +481,20 @@ def test_gemm_tcgen05_many_rows(M, N, K, tile_n, act, out_dtype, pair):
 
 
 SPLIT_GEMM_CASES = [
-    # M, N, K, tile_n, parts: tiles * parts fit the SMs, the tile width is a multiple of 16 * parts
-    (128, 1600, 6400, 128, 8), (300, 200, 1600, 64, 4), (130, 328, 1000, 96, 2), (576, 1600, 6400, 256, 4),
+    # M, N, K, tile_n, parts: the tiles' clusters all run at once, the tile width is a multiple of 16 * parts
+    (128, 1600, 6400, 128, 8), (300, 200, 1600, 64, 4), (130, 328, 1000, 96, 2), (512, 1600, 6400, 256, 4),
     (129, 72, 4096, 32, 2), (1024, 264, 712, 128, 2), (200, 768, 3072, 128, 8), (70, 1600, 6400, 128, 8), (17, 64, 512, 64, 4),
+    (1024, 1600, 6400, 192, 2),
 ]
 
 
 @pytest.mark.parametrize("M,N,K,tile_n,parts", SPLIT_GEMM_CASES)
 @pytest.mark.parametrize("act,out_dtype", [("none", "float32"), ("gelu_tanh", "bfloat16")])
 def test_gemm_tcgen05_many_rows_split_along_k(M, N, K, tile_n, parts, act, out_dtype):
-    """The many-row product with the K blocks of a tile split over 2, 4 or 8 CTAs (sums left in scratch,
-    each CTA finishing its share of the columns): the plain float32 product, the unsplit kernel to
-    rounding of the sums, the same bits in a second run (flags cleared, sums added in a fixed order), in
-    place over the residual, and the library's own choice."""
+    """The many-row product with the K blocks of a tile split over a cluster of 2, 4 or 8 CTAs (sums
+    exchanged through shared memory, each CTA finishing its share of the columns): the plain float32
+    product, the unsplit kernel to rounding of the sums, the same bits in a second run (sums added in a
+    fixed order), in place over the residual, and the library's own choice."""
     from ayaka_py_b200 import ops
     rs = np.random.RandomState(31)
     a, w = rs.randn(M, K).astype(np.float32), (rs.randn(N, K) / np.sqrt(K)).astype(np.float32)

@@ -16,18 +16,20 @@ SMALL = {"qkv": (2304, 768), "proj": (768, 768), "fc": (3072, 768), "proj2": (76
 
 @pytest.mark.parametrize("shape,M,tile", [
     (XL["qkv"], 2048, 192), (XL["fc"], 2048, 256), (XL["proj"], 2048, 192), (XL["qkv"], 1024, 160), (XL["fc"], 768, 160),
-    (XL["fc"], 256, 96), (XL["proj"], 768, 96), (XL["qkv"], 512, 160), (XL["qkv"], 128, 64),
-    (SMALL["qkv"], 2048, 256), (SMALL["fc"], 2048, 192), (SMALL["proj"], 2048, 96), (SMALL["proj2"], 2048, 96),
+    (XL["fc"], 256, 96), (XL["proj"], 768, 96), (XL["qkv"], 512, 160),
+    (SMALL["qkv"], 2048, 256), (SMALL["fc"], 2048, 192), (SMALL["proj"], 2048, 96),
 ])
 def test_tile_width_is_the_measured_best(shape, M, tile):
     N, K = shape
     assert ops.prefill_plan(M, N, K) == (tile, 1)
 
 
-@pytest.mark.parametrize("M,tile,parts", [(128, 128, 8), (256, 128, 4), (512, 192, 4), (768, 160, 2)])
-def test_long_k_with_few_tiles_is_split(M, tile, parts):
-    N, K = XL["proj2"]
-    assert ops.prefill_plan(M, N, K) == (tile, parts)
+@pytest.mark.parametrize("shape,M", [(XL["proj2"], 128), (XL["proj2"], 256), (XL["proj2"], 576), (XL["proj2"], 1024),
+                                     (SMALL["proj2"], 128), (SMALL["proj2"], 512), (SMALL["proj2"], 2048), (XL["proj"], 128)])
+def test_long_k_with_few_tiles_is_split(shape, M):
+    N, K = shape
+    tile, parts = ops.prefill_plan(M, N, K)
+    assert parts > 1, (tile, parts)
 
 
 def test_a_split_fits_the_sms_and_the_tile():
@@ -40,6 +42,7 @@ def test_a_split_fits_the_sms_and_the_tile():
                     tiles = -(-M // 128) * -(-N // tile)
                     blocks = -(-K // 64)
                     assert tiles * parts <= sms and tile % (16 * parts) == 0 and N % 8 == 0
+                    assert 128 * (tile + 4 * parts) * 4 <= 196608                # the sums meet in the stage ring
                     assert (parts - 1) * -(-blocks // parts) < blocks       # every part has a K block
 
 

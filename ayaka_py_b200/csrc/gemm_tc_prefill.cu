@@ -43,6 +43,8 @@ constexpr int THREADS = 320;
 constexpr int EPI_WARPS = 8;
 constexpr int MAX_STAGES = 8;
 constexpr int SMEM_TILES = 196608;             // bytes available to the stage ring
+constexpr int TURNED_ROW_BYTES = 144;           // a row of the turned epilogue's 32 x 32 floats: 128 bytes + 16, which keeps 8 rows off each other's banks
+constexpr int TURNED_BYTES = EPI_WARPS * 32 * TURNED_ROW_BYTES;
 constexpr int STAGED_CHUNK = 16384;            // a buffer of the staged residual epilogue: 128 rows x 32 floats; it takes 2 halves x 1 or 2 of them
 
 struct PrefillArgs {
@@ -76,6 +78,11 @@ struct PrefillArgs {
   // otherwise read and write 16 bytes of 32 different lines per instruction.  staged = buffers per half of
   // the tile's columns (1 or 2; 0: the form is not taken): two where the ring keeps four stages beside them.
   int staged;
+  // Turned epilogue (one-SM form, rows of C that are no whole 16-byte pieces, as the 50,257 columns of an LM
+  // head give them): a warp leaves its 32 rows x 32 columns in shared memory and stores them row by row, a
+  // lane per column, so that an instruction writes one run of up to 128 contiguous bytes whatever the rows'
+  // alignment, where a thread that owns a row would store 32 separate elements.  No residual in this form.
+  int turned;
 };
 
 // Where the keys of row `row` go: element offset of the row's place in a cache tensor, or -1 (a row
@@ -427,6 +434,62 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     __syncwarp();
   } else if (splits > 1) {
     pdl_wait();            // the residual and C belong to earlier kernels until here; the work follows below, with the whole CTA
+  } else if (args.turned) {
+    // ---- rows of C that are no whole 16-byte pieces: through shared memory, stored a row at a time (see PrefillArgs)
+    pdl_wait();
+    const int e = warp - 2;
+    const int quarter = warp & 3, half = e >> 2;
+    const int half_cols = BN >> 1;
+    const uint32_t mine = tiles + (uint32_t)(SMEM_TILES - TURNED_BYTES) + (uint32_t)e * 32u * TURNED_ROW_BYTES;
+    const int act = args.act;
+    bool ok = true;
+    for (int t = 0; t < my_tiles && ok; ++t) {
+      const int b = t & 1;
+      const int tile = blockIdx.x + t * gridDim.x;
+      const int m0 = (tile / args.n_tiles) * BM + quarter * 32, nh = (tile % args.n_tiles) * BN + half * half_cols;
+      if (lane == 0) ok = mbar_wait(tmem_full(b), (uint32_t)(t >> 1) & 1u, args.error, 25);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t)b * 256u + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * half_cols);
+      for (int c = 0; c < half_cols; c += 32) {
+        const int w = min(32, half_cols - c);          // 32, or 16 at the end of a half of 48, 80 or 112 columns
+        uint32_t r[32];
+        if (w == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
+        tmem_ld_wait();
+        // this thread's row of the chunk into shared memory ...
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          if (j < w)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(mine + (uint32_t)lane * TURNED_ROW_BYTES + (uint32_t)j * 4u),
+                         "f"(__uint_as_float(r[j])), "f"(__uint_as_float(r[j + 1])), "f"(__uint_as_float(r[j + 2])),
+                         "f"(__uint_as_float(r[j + 3])) : "memory");
+        }
+        __syncwarp();
+        // ... and the warp's 32 rows out, a row an instruction, this lane's column of each
+        const int col = nh + c + lane;
+        const bool col_ok = lane < w && col < args.N;
+        const float bias = (col_ok && args.bias) ? __ldg(args.bias + col) : 0.f;
+        for (int i = 0; i < 32; ++i) {
+          const int row = m0 + i;
+          if (row >= args.M) break;
+          float v;
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(mine + (uint32_t)i * TURNED_ROW_BYTES + (uint32_t)lane * 4u));
+          if (col_ok) {
+            v += bias;
+            if (act == AYK_ACT_GELU_TANH) v = apply_activation_tc<AYK_ACT_GELU_TANH>(v, act);
+            else if (act != AYK_ACT_NONE) v = apply_activation(v, act);
+            const size_t idx = (size_t)row * args.N + col;
+            if (args.out_bf16) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(v);
+            else ((float*)args.C)[idx] = v;
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty(b));
+    }
   } else if (args.staged) {
     // ---- float32 out over a float32 residual, both through shared memory by TMA (see PrefillArgs)
     pdl_wait();
@@ -1164,6 +1227,15 @@ int prefill_product(void* C, const void* X, const void* W, const float* bias, co
     }
   }
   g_last_staged = args.staged;
+  // rows of C that are no whole 16-byte pieces (N no multiple of 8), no residual: the turned epilogue
+  args.turned = 0;
+  if (g_staged && args.splits == 1 && !args.vec_ok && residual == nullptr && args.mode != 4) {
+    const int left = (SMEM_TILES - TURNED_BYTES) / (A_BYTES + BN * BLOCK_K * 2);
+    if (left >= 3) {
+      args.turned = 1;
+      args.stages = left > MAX_STAGES ? MAX_STAGES : left;
+    }
+  }
   if (args.splits > 1) {                          // the CTAs of a tile as one cluster along x
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid_x);

@@ -566,6 +566,35 @@ def test_gemm_tcgen05_many_rows_staged_residual(M, N, K, tile_n, in_place):
         ops.set_split(None)
 
 
+@pytest.mark.parametrize("M,N,K,tile_n", [(200, 50257, 64, 0), (129, 331, 72, 96), (1000, 1003, 328, 160), (65, 77, 200, 32),
+                                          (300, 4802, 1600, 0)])
+@pytest.mark.parametrize("act,out_dtype", [("none", "float32"), ("gelu_tanh", "bfloat16")])
+def test_gemm_tcgen05_many_rows_of_odd_width(M, N, K, tile_n, act, out_dtype):
+    """Output rows that are no whole 16-byte pieces (an LM head's 50,257 columns) and no residual: the epilogue
+    that turns a warp's 32 x 32 block in shared memory and stores it a row at a time gives the bits of the
+    epilogue that stores element by element, and the plain float32 product."""
+    from ayaka_py_b200 import ops
+    rs = np.random.RandomState(51)
+    a, w = rs.randn(M, K).astype(np.float32), (rs.randn(N, K) / np.sqrt(K)).astype(np.float32)
+    bias = rs.randn(N).astype(np.float32)
+    A, W = dev(a, torch.bfloat16), dev(w, torch.bfloat16)
+    y = (A.float() @ W.float().t()).double() + dev(bias).double()
+    want = (torch.nn.functional.gelu(y, approximate="tanh") if act != "none" else y).cpu().numpy()
+    try:
+        outs = []
+        for turned in (False, True):
+            ops.set_staged(turned)
+            out = ops.gemm_tc_prefill(A, W, dev(bias), act, None, out_dtype=DTYPES[out_dtype], tile_n=tile_n, pair=False)
+            torch.cuda.synchronize()
+            assert ops.tc_error() == 0
+            outs.append(out)
+        err = np.abs(outs[1].float().cpu().numpy() - want).max()
+        assert err < (1e-3 if out_dtype == "float32" else 5e-2), err
+        assert torch.equal(outs[0], outs[1])
+    finally:
+        ops.set_staged(True)
+
+
 def test_gemm_prefill_split_files_keys_and_values():
     """The split form as a q | k | v projection: the CTA that finishes a share of the columns also stores
     the keys and values among them into the paged cache."""

@@ -88,8 +88,8 @@ AYK_EXPORT int ayk_linear(void* out, const void* a, const void* w, const float* 
     // Up to 64 rows with few output tiles: weights as the MMA's M side, K split over a cluster.  More
     // rows: tiles of 128 rows by a width from the kernel's time model.  (An out width that is no multiple
     // of 8 makes rows of C that are no whole 16-byte pieces: the many-row kernel turns such tiles in
-    // shared memory and stores them a row at a time, which beats the first kernel from 65 rows on, 30
-    // against 42 us for 65 rows of an LM head of 50,257 columns; with a residual to add, up to 128 rows
+    // shared memory and stores them a row at a time, which beats the first kernel from 17 rows on, 30
+    // against 38 us for 64 rows of an LM head of 50,257 x 768; with a residual to add, up to 128 rows
     // stay with the first kernel, whose loads and stores run along the features.)
     int splits = 1;
     if (M <= CLUSTER_ROWS) splits = ayk_tc_splits(M, N, K);
@@ -97,7 +97,7 @@ AYK_EXPORT int ayk_linear(void* out, const void* a, const void* w, const float* 
       const int cluster = splits > 1 ? 1 : 0;
       return ayk_gemm_tc(out, a, w, bias, residual, M, N, K, act, out_dtype, splits, nullptr, nullptr, 1, cluster, stream);
     }
-    if (N % 8 == 0 || M > 128 || (M > CLUSTER_ROWS && residual == nullptr)) {
+    if (N % 8 == 0 || M > 128 || residual == nullptr) {
       if (kv != nullptr && N % 8 == 0 && act == AYK_ACT_NONE && residual == nullptr && out_dtype == AYK_DTYPE_BF16 &&
           kv->dtype == AYK_DTYPE_BF16 && kv->col0 % 8 == 0 && kv->width % 8 == 0 && N == kv->col0 + 2 * kv->width &&
           (bias == nullptr || (uintptr_t)bias % 16 == 0)) {

@@ -874,8 +874,8 @@ int g_split = -1;
 int g_last_splits = 1;          // parts per tile of the last one-SM launch (1: whole tiles), for tests and tuning
 
 // How many clusters of `size` CTAs of the one-SM kernel the device runs at once.  A cluster lives inside one
-// GPC, so fewer CTAs run at once the larger the cluster (on a B200 of 148 SMs: 72 pairs, 32 clusters of 4,
-// 16 of 8).  Asked of the driver once per device where there is one; estimated from GPCs of 18 SMs otherwise
+// GPC, so fewer CTAs run at once the larger the cluster (on a B200 of 148 SMs the driver says 74 pairs, 33
+// clusters of 4, 15 of 8).  Asked of the driver once per device where there is one; estimated from GPCs of 18 SMs otherwise
 // (the plan can be asked for without a GPU).
 void prefill_kernel_symbol(const void** fn);
 int cluster_capacity(int sms, int size) {
@@ -981,6 +981,9 @@ AYK_EXPORT void ayk_gemm_tc_prefill_split(int mode) { g_split = mode; }
 // applies (default), 0 never.
 AYK_EXPORT void ayk_gemm_tc_prefill_staged(int on) { g_staged = on ? 1 : 0; }
 AYK_EXPORT int ayk_gemm_tc_prefill_last_staged() { return g_last_staged; }
+// How many clusters of `size` CTAs of the one-SM kernel run at once (asked of the driver once a product has run on
+// the device, else estimated).
+AYK_EXPORT int ayk_gemm_tc_prefill_cluster_capacity(int sms, int size) { return cluster_capacity(sms, size); }
 // Into how many parts the last one-SM product split the K blocks of its tiles (1: it did not).
 AYK_EXPORT int ayk_gemm_tc_prefill_last_split() { return g_last_splits; }
 

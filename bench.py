@@ -27,6 +27,11 @@ Weights are random (seeded), token ids synthetic.  The inputs of every step
 between iterations.  ``--impl reference`` runs the unmodified reference from
 ``baseline/_ref`` (see ``baseline/reference_arm.py``) on the same shape, batch,
 prompts and step counts and prints the same line with ``"impl": "reference"``.
+
+``--only prefill|small|large|products`` runs one workload alone (for profiling):
+``products`` prints, a JSON line each, the four matrix products of an XL layer
+through the engine's dispatcher over row counts beside ``torch.matmul`` on the same
+operands.
 """
 
 from __future__ import annotations

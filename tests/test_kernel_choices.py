@@ -9,6 +9,13 @@ CUDA events); a change of the model that moves one of them has to be measured ag
 import pytest
 
 from ayaka_py_b200 import ops
+from ayaka_py_b200.csrc import build
+
+try:                                   # the library is there already, or nvcc is there to make it
+    if not build.library_path().is_file():
+        build.find_nvcc()
+except RuntimeError as problem:
+    pytest.skip(f"the CUDA library cannot be built here: {problem}", allow_module_level=True)
 
 XL = {"qkv": (4800, 1600), "proj": (1600, 1600), "fc": (6400, 1600), "proj2": (1600, 6400)}
 SMALL = {"qkv": (2304, 768), "proj": (768, 768), "fc": (3072, 768), "proj2": (768, 3072)}

@@ -208,26 +208,27 @@ __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.w
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Split along K: where the sums of the cluster's CTAs meet.  In every CTA the ring holds `splits` slots, one per
-// sending CTA, of 128 rows by (share + 4) floats (share = BN / splits columns; the 16 bytes more keep the rows of
-// a warp off each other's banks).
-__device__ __forceinline__ uint32_t split_row_bytes(int share) { return (uint32_t)(share + 4) * 4u; }
+// sending CTA, of `share` columns (share = BN / splits) by 128 rows of floats, a column's rows side by side: the
+// 32 threads of a warp own 32 consecutive rows, so their stores of one column are 128 contiguous bytes on their
+// way to the owner's shared memory, and the owner's loads of one column fall into 32 different banks.  (With a
+// row's columns side by side, 16 bytes per thread and row, the same exchange took 1 to 5 us longer: scattered
+// pieces are what the network between the SMs of a cluster is slow at.)
+constexpr uint32_t SPLIT_COL_BYTES = BM * 4u;
 
 // This thread's `cols` accumulator columns (a multiple of 16, from tile column c0 on) of row `row_in_tile`, each
-// 16-byte piece into the shared memory of the CTA that owns its columns.
+// into the shared memory of the CTA that owns it (share is a multiple of 16: sixteen columns have one owner).
 __device__ __forceinline__ void send_partial_row(uint32_t taddr, uint32_t recv, int my_rank, int share, int row_in_tile, int c0,
                                                  int cols) {
-  const uint32_t row_bytes = split_row_bytes(share);
-  const uint32_t mine = recv + ((uint32_t)my_rank * BM + (uint32_t)row_in_tile) * row_bytes;     // offset within any CTA
+  const uint32_t mine = recv + (uint32_t)my_rank * (uint32_t)share * SPLIT_COL_BYTES + (uint32_t)row_in_tile * 4u;   // offset within any CTA
   for (int c = 0; c < cols; c += 16) {
     uint32_t r[16];
     tmem_ld16(taddr + c, r);
     tmem_ld_wait();
+    const int col = c0 + c, owner = col / share;
+    const uint32_t at = map_to_cta(mine + (uint32_t)(col - owner * share) * SPLIT_COL_BYTES, (uint32_t)owner);
 #pragma unroll
-    for (int j = 0; j < 16; j += 4) {
-      const int col = c0 + c + j, owner = col / share;
-      st_cluster_v4(map_to_cta(mine + (uint32_t)(col - owner * share) * 4u, (uint32_t)owner), __uint_as_float(r[j]),
-                    __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-    }
+    for (int j = 0; j < 16; ++j)
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(at + (uint32_t)j * SPLIT_COL_BYTES), "f"(__uint_as_float(r[j])) : "memory");
   }
 }
 
@@ -238,18 +239,20 @@ __device__ __forceinline__ void finish_split_cols(const PrefillArgs& a, uint32_t
                                                   int row_in_tile, int c0, int cols) {
   const int row = m0 + row_in_tile;
   if (row >= a.M) return;
-  const uint32_t row_bytes = split_row_bytes(share), slot_bytes = BM * row_bytes;
+  const uint32_t slot_bytes = (uint32_t)share * SPLIT_COL_BYTES;
   const long long place = cache_place(a, row);
   for (int c = c0; c < c0 + cols; c += 8) {
     const int col = n0 + c;
     if (col >= a.N) break;                         // N is a multiple of 8: a group lies inside the matrix or outside
-    const uint32_t at = recv + (uint32_t)row_in_tile * row_bytes + (uint32_t)c * 4u;
+    const uint32_t at = recv + (uint32_t)c * SPLIT_COL_BYTES + (uint32_t)row_in_tile * 4u;
     float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int p = 0; p < splits; ++p) {
-      float4 lo, hi;
-      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w) : "r"(at + p * slot_bytes));
-      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w) : "r"(at + p * slot_bytes + 16u));
-      y[0] += lo.x; y[1] += lo.y; y[2] += lo.z; y[3] += lo.w; y[4] += hi.x; y[5] += hi.y; y[6] += hi.z; y[7] += hi.w;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v;
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(at + p * slot_bytes + (uint32_t)j * SPLIT_COL_BYTES));
+        y[j] += v;
+      }
     }
     if (a.bias) {
       const float4 b0 = __ldg(reinterpret_cast<const float4*>(a.bias + col)), b1 = __ldg(reinterpret_cast<const float4*>(a.bias + col + 4));
@@ -911,7 +914,7 @@ int cluster_capacity(int sms, int size) {
 // part holds a K block, every CTA's share of the columns is whole 16-column pieces.
 bool split_fits(int tiles, int num_kb, int splits, int sms, int bn) {
   if (splits < 2 || splits > 8 || bn % (16 * splits) != 0 || tiles > cluster_capacity(sms, splits)) return false;
-  if (BM * (bn + 4 * splits) * 4 > SMEM_TILES) return false;        // the sums meet in the ring
+  if (BM * bn * 4 > SMEM_TILES) return false;                       // the sums meet in the ring
   const int part = (num_kb + splits - 1) / splits;
   return part >= 2 && (splits - 1) * part < num_kb;
 }
@@ -921,10 +924,11 @@ double whole_tiles_us(int M, int N, int K, int bn, int sms, bool wide_rows);
 
 // Does splitting K beat whole tiles going round the CTAs, and with which tile width and how many parts?
 // Times from the model above; the two cluster barriers, the exchange of the sums through shared memory and
-// their addition cost the split form about 1 us + 24 ns per column of the tile + 0.45 us per CTA of the
-// cluster on top of its K blocks (measured: 2 us for two CTAs and 64 columns, 5.5 for two and 192, 3.5 for
-// four and 64, 7.6 for eight and 128).
-constexpr double SPLIT_FIX_US = 1.0, SPLIT_FIX_PER_COL = 0.024, SPLIT_FIX_PER_CTA = 0.45;
+// their addition cost the split form about 16 ns per column of the tile + 0.35 us per CTA of the cluster on
+// top of its K blocks (fitted to 261 measured split products of GPT-2 small and XL layer shapes at 128 to 1,024
+// rows, residual 0.7 us rms; with a split taken where it is modelled 10 % ahead, the choice is within 1.4 % of the
+// best measured form in 46 of 48 cases and 4.3 % behind at worst).
+constexpr double SPLIT_FIX_US = 0.0, SPLIT_FIX_PER_COL = 0.016, SPLIT_FIX_PER_CTA = 0.35, SPLIT_MARGIN = 0.90;
 bool split_pays(int M, int N, int K, int sms, int tile_n, bool wide_rows, int* bn_out, int* splits_out) {
   const int m_tiles = (M + BM - 1) / BM, num_kb = (K + BLOCK_K - 1) / BLOCK_K;
   if (N % 8 != 0) return false;
@@ -945,7 +949,7 @@ bool split_pays(int M, int N, int K, int sms, int tile_n, bool wide_rows, int* b
       if (best_split < 0 || us < best_split) { best_split = us; *bn_out = bn; *splits_out = sp; }
     }
   }
-  return best_split > 0 && best_split < 0.95 * best_whole;
+  return best_split > 0 && best_split < SPLIT_MARGIN * best_whole;
 }
 
 // rows x n float32, row-major; box of 128 rows x 32 columns (128 bytes), 128-byte swizzle: a chunk of the

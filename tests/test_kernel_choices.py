@@ -23,7 +23,7 @@ SMALL = {"qkv": (2304, 768), "proj": (768, 768), "fc": (3072, 768), "proj2": (76
 
 @pytest.mark.parametrize("shape,M,tile", [
     (XL["qkv"], 2048, 192), (XL["fc"], 2048, 256), (XL["proj"], 2048, 192), (XL["qkv"], 1024, 160), (XL["fc"], 768, 160),
-    (XL["fc"], 256, 96), (XL["proj"], 768, 96), (XL["qkv"], 512, 160),
+    (XL["fc"], 256, 96), (XL["proj"], 1024, 96), (XL["qkv"], 512, 160),
     (SMALL["qkv"], 2048, 256), (SMALL["fc"], 2048, 192), (SMALL["proj"], 2048, 96),
 ])
 def test_tile_width_is_the_measured_best(shape, M, tile):
@@ -39,6 +39,15 @@ def test_long_k_with_few_tiles_is_split(shape, M):
     assert parts > 1, (tile, parts)
 
 
+@pytest.mark.parametrize("shape,M,plan", [
+    (XL["proj"], 128, (64, 4)), (XL["proj"], 768, (160, 2)), (XL["proj2"], 128, (128, 8)), (XL["proj2"], 512, (256, 4)),
+    (XL["proj2"], 1024, (192, 2)), (XL["qkv"], 128, (96, 2)), (SMALL["proj2"], 768, (192, 4)), (SMALL["proj"], 256, (32, 2)),
+])
+def test_split_plan_is_the_measured_best(shape, M, plan):
+    N, K = shape
+    assert ops.prefill_plan(M, N, K) == plan
+
+
 def test_a_split_fits_the_sms_and_the_tile():
     for M in (65, 100, 128, 300, 576, 1000, 2048):
         for N, K in list(XL.values()) + list(SMALL.values()) + [(264, 12800), (8, 64), (50257, 1600)]:
@@ -49,7 +58,7 @@ def test_a_split_fits_the_sms_and_the_tile():
                     tiles = -(-M // 128) * -(-N // tile)
                     blocks = -(-K // 64)
                     assert tiles * parts <= sms and tile % (16 * parts) == 0 and N % 8 == 0
-                    assert 128 * (tile + 4 * parts) * 4 <= 196608                # the sums meet in the stage ring
+                    assert 128 * tile * 4 <= 196608                              # the sums meet in the stage ring
                     assert (parts - 1) * -(-blocks // parts) < blocks       # every part has a K block
 
 

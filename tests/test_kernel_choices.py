@@ -19,6 +19,7 @@ except RuntimeError as problem:
 
 XL = {"qkv": (4800, 1600), "proj": (1600, 1600), "fc": (6400, 1600), "proj2": (1600, 6400)}
 SMALL = {"qkv": (2304, 768), "proj": (768, 768), "fc": (3072, 768), "proj2": (768, 3072)}
+LARGE = {"qkv": (3840, 1280), "proj": (1280, 1280), "fc": (5120, 1280), "proj2": (1280, 5120)}
 
 
 @pytest.mark.parametrize("shape,M,tile", [
@@ -42,6 +43,9 @@ def test_long_k_with_few_tiles_is_split(shape, M):
 @pytest.mark.parametrize("shape,M,plan", [
     (XL["proj"], 128, (64, 4)), (XL["proj"], 768, (160, 2)), (XL["proj2"], 128, (128, 8)), (XL["proj2"], 512, (256, 4)),
     (XL["proj2"], 1024, (192, 2)), (XL["qkv"], 128, (96, 2)), (SMALL["proj2"], 768, (192, 4)), (SMALL["proj"], 256, (32, 2)),
+    # a shape the model was not fitted to (GPT-2 large), measured afterwards: the pick is the best of 8 widths x 4 splits
+    (LARGE["qkv"], 576, (160, 1)), (LARGE["proj"], 576, (96, 2)), (LARGE["fc"], 576, (192, 1)), (LARGE["proj2"], 576, (256, 4)),
+    (LARGE["proj2"], 192, (128, 4)), (LARGE["qkv"], 1088, (256, 1)), (LARGE["proj2"], 1088, (160, 2)),
 ])
 def test_split_plan_is_the_measured_best(shape, M, plan):
     N, K = shape

@@ -252,6 +252,13 @@ class CacheManager:
         pool = self.pools[g]
         return 0 if pool is None else len(pool.free)
 
+    def pages_held(self, slots) -> list:
+        """Per group: the pages that each of ``slots`` holds, as an array (None for a group of
+        state slots).  With ``free_pages`` this lets a planner try portions of other sizes by
+        arithmetic and call ``reserve`` once, for the one that fits."""
+        slots_a = np.fromiter((int(s) for s in slots), dtype=np.int64, count=len(slots))
+        return [None if pool is None else self.num_pages[g][slots_a].astype(np.int64) for g, pool in enumerate(self.pools)]
+
     def reserve(self, entries) -> Reservation:
         """entries: (slot, start, count).  Each must start at the request's
         committed length.  All or nothing: raises ``OutOfPages`` with nothing

@@ -96,26 +96,28 @@ class Engine:
     def _launch(self, plan: ScheduledStep, tokens_from: torch.Tensor | None = None) -> "_Launched":
         """Hands a planned step to the GPU: upload, forward, sampling, and the copy
         of the sampled tokens to the host on a stream of its own.  ``tokens_from``:
-        the sampled tokens of the step before, still on the device, are this step's
-        tokens (one per entry, same order)."""
-        ahead = tokens_from is not None
+        the sampled tokens of the step before, still on the device; the plan's
+        ``pending`` entries take theirs from there (``token_rows``)."""
+        take = plan.token_rows                  # the first len(take) entries decode with tokens that are still on their way
+        if take and tokens_from is None:
+            raise RuntimeError("a step planned ahead needs the sampled tokens of the step before it")
         try:
             entries = [StepEntry(e.state.slot, e.start,
-                                 [0] * e.count if ahead else e.state.tokens[e.start:e.start + e.count],
+                                 [0] if e.pending else e.state.tokens[e.start:e.start + e.count],
                                  [e.count - 1] if e.sample else []) for e in plan.entries]
-            rows = [e.state for e in plan.entries if e.sample]
-            take = plan.token_rows if ahead else None
+            sampling = [e for e in plan.entries if e.sample]
+            rows = [e.state for e in sampling]
             if self.decode_graphs is not None and plan.decode_only:
-                logits = self.decode_graphs.run(entries, tokens_from=tokens_from, take_rows=take)
+                logits = self.decode_graphs.run(entries, tokens_from=tokens_from if take else None, take_rows=take)
             else:
-                logits = self.runner.run(entries, tokens_from=tokens_from, take_rows=take)
+                logits = self.runner.run(entries, tokens_from=tokens_from if take else None, take_rows=take)
             sampled = host = done = None
             if rows:
-                pending = 1 if ahead else 0         # a token of each row is still on its way
-                banned = ([(i, t) for i, s in enumerate(rows) for t in self.scheduler.banned_tokens(s, pending)]
+                pending = [1 if e.pending else 0 for e in sampling]      # a token of the row is still on its way
+                banned = ([(i, t) for i, s in enumerate(rows) for t in self.scheduler.banned_tokens(s, pending[i])]
                           if self.scheduler.with_min_tokens else ())
                 sampled = self.sampler.sample(logits, [s.request.sampling for s in rows], [s.seed for s in rows],
-                                              [s.generated + pending for s in rows], banned=banned)
+                                              [s.generated + p for s, p in zip(rows, pending)], banned=banned)
                 host = self._pinned.pop() if self._pinned else None
                 if host is None or host.numel() < len(rows):
                     host = torch.empty(max(len(rows), self.config.max_requests), dtype=torch.int32, pin_memory=True)

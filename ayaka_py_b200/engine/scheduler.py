@@ -38,7 +38,7 @@ class RequestRefused(ValueError):
     """The request can never run in this engine (too long, duplicate id, ...)."""
 
 
-@dataclass
+@dataclass(eq=False)             # a request is itself: lists of states are searched by identity
 class RequestState:
     request: Request
     ordinal: int                      # admission order: FCFS key and seed source
@@ -65,12 +65,13 @@ class ScheduledEntry:
     start: int
     count: int
     sample: bool                      # the portion ends at the last known token
+    pending: bool = False             # its one token is being sampled by the step in flight (see ``lookahead``)
 
     @property
     def is_decode(self) -> bool:
         """One token of a request whose other tokens are all cached."""
         state = self.state
-        return len(state.tokens) - state.computed == 1 and state.computed > 0
+        return self.pending or (len(state.tokens) - state.computed == 1 and state.computed > 0)
 
 
 @dataclass
@@ -78,8 +79,9 @@ class ScheduledStep:
     entries: list[ScheduledEntry]
     reservation: Reservation
     decode_only: bool
-    # A step planned ahead of the tokens of the step before it: for each entry, the row of that
-    # step's sampled tokens that is this entry's token (None: the same rows in the same order).
+    # A step planned ahead of the tokens of the step before it: its first len(token_rows) entries are the
+    # ``pending`` ones, and token_rows[i] is the row of that step's sampled tokens that is entry i's token
+    # (None: no entry is pending).
     token_rows: list[int] | None = None
 
 
@@ -167,23 +169,57 @@ class Scheduler:
                     return None
                 self._preempt(victim)
 
-    def _plan(self) -> ScheduledStep | None:
+    def _plan(self, after: ScheduledStep | None = None) -> ScheduledStep | None:
+        """One pass of the rules above.  ``after``: the step in flight (already advanced, its
+        tokens not yet known), when the step is planned ahead of them: see ``lookahead``."""
         budget = self.batch_tokens
         entries: list[ScheduledEntry] = []
+        ahead = after is not None
+        row_of: dict[int, int] = {}            # id(state) -> row of the step in flight that samples its next token
+        leaving: set[int] = set()              # requests that the token on its way finishes by length
+        if ahead:
+            row = 0
+            for e in after.entries:
+                if not e.sample:
+                    continue
+                s = e.state
+                if s.finish_reason is None:
+                    if len(s.tokens) != s.computed:
+                        return None            # not advanced, or resolved already: nothing to plan ahead of
+                    stop = s.request.stop
+                    if s.generated + 1 >= stop.max_tokens or len(s.tokens) + 1 >= self.max_model_len:
+                        leaving.add(id(s))
+                    else:
+                        row_of[id(s)] = row
+                row += 1
 
         # 1. decoding first, round robin from the cursor
-        decoders = [s for s in self.running if len(s.tokens) - s.computed == 1 and s.computed > 0]
-        if decoders:
-            if len(decoders) > budget:          # not all fit: take turns
-                start = self.cursor % len(decoders)
-                decoders = (decoders[start:] + decoders[:start])[:budget]
-                self.cursor += budget
+        if ahead:
+            # every decoder's token is on its way; one whose token is known was left out of the step in
+            # flight for want of budget, and the pass that knows the tokens takes the turns
+            if any(len(s.tokens) - s.computed == 1 and s.computed > 0 for s in self.running):
+                return None
+            decoders = [s for s in self.running if id(s) in row_of]
+            if len(decoders) > budget:
+                return None
             for s in decoders:
-                entries.append(ScheduledEntry(s, s.computed, 1, True))
+                entries.append(ScheduledEntry(s, s.computed, 1, True, pending=True))
                 budget -= 1
+        else:
+            decoders = [s for s in self.running if len(s.tokens) - s.computed == 1 and s.computed > 0]
+            if decoders:
+                if len(decoders) > budget:          # not all fit: take turns
+                    start = self.cursor % len(decoders)
+                    decoders = (decoders[start:] + decoders[:start])[:budget]
+                    self.cursor += budget
+                for s in decoders:
+                    entries.append(ScheduledEntry(s, s.computed, 1, True))
+                    budget -= 1
 
         # 2. prompt portions: the unfinished prompt first, then waiting requests
-        partial = [s for s in self.running if len(s.tokens) - s.computed > 1 or s.computed == 0]
+        partial = [s for s in self.running if (len(s.tokens) - s.computed > 1 or s.computed == 0)
+                   and id(s) not in row_of and id(s) not in leaving]
+        admitted: list[RequestState] = []
         for s in partial:
             if budget < 1:
                 break
@@ -203,6 +239,7 @@ class Scheduler:
                 break
             self.waiting.popleft()
             self.running.append(s)
+            admitted.append(s)
             entries.append(ScheduledEntry(s, 0, n, n == s.remaining))
             budget -= n
             if n < s.remaining:
@@ -240,6 +277,15 @@ class Scheduler:
                     break
                 except OutOfPages:            # not expected after the arithmetic above; the ladder goes on
                     pass
+            if ahead:
+                # short of pages: the pass that knows who has finished decides what gives; what this pass
+                # admitted goes back to the head of the line, in its order
+                for s in reversed(admitted):
+                    self.cache.close(s.slot)
+                    s.slot = None
+                    self.running.remove(s)
+                    self.waiting.appendleft(s)
+                return None
             shrunk = True
             prefills = [i for i in range(len(entries)) if not decode[i]]
             big = [i for i in prefills if entries[i].count > 1]
@@ -269,7 +315,8 @@ class Scheduler:
         decoding = sum(1 for e in entries if e.is_decode)
         self.stats.decode_tokens += decoding
         self.stats.prefill_tokens += sum(e.count for e in entries) - decoding
-        return ScheduledStep(entries, reservation, decoding == len(entries))
+        return ScheduledStep(entries, reservation, decoding == len(entries),
+                             [row_of[id(e.state)] for e in entries if e.pending] or None)
 
     def _pick_victim(self, entries) -> RequestState | None:
         """The newest running request that holds pages; never the only one."""
@@ -321,40 +368,23 @@ class Scheduler:
         return finished
 
     def lookahead(self, step: ScheduledStep) -> ScheduledStep | None:
-        """The step after ``step``, planned before ``step``'s tokens are known, or
-        None when that cannot be done without guessing more than "nobody stops on a
-        stop id": ``step`` (already advanced) must be a pure decode step of every
-        running request, nobody waits, and the pages are there.  A request that
-        reaches a length limit with the token on its way is known to finish: it is
-        left out of the next step (its token is its last) and the others go on.  A
-        request that stops on the token on its way (EOS, a stop id) has then one
-        more token computed than it needed; ``resolve`` drops it.  The reference
-        keeps one step in flight (``configs/scheduler.py:131``); this is the same
-        loop with the host's share of the next step done while the GPU works on
-        this one."""
-        if not step.decode_only or self.waiting or len(step.entries) != len(self.running):
+        """The step after ``step``, planned before ``step``'s tokens are known, or None
+        when that cannot be done without guessing more than "nobody stops on a stop
+        id".  ``step`` has been advanced.  The rules are ``_plan``'s, with three
+        differences.  A request whose next token ``step`` samples decodes with that
+        token, which the engine takes from the device (``pending`` entries, first in
+        the step; ``token_rows``).  A request that reaches a length limit with the
+        token on its way is known to finish: it is left out, and its pages and slot
+        stay taken until its token is there.  And nothing is taken away to make room:
+        when pages are short, or more requests decode than the budget holds, the
+        answer is None and the step is planned when the tokens are known.  A request
+        that stops on the token on its way (EOS, a stop id) has then one more token
+        computed than it needed; ``resolve`` drops it.  The reference keeps one step in
+        flight (``configs/scheduler.py:131``); this is the same loop with the host's
+        share of the next step done while the GPU works on this one."""
+        if not self.running and not self.waiting:
             return None
-        if len(step.entries) > self.batch_tokens:
-            return None
-        rows, going_on = [], []
-        for row, (e, s) in enumerate(zip(step.entries, self.running)):
-            if e.state is not s or not e.sample or s.finish_reason is not None or len(s.tokens) != s.computed:
-                return None
-            stop = s.request.stop
-            if s.generated + 1 >= stop.max_tokens or len(s.tokens) + 1 >= self.max_model_len:
-                continue                           # finishes by length when its token arrives: not in the next step
-            rows.append(row)
-            going_on.append(s)
-        if not going_on:
-            return None
-        entries = [ScheduledEntry(s, s.computed, 1, True) for s in going_on]
-        try:
-            reservation = self.cache.reserve([(e.state.slot, e.start, 1) for e in entries])
-        except OutOfPages:
-            return None
-        self.stats.steps += 1
-        self.stats.decode_tokens += len(entries)
-        return ScheduledStep(entries, reservation, True, None if len(rows) == len(step.entries) else rows)
+        return self._plan(after=step)
 
     def banned_tokens(self, s: RequestState, pending: int = 0) -> tuple[int, ...]:
         """Token ids that ``s`` must not sample next: its stop ids, and EOS unless it

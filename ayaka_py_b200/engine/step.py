@@ -196,9 +196,10 @@ class StepRunner:
         self._field(h, "req_slot", R)[:] = slots
         self._field(h, "req_kv_len", R)[:] = ends
         if take_rows is not None:
-            if len(take_rows) != n or T != R:
-                raise ValueError("rows of another step's tokens can be named only for entries of one token each")
-            self._field(h, "take_rows", R)[:n] = take_rows
+            k = len(take_rows)
+            if k > n or any(order[i] != i or lengths[i] != 1 for i in range(k)):
+                raise ValueError("rows of another step's tokens can be named only for the first entries, of one token each")
+            self._field(h, "take_rows", R)[:k] = take_rows
         C = self.cache.columns
         for g in self.kv_groups:
             rows = self._field(h, f"table{g}", R * C).reshape(R, C)
@@ -245,8 +246,9 @@ class StepRunner:
             take_rows: Sequence[int] | None = None) -> torch.Tensor:
         """Logits [S, V] float32 on the device.  The caller has reserved the
         step in the cache manager and commits it afterwards.  ``tokens_from``
-        (int32 on the device): the tokens of a step of single tokens whose host copies
-        are not known yet, entry i taking row ``take_rows[i]`` of it (None: row i)."""
+        (int32 on the device): tokens whose host copies are not known yet, entry i of
+        the first ``len(take_rows)`` (each of one token) taking row ``take_rows[i]`` of
+        it (None: every entry brings one token and takes row i)."""
         ctx = self.prepare(entries, take_rows=take_rows)
         if tokens_from is not None:
             self.place_tokens(ctx, len(entries), tokens_from, take_rows)
@@ -254,10 +256,14 @@ class StepRunner:
 
     @staticmethod
     def place_tokens(ctx: StepContext, n: int, tokens_from: torch.Tensor, take_rows) -> None:
-        """Copies the step's tokens on the device from the sampled tokens of the step before."""
-        if ctx.num_rows != ctx.num_requests:      # then the packed order is the caller's order
-            raise ValueError("tokens can come from the device only for entries of one token each")
+        """Copies tokens of the step on the device from the sampled tokens of the step before:
+        the first n entries' (row i of them each), or the first len(take_rows) entries' (row
+        take_rows[i] each).  Single-token entries are packed first and in the caller's order, so
+        these are the step's first rows."""
         if take_rows is None:
+            if ctx.num_rows != ctx.num_requests:
+                raise ValueError("without named rows, tokens can come from the device only for a step of single tokens")
             ctx.tokens[:n].copy_(tokens_from[:n])
-        else:
-            torch.index_select(tokens_from, 0, ctx.take_rows[:n], out=ctx.tokens[:n])
+        elif len(take_rows):
+            k = len(take_rows)
+            torch.index_select(tokens_from, 0, ctx.take_rows[:k], out=ctx.tokens[:k])

@@ -257,17 +257,19 @@ def test_lookahead_gives_the_same_tokens_and_reasons(seed):
     assert len(results[0]) == 6
 
 
-def test_lookahead_refuses_what_it_cannot_know():
+def test_lookahead_plans_past_prompts_and_leaves_out_who_finishes():
     sched, cache = make(pages=20, page_size=4, max_requests=4, batch_tokens=8)
     sched.add(req(0, 3, max_tokens=5))
     sched.add(req(1, 2, max_tokens=2))
-    plan = sched.schedule()                        # both prompts: not a decode step
+    plan = sched.schedule()                        # both prompts, both sampled
+    assert sched.lookahead(plan) is None           # not handed over yet: nothing is on its way
     sched.advance(plan)
-    assert sched.lookahead(plan) is None
+    ahead = sched.lookahead(plan)                  # both decode with the tokens on their way
+    assert ahead is not None and ahead.decode_only and ahead.token_rows == [0, 1]
+    assert [(e.state.request.request_id, e.start, e.count, e.pending) for e in ahead.entries] == [("r0", 3, 1, True), ("r1", 2, 1, True)]
+    sched.advance(ahead)
     sched.resolve(plan, {"r0": 7, "r1": 7})
-    plan = sched.schedule()                        # decode step; r1 reaches max_tokens with the token on its way
-    assert plan.decode_only and [e.state.request.request_id for e in plan.entries] == ["r0", "r1"]
-    sched.advance(plan)
+    plan = ahead                                   # r1 reaches max_tokens with the token on its way
     ahead = sched.lookahead(plan)                  # ... so it is left out of the next step, and r0 takes row 0 of the tokens
     assert ahead is not None and [e.state.request.request_id for e in ahead.entries] == ["r0"]
     assert ahead.token_rows == [0] and [(e.start, e.count) for e in ahead.entries] == [(4, 1)]
@@ -275,17 +277,82 @@ def test_lookahead_refuses_what_it_cannot_know():
     done = sched.resolve(plan, {"r0": 7, "r1": 7})
     assert [s.request.request_id for s in done] == ["r1"]
     cache.check_invariants()
+    plan = ahead
+    sched.add(req(2, 2, max_tokens=1))             # somebody waits now: its prompt goes beside the decoding request
+    ahead = sched.lookahead(plan)
+    assert [(e.state.request.request_id, e.start, e.count, e.pending, e.sample) for e in ahead.entries] == \
+        [("r0", 5, 1, True, True), ("r2", 0, 2, False, True)]
+    assert ahead.token_rows == [0] and not ahead.decode_only
+    sched.advance(ahead)
+    sched.resolve(plan, {"r0": 7})
+    plan = ahead
+    ahead = sched.lookahead(plan)                  # r0 has one token to go and r2 one of one: r0 goes on, r2 leaves
+    assert [(e.state.request.request_id, e.start) for e in ahead.entries] == [("r0", 6)] and ahead.token_rows == [0]
+    sched.advance(ahead)
+    sched.resolve(plan, {"r0": 7, "r2": 7})
+    assert sched.lookahead(ahead) is None          # r0's last token is on its way and nobody else is there
     sched.resolve(ahead, {"r0": 7})
+    assert not sched.states or sorted(sched.states) == ["r0", "r1", "r2"]
+    assert not sched.has_work()
+    cache.assert_clean()
+
+
+def test_lookahead_goes_on_with_a_prompt_in_portions():
+    sched, cache = make(pages=40, page_size=4, max_requests=4, batch_tokens=6, prefill_chunk=4, max_len=64)
+    sched.add(req(0, 2, max_tokens=9))
+    plan = sched.schedule()
+    sched.update(plan, {"r0": 7})
+    sched.add(req(1, 10, max_tokens=3))
+    plan = sched.schedule()                        # r0 decodes, r1's first portion beside it
+    assert [(e.state.request.request_id, e.start, e.count, e.sample) for e in plan.entries] == [("r0", 2, 1, True), ("r1", 0, 4, False)]
+    sched.advance(plan)
+    for start, count, sample in ((4, 4, False), (8, 2, True)):
+        ahead = sched.lookahead(plan)              # r0's token is on its way; r1's next portion is known
+        assert ahead.token_rows == [0]
+        assert [(e.state.request.request_id, e.start, e.count, e.sample, e.pending) for e in ahead.entries][1] == ("r1", start, count, sample, False)
+        sched.advance(ahead)
+        sched.resolve(plan, {"r0": 7})
+        cache.check_invariants()
+        plan = ahead
+    ahead = sched.lookahead(plan)                  # both decode now: r0's token is row 0, r1's row 1
+    assert ahead.decode_only and ahead.token_rows == [0, 1] and all(e.pending for e in ahead.entries)
+    sched.advance(ahead)
+    sched.resolve(plan, {"r0": 7, "r1": 7})
+    sched.resolve(ahead, {"r0": 7, "r1": 7})
+    cache.check_invariants()
+
+
+def test_lookahead_takes_nothing_away():
+    # 5 usable pages of 4 tokens, two requests of 7 tokens hold 4; a third waits for 8 tokens
+    sched, cache = make(pages=6, page_size=4, max_requests=3, batch_tokens=16, prefill_chunk=16, max_len=32)
+    sched.add(req(0, 7, max_tokens=12))
+    sched.add(req(1, 7, max_tokens=12))
+    plan = sched.schedule()
+    sched.update(plan, {"r0": 1, "r1": 1})
     plan = sched.schedule()
     sched.advance(plan)
-    ahead = sched.lookahead(plan)                  # r0 alone, two tokens to go: the same rows, no map
-    assert ahead is not None and [(e.start, e.count) for e in ahead.entries] == [(6, 1)] and ahead.token_rows is None
-    sched.advance(ahead)
-    sched.add(req(2, 2))                           # somebody waits now: no further lookahead
-    sched.resolve(plan, {"r0": 7})
-    assert sched.lookahead(ahead) is None
-    sched.resolve(ahead, {"r0": 7})
-    assert "r0" not in sched.states
+    sched.add(req(2, 8, max_tokens=2))
+    free, slots, waiting = cache.free_pages(0), len(cache.free_slots), [s.request.request_id for s in sched.waiting]
+    assert sched.lookahead(plan) is None           # r0 and r1 need a page each at position 8 and r2 two: 1 is free
+    assert (cache.free_pages(0), len(cache.free_slots)) == (free, slots)           # the admission was taken back
+    assert [s.request.request_id for s in sched.waiting] == waiting and len(sched.running) == 2
+    assert sched.states["r2"].slot is None
+    cache.check_invariants()
+    sched.resolve(plan, {"r0": 1, "r1": 1})
+    assert sched.schedule() is not None            # the pass that knows the tokens decides what gives
+    # more requests decoding than the budget holds: the turns are taken by the pass that knows the tokens
+    sched, cache = make(pages=40, page_size=4, max_requests=4, batch_tokens=3, prefill_chunk=3, max_len=32)
+    for i in range(3):
+        sched.add(req(i, 1, max_tokens=6))
+    plan = sched.schedule()
+    sched.update(plan, {e.state.request.request_id: 1 for e in plan.entries})
+    sched.batch_tokens = 2
+    plan = sched.schedule()                        # two of the three decode; the third one's token is known and waits its turn
+    assert len(plan.entries) == 2
+    sched.advance(plan)
+    assert sched.lookahead(plan) is None
+    sched.resolve(plan, {e.state.request.request_id: 1 for e in plan.entries})
+    assert [e.state.request.request_id for e in sched.schedule().entries] == ["r2", "r0"]
 
 
 def test_lookahead_leaves_out_every_request_that_finishes_by_length():
@@ -307,7 +374,7 @@ def test_lookahead_leaves_out_every_request_that_finishes_by_length():
         sched.resolve(plan, {e.state.request.request_id: 7 for e in plan.entries})
         cache.check_invariants()
         plan = ahead
-    assert seen == [(["r0", "r1", "r2"], None), (["r0", "r2"], [0, 2]), (["r0", "r2"], None), (["r0"], [0])]
+    assert seen == [(["r0", "r1", "r2"], [0, 1, 2]), (["r0", "r2"], [0, 2]), (["r0", "r2"], [0, 1]), (["r0"], [0])]
     sched.resolve(plan, {"r0": 7})
     assert sorted(sched.states) == ["r0"]
 
@@ -410,7 +477,7 @@ def test_lookahead_needs_pages_and_a_plain_decode_step():
     sched.add(req(0, 7, max_tokens=12))
     sched.add(req(1, 7, max_tokens=12))
     plan = sched.schedule()
-    assert not plan.decode_only and sched.lookahead(plan) is None            # a prompt step is never looked past
+    assert not plan.decode_only and sched.lookahead(plan) is None            # not handed over yet: nothing to look past
     sched.update(plan, {"r0": 1, "r1": 1})
     plan = sched.schedule()                                                   # decode at position 7: the pages exist
     assert plan.decode_only

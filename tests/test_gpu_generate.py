@@ -229,6 +229,50 @@ def test_lookahead_gives_the_same_tokens(model_folders, graph):
     assert want["r0"][1] == "stop" and len(want["r0"][0]) <= 14
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_lookahead_past_prompt_portions_and_page_pressure(model_folders, dtype):
+    """Steps planned ahead that hold prompt portions and newly admitted requests beside the decoding ones,
+    in a pool so small that pages run out (the step is then planned when its tokens are known, and requests
+    are preempted and recompute): the same tokens as the plain loop, and the same steps."""
+    from ayaka_py_b200 import EngineConfig, Request, SamplingParams, StopCriteria
+    from ayaka_py_b200.engine.engine import Engine
+    from ayaka_py_b200.engine.loading import load_model
+    folder, cfg, weights = model_folders["B"]
+    lens, news, arrive = [70, 45, 60, 30, 52], [22, 30, 12, 26, 9], [0, 0, 3, 9, 20]
+    prompts = tiny_models.prompts(cfg, lens, seed=37)
+    _, model = load_model(folder, dtype, "cuda")
+
+    def run(lookahead):
+        config = EngineConfig(dtype=dtype, page_size=8, kv_pages=27, batch_tokens=24, prefill_chunk=16, max_requests=4,
+                              decode_graph=True, lookahead=lookahead)
+        engine = Engine(model, config, eos_token_id=None)
+        step, nxt, ahead, kinds = 0, 0, 0, set()
+        while engine.has_work() or nxt < len(lens):
+            while nxt < len(lens) and arrive[nxt] <= step:
+                engine.submit(Request(f"r{nxt}", prompts[nxt], SamplingParams(temperature=0.0),
+                                      StopCriteria(max_tokens=news[nxt], ignore_eos=True)))
+                nxt += 1
+            if engine.has_work():
+                engine.step()
+                if engine._inflight is not None:
+                    ahead += 1
+                    plan = engine._inflight.plan
+                    kinds.add(("decode" if plan.decode_only else "mixed", bool(plan.token_rows)))
+            step += 1
+        engine.cache.assert_clean()
+        stats = engine.scheduler.stats
+        return [engine.finished[f"r{i}"].token_ids for i in range(len(lens))], ahead, kinds, (stats.steps, stats.preemptions)
+
+    want, none_ahead, _, plain_stats = run(False)
+    got, some_ahead, kinds, ahead_stats = run(True)
+    assert none_ahead == 0 and some_ahead > 20
+    assert ("mixed", True) in kinds and ("decode", True) in kinds          # portions beside tokens on their way, and pure decoding
+    assert plain_stats[1] > 0 and ahead_stats == plain_stats              # pages ran out, and both loops took the same steps
+    assert got == want
+    for i in (0, 3):
+        assert got[i] == plain_gpt2.greedy_generate(cfg, weights, prompts[i], news[i]) or dtype == "bfloat16"
+
+
 @pytest.mark.parametrize("graph", [False, True], ids=["eager", "graphs"])
 def test_stop_ids_are_banned_until_min_tokens(model_folders, graph):
     """``request/stream.py:130-163``: before ``min_tokens`` the stop ids are masked out of the

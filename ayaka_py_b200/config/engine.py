@@ -24,7 +24,7 @@ class EngineConfig:
     prefill_chunk: int = 128      # largest portion of one prompt in a step
     max_model_len: int | None = None   # None: the model's own limit
     decode_graph: bool = True     # replay pure-decode steps from CUDA graphs (False: every kernel launched from Python)
-    lookahead: bool = True        # plan and launch the next decode step while this one's tokens are on their way
+    lookahead: bool = True        # plan and launch the next step while this one's tokens are on their way
     seed: int = 0                 # base of the seeds of requests that name none
 
     def __post_init__(self) -> None:

@@ -3,11 +3,13 @@
 One step is in flight at a time, as in the reference's default
 (``configs/scheduler.py:131``; ``runtime/engine.py:180-279``).  With
 ``EngineConfig.lookahead`` the host's share of the next step overlaps the GPU's
-work on this one: when a step is a pure decode step of every running request
-and nobody can reach a length limit, the next step is planned, uploaded and
-launched (its tokens copied from the sampler's output on the device) before this
-step's tokens have reached the host.  The tokens a request sees are the same
-either way; a request that stops on EOS or a stop id has one more position
+work on this one: the next step is planned by the scheduler's own rules while
+this step's tokens are on their way (``Scheduler.lookahead``: requests whose
+token is being sampled decode with it, prompts go on in portions, waiting
+requests are admitted; nothing is preempted or shrunk ahead of the tokens),
+uploaded and launched, the tokens that are not on the host yet copied from the
+sampler's output on the device.  The tokens a request sees are the same either
+way; a request that stops on EOS or a stop id has one more position
 computed than it needed, which is dropped.
 """
 
